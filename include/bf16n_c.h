@@ -1,0 +1,139 @@
+/* C ABI of the B200 (sm_100a) BF16N library: libbf16n_b200.so.
+ *
+ * Every entry point replaces one function of the reference project's C++ core (namespace bf16n); the comment on each
+ * declaration names it by file:line inside the reference checkout.  Conventions:
+ *   - plain C types only; device pointers are ordinary pointers into CUDA device memory owned by the caller;
+ *   - `stream` is a cudaStream_t passed as void*; launchers only enqueue work on it: no allocation, no host
+ *     synchronisation, no environment lookups, so every launch can be captured into a CUDA graph after bf16n_init();
+ *   - return value: BF16N_OK, or an error code with a message in bf16n_last_error() (thread-local). The reference
+ *     throws std::invalid_argument where this returns BF16N_EINVAL and std::runtime_error elsewhere; the C++ wrappers
+ *     in include/bf16n/ re-throw exactly those.
+ */
+#ifndef BF16N_C_H
+#define BF16N_C_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { BF16N_OK = 0, BF16N_EINVAL = 1, BF16N_ECUDA = 2, BF16N_EINTERNAL = 3 };
+
+enum { BF16N_FMT_NIBBLE = 1, BF16N_FMT_HUFFMAN = 2, BF16N_FMT_HUFPAIR = 3 }; /* core/include/bf16n/format.h:12-14 */
+enum { BF16N_FLAG_CHUNK_MAJOR = 1, BF16N_FLAG_FRAG_ORDER = 2 };             /* format.h:27-33 */
+
+/* Device view of one encoded matrix; fields parsed once on the host from the aux header.
+ * Replaces struct bf16n::weight (core/include/bf16n/launch.h:14-23). */
+typedef struct bf16n_weight {
+    const uint8_t * plane; /* rows*K sign|mantissa bytes (device) */
+    const uint8_t * aux;   /* header + exponent data (device) */
+    int32_t format;
+    int32_t R;             /* rows per unit; 0 for NIBBLE */
+    int64_t K;
+    int64_t rows;
+    int32_t cm;            /* HUFPAIR chunk-major units */
+    int32_t fo;            /* HUFPAIR fragment-order bands */
+    uint64_t off_a, off_b, off_c, off_d;
+} bf16n_weight;
+
+/* One matrix-vector product call: y[col] = W[rbase : rbase+nrows] x[col] for ncols columns.
+ * Dense: column c = token c, rbase = row0.  With ids: column c = (token c / n_used, slot c % n_used), expert
+ * e = ids[token, slot], rbase = row0 + e*rows_per_matrix; x of a column at x_tok*token + x_slot*(slot % x_per_slot),
+ * y at y_tok*token + y_slot*slot.  Strides are signed byte counts; ids are int32, or int64 < 2^31 (low word read).
+ * Replaces struct bf16n::mmv_args (launch.h:27-41). */
+typedef struct bf16n_mmv_args {
+    const void * x; int32_t x_bf16;
+    void * y;       int32_t y_bf16;
+    int32_t ncols;
+    int32_t n_used, x_per_slot;
+    int64_t x_tok, y_tok;
+    const void * ids; int64_t ids_s0, ids_s1;
+    int64_t x_slot, y_slot;
+    int64_t rows_per_matrix, row0, nrows;
+} bf16n_mmv_args;
+
+const char * bf16n_last_error(void);
+
+/* ---- host side ------------------------------------------------------------------------------------------------ */
+
+/* Opaque result of bf16n_encode. Replaces struct bf16n::encoded (core/include/bf16n/encode.h:12-17). */
+typedef struct bf16n_encoded bf16n_encoded;
+
+/* Encode rows x K BF16 bit patterns (host memory, row-major) on all host threads.
+ * Replaces bf16n::encode (encode.h:26, core/src/encode.cpp:443-526): same argument rules, same bytes. */
+int bf16n_encode(const uint16_t * w, int64_t rows, int64_t K, int format, int R, int chunk_major, int frag_order,
+                 bf16n_encoded ** out);
+const uint8_t * bf16n_encoded_plane(const bf16n_encoded * e, size_t * nbytes);
+const uint8_t * bf16n_encoded_aux(const bf16n_encoded * e, size_t * nbytes);
+int bf16n_encoded_format(const bf16n_encoded * e);
+int bf16n_encoded_R(const bf16n_encoded * e);
+void bf16n_encoded_free(bf16n_encoded * e);
+
+/* Fill every field of *w except the two device pointers from the first 256 bytes of a HOST copy of the aux buffer.
+ * Replaces the header parse each engine does once per tensor (engines/vllm/vllm_bf16n/ops.py:54-63;
+ * engines/llamacpp/patches/0002 bf16n.cu registry insert). */
+int bf16n_parse_header(const uint8_t * aux_host, size_t nbytes, bf16n_weight * w);
+
+/* Shape policy. engine: 0 llama, 1 vllm; mode: 0 hybrid, 1 huffman, 2 nibble. out = {format, R, chunk_major,
+ * frag_order}. Returns 1 when a format was chosen, 0 when the shape stays BF16 (never fails).
+ * Replaces bf16n::choose (core/include/bf16n/policy.h:37, core/src/policy.cpp:45-69). */
+int bf16n_choose(int64_t rows, int64_t K, int64_t n_matrices, int engine, int mode, int64_t dense_min, int expert,
+                 int dense_frag_order, int out[4]);
+
+/* ---- device side ---------------------------------------------------------------------------------------------- */
+
+/* Once per process and device, before the first launch and before any graph capture: device attributes and the
+ * kernels' shared-memory limits. Replaces bf16n::init / bf16n::sm_count (launch.h:45-46, core/src/launch.cu:270-311). */
+int bf16n_init(void);
+int bf16n_sm_count(int * out);
+
+/* GEMV (<= a few columns), dense or routed by expert ids. multi_col != 0: dense batches of 2..4 columns decode the
+ * matrix once per group of 4. Replaces bf16n::mmv (launch.h:50, launch.cu:313-325). */
+int bf16n_mmv(const bf16n_weight * w, const bf16n_mmv_args * a, void * stream, int multi_col);
+/* y = silu(gate x) * (up x) for a NIBBLE matrix whose rows_per_matrix rows are [gate (nrows); up (nrows)].
+ * Replaces bf16n::mmv_glu(w, a, stream) (launch.h:53, launch.cu:327-339). */
+int bf16n_mmv_glu_merged(const bf16n_weight * w, const bf16n_mmv_args * a, void * stream);
+/* Same with separate gate and up matrices (NIBBLE, row-major HUFPAIR, HUFFMAN).
+ * Replaces bf16n::mmv_glu(gate, up, a, stream) (launch.h:60, launch.cu:341-365). */
+int bf16n_mmv_glu(const bf16n_weight * gate, const bf16n_weight * up, const bf16n_mmv_args * a, void * stream);
+/* Exact BF16 bits of rows [row0, row0+nrows) into out (device, row-major nrows x K).
+ * Replaces bf16n::dequant (launch.h:62, launch.cu:367-402). */
+int bf16n_dequant(const bf16n_weight * w, int64_t row0, int64_t nrows, uint16_t * out, void * stream);
+/* Verify-at-load without materialising the tensor: decodes rows [row0, row0+nrows) and adds the number of BF16 words
+ * that differ from src (device, row-major, row 0 = row0) to *mismatches (device, caller zeroes it).
+ * Replaces the dequant + compare loop of engines/vllm/vllm_bf16n/ops.py:104-116 (roundtrip_equal). */
+int bf16n_verify(const bf16n_weight * w, int64_t row0, int64_t nrows, const uint16_t * src, unsigned long long * mismatches,
+                 void * stream);
+/* dst[i] = W[row0 + ids[i]] as FP32 or BF16 (row gather for embeddings). Replaces bf16n::get_rows (launch.h:67-68,
+ * launch.cu:404-443). */
+int bf16n_get_rows(const bf16n_weight * w, const void * ids, int64_t ids_s0, int64_t n, void * dst, int dst_bf16,
+                   int64_t dst_s1, void * stream, int64_t row0);
+
+/* Batched (prefill) routed product. Replaces bf16n::mm_ids_supported / mm_ids_route / mm_ids (launch.h:73-78,
+ * launch.cu:446-535; routing semantics core/src/mmid_helper.cu:4-8). */
+int bf16n_mm_ids_supported(const bf16n_weight * w, const bf16n_weight * up);
+int bf16n_mm_ids_route(const void * ids, int ids_i64, int64_t ids_row_stride, int32_t * ids_src1, int32_t * ids_dst,
+                       int32_t * bounds, int n_experts, int n_tok, int n_used, int nchannels_y, int sis1, void * stream);
+int bf16n_mm_ids(const bf16n_weight * w, const bf16n_weight * up, const void * x_bf16, int64_t x_row,
+                 const int32_t * ids_src1, const int32_t * ids_dst, const int32_t * bounds, void * dst, int dst_bf16,
+                 int64_t dst_col, int n_experts, int n_tok, int n_used, void * stream);
+
+/* y[t, i] = sum_k w[t, k] * ys[t, k, i] in slot order (FP32). Replaces bf16n::moe_combine (launch.h:81-82,
+ * launch.cu:539-572). */
+int bf16n_moe_combine(const float * ys, const void * w, int w_bf16, void * y, int y_bf16, int n_tok, int n_used, int64_t n,
+                      void * stream);
+/* y = silu(g) * u elementwise. Replaces bf16n::swiglu (launch.h:84, launch.cu:554-582). */
+int bf16n_swiglu(const float * g, const float * u, float * y, int64_t n, void * stream);
+
+/* Router on the GPU: softmax over n_experts logits per token, the k largest (ties: lowest index), weights renormalised
+ * to sum 1. The reference core takes ids and weights from its engines (tests/core/test_kernels.py:333-345 synthesise
+ * them); this keeps the 1-4 token decode step on the device. logits FP32 [n_tok, n_experts]; ids int32 [n_tok, k];
+ * weights FP32 [n_tok, k]. */
+int bf16n_moe_topk(const float * logits, int n_tok, int n_experts, int k, int32_t * ids, float * weights, void * stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BF16N_C_H */

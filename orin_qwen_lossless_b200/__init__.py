@@ -1,0 +1,6 @@
+"""B200 (sm_100a) implementation of the BF16N lossless weight path: host encoder and shape policy, decode-inside-GEMV
+kernels, routed-MoE decode and batched-MoE prefill behind a C ABI (include/bf16n_c.h), with `ops` mirroring the
+reference's Python operator interface on top of it."""
+from . import ops  # noqa: F401
+
+__all__ = ["ops"]

@@ -1,0 +1,275 @@
+// The C ABI (include/bf16n_c.h): argument validation with the reference's rules and messages
+// (core/src/launch.cu:261-268, 313-365, 367-376, 404-413, 458-490), error translation, one-time initialisation.
+#include "encode.h"
+#include "launch.h"
+#include "policy.h"
+
+#include <cstring>
+#include <mutex>
+
+namespace b16 {
+namespace {
+
+thread_local std::string g_error;
+DeviceInfo g_info;
+std::once_flag g_once;
+int g_init_status = BF16N_OK;
+std::string g_init_error;
+
+template <typename F>
+int guarded(F && f) {
+    try {
+        f();
+        return BF16N_OK;
+    } catch (const std::invalid_argument & e) {
+        g_error = e.what();
+        return BF16N_EINVAL;
+    } catch (const std::runtime_error & e) {
+        g_error = e.what();
+        return std::strstr(e.what(), "CUDA error") ? BF16N_ECUDA : BF16N_EINTERNAL;
+    } catch (const std::exception & e) {
+        g_error = e.what();
+        return BF16N_EINTERNAL;
+    }
+}
+
+void ensure_init() {
+    std::call_once(g_once, [] {
+        try {
+            int dev = 0;
+            cuda_ok(cudaGetDevice(&dev), "cudaGetDevice");
+            cuda_ok(cudaDeviceGetAttribute(&g_info.sms, cudaDevAttrMultiProcessorCount, dev), "SM count");
+            cuda_ok(cudaDeviceGetAttribute(&g_info.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev), "shared memory limit");
+            gemv_init();
+            moe_init();
+            prefill_init();
+        } catch (const std::exception & e) {
+            g_init_status = BF16N_ECUDA;
+            g_init_error = e.what();
+        }
+    });
+    if (g_init_status != BF16N_OK) { throw std::runtime_error(g_init_error); }
+}
+
+void check_weight(const bf16n_weight & w) {
+    require(w.K % CHUNK == 0 && w.K >= CHUNK && w.K <= K_MAX, "K must be a multiple of 512 in [512, 4096]");
+    require(w.format == FMT_NIBBLE || w.format == FMT_HUFFMAN || w.format == FMT_HUFPAIR, "unknown format");
+    require(w.format == FMT_NIBBLE || (w.R > 0 && w.rows % w.R == 0), "rows must be a multiple of R");
+    require(!w.cm || w.format == FMT_HUFPAIR, "chunk-major units exist only for HUFPAIR");
+    require(!w.fo || (w.format == FMT_HUFPAIR && !w.cm && w.R == 16),
+            "fragment order exists only for HUFPAIR with R = 16, without chunk-major units");
+    require(((uintptr_t) w.plane | (uintptr_t) w.aux) % 16 == 0, "plane and aux must be 16-byte aligned");
+}
+void no_frag_order(const bf16n_weight & w) {
+    require(!w.fo, "fragment-order matrices have no kernels in this build");
+}
+void whole_units(const bf16n_weight & w, const bf16n_mmv_args & a) {
+    require(w.format == FMT_NIBBLE || (a.nrows % w.R == 0 && a.row0 % w.R == 0 && a.rows_per_matrix % w.R == 0),
+            "rows of a product must be whole units");
+}
+void check_x(const bf16n_weight & w, const bf16n_mmv_args & a) {
+    // vector loads: 16 bytes for FP32 activations, 8 for BF16 (the kernels read 4 activations at a time)
+    const uintptr_t al = a.x_bf16 ? 8 : 16;
+    require((uintptr_t) a.x % al == 0 && a.x_tok % (int64_t) al == 0 && a.x_slot % (int64_t) al == 0,
+            "activation base and strides must be 16-byte aligned (8 for BF16)");
+    (void) w;
+}
+
+} // namespace
+
+const DeviceInfo & device_info() { return g_info; }
+
+} // namespace b16
+
+using namespace b16;
+
+struct bf16n_encoded { Encoded e; };
+
+extern "C" {
+
+const char * bf16n_last_error(void) { return g_error.c_str(); }
+
+int bf16n_encode(const uint16_t * w, int64_t rows, int64_t K, int format, int R, int chunk_major, int frag_order,
+                 bf16n_encoded ** out) {
+    return guarded([&] {
+        require(w != nullptr && out != nullptr, "encode: null argument");
+        auto * r = new bf16n_encoded;
+        try {
+            r->e = encode(w, rows, K, format, R, chunk_major != 0, frag_order != 0);
+        } catch (...) {
+            delete r;
+            throw;
+        }
+        *out = r;
+    });
+}
+const uint8_t * bf16n_encoded_plane(const bf16n_encoded * e, size_t * n) { if (n) { *n = e->e.plane.size(); } return e->e.plane.data(); }
+const uint8_t * bf16n_encoded_aux(const bf16n_encoded * e, size_t * n) { if (n) { *n = e->e.aux.size(); } return e->e.aux.data(); }
+int bf16n_encoded_format(const bf16n_encoded * e) { return e->e.format; }
+int bf16n_encoded_R(const bf16n_encoded * e) { return e->e.R; }
+void bf16n_encoded_free(bf16n_encoded * e) { delete e; }
+
+int bf16n_parse_header(const uint8_t * aux_host, size_t nbytes, bf16n_weight * w) {
+    return guarded([&] {
+        require(aux_host && w && nbytes >= (size_t) HEADER_BYTES, "aux must hold at least the 256-byte header");
+        AuxHeader h;
+        memcpy(&h, aux_host, sizeof h);
+        require(h.magic == MAGIC, "bad aux header (magic)");
+        require(h.format == (uint32_t) FMT_NIBBLE || h.format == (uint32_t) FMT_HUFFMAN || h.format == (uint32_t) FMT_HUFPAIR,
+                "bad aux header (format)");
+        require((h.flags & ~(FLAG_CHUNK_MAJOR | FLAG_FRAG_ORDER)) == 0, "unknown layout flags");
+        w->format = (int32_t) h.format; w->R = (int32_t) h.R; w->K = h.K; w->rows = (int64_t) h.rows;
+        w->cm = (h.flags & FLAG_CHUNK_MAJOR) != 0; w->fo = (h.flags & FLAG_FRAG_ORDER) != 0;
+        w->off_a = h.off_a; w->off_b = h.off_b; w->off_c = h.off_c; w->off_d = h.off_d;
+    });
+}
+
+int bf16n_choose(int64_t rows, int64_t K, int64_t n_matrices, int engine, int mode, int64_t dense_min, int expert,
+                 int dense_frag_order, int out[4]) {
+    PolicyOptions o;
+    o.engine = engine ? Engine::vllm : Engine::llama;
+    o.mode = mode == 1 ? Mode::huffman : mode == 2 ? Mode::nibble : Mode::hybrid;
+    o.dense_min = dense_min; o.expert = expert != 0; o.dense_frag_order = dense_frag_order != 0;
+    PolicyChoice c;
+    if (!choose(rows, K, n_matrices, o, &c)) { return 0; }
+    out[0] = c.format; out[1] = c.R; out[2] = c.chunk_major; out[3] = c.frag_order;
+    return 1;
+}
+
+int bf16n_init(void) { return guarded([] { ensure_init(); }); }
+int bf16n_sm_count(int * out) { return guarded([&] { ensure_init(); *out = g_info.sms; }); }
+
+int bf16n_mmv(const bf16n_weight * w, const bf16n_mmv_args * a, void * stream, int multi_col) {
+    return guarded([&] {
+        ensure_init();
+        check_weight(*w);
+        no_frag_order(*w);
+        require(a->ncols > 0 && a->ncols <= 65535, "ncols out of range");
+        whole_units(*w, *a);
+        check_x(*w, *a);
+        if (a->nrows == 0) { return; }
+        gemv(*w, *a, (cudaStream_t) stream, multi_col != 0);
+    });
+}
+
+int bf16n_mmv_glu_merged(const bf16n_weight * w, const bf16n_mmv_args * a, void * stream) {
+    return guarded([&] {
+        ensure_init();
+        check_weight(*w);
+        require(w->format == FMT_NIBBLE, "mmv_glu supports NIBBLE matrices only");
+        require(a->rows_per_matrix == 2 * a->nrows, "mmv_glu: rows per matrix must be [gate; up] of nrows each");
+        require(a->ncols > 0 && a->ncols <= 65535, "ncols out of range");
+        check_x(*w, *a);
+        if (a->nrows == 0) { return; }
+        gemv_glu_merged(*w, *a, (cudaStream_t) stream);
+    });
+}
+
+int bf16n_mmv_glu(const bf16n_weight * g, const bf16n_weight * u, const bf16n_mmv_args * a, void * stream) {
+    return guarded([&] {
+        ensure_init();
+        check_weight(*g);
+        check_weight(*u);
+        require(g->format == u->format && g->K == u->K, "mmv_glu: gate/up format and K must match");
+        require(g->rows == u->rows, "mmv_glu: gate/up row counts must match");
+        require(a->row0 >= 0 && a->nrows >= 0 && a->row0 <= g->rows && a->nrows <= g->rows - a->row0, "mmv_glu: product rows out of range");
+        require(!g->cm && !u->cm, "mmv_glu: chunk-major weights require separate mmv launches");
+        require(!g->fo && !u->fo, "mmv_glu: fragment-order weights require separate mmv launches");
+        require(g->format == FMT_NIBBLE || g->R == u->R, "mmv_glu: gate/up R must match");
+        require(a->ncols > 0 && a->ncols <= 65535, "ncols out of range");
+        whole_units(*g, *a);
+        check_x(*g, *a);
+        if (a->nrows == 0) { return; }
+        gemv_glu(*g, *u, *a, (cudaStream_t) stream);
+    });
+}
+
+int bf16n_dequant(const bf16n_weight * w, int64_t row0, int64_t nrows, uint16_t * out, void * stream) {
+    return guarded([&] {
+        ensure_init();
+        check_weight(*w);
+        no_frag_order(*w);
+        if (nrows == 0) { return; }
+        require(row0 >= 0 && nrows > 0 && row0 + nrows <= w->rows, "dequant rows out of range");
+        require(w->format == FMT_NIBBLE || (nrows % w->R == 0 && row0 % w->R == 0), "dequant rows must be whole units");
+        expand_store(*w, row0, nrows, out, (cudaStream_t) stream);
+    });
+}
+
+int bf16n_verify(const bf16n_weight * w, int64_t row0, int64_t nrows, const uint16_t * src, unsigned long long * mismatches,
+                 void * stream) {
+    return guarded([&] {
+        ensure_init();
+        check_weight(*w);
+        no_frag_order(*w);
+        if (nrows == 0) { return; }
+        require(row0 >= 0 && nrows > 0 && row0 + nrows <= w->rows, "verify rows out of range");
+        require(w->format == FMT_NIBBLE || (nrows % w->R == 0 && row0 % w->R == 0), "verify rows must be whole units");
+        require((uintptr_t) src % 8 == 0, "verify source must be 8-byte aligned");
+        expand_compare(*w, row0, nrows, src, mismatches, (cudaStream_t) stream);
+    });
+}
+
+int bf16n_get_rows(const bf16n_weight * w, const void * ids, int64_t ids_s0, int64_t n, void * dst, int dst_bf16, int64_t dst_s1,
+                   void * stream, int64_t row0) {
+    return guarded([&] {
+        ensure_init();
+        check_weight(*w);
+        no_frag_order(*w);
+        require(n >= 0, "get_rows: n must be nonnegative");
+        require(row0 >= 0 && (n == 0 ? row0 <= w->rows : row0 < w->rows), "get_rows: row0 out of range");
+        require(!w->cm, "get_rows of a chunk-major (expert) matrix");
+        require(w->format != FMT_HUFFMAN, "get_rows is not implemented for the single-symbol Huffman format");
+        if (n == 0) { return; }
+        gather_rows(*w, ids, ids_s0, n, dst, dst_bf16 != 0, dst_s1, row0, (cudaStream_t) stream);
+    });
+}
+
+int bf16n_mm_ids_supported(const bf16n_weight * w, const bf16n_weight * up) { return prefill_supported(*w, up) ? 1 : 0; }
+
+int bf16n_mm_ids_route(const void * ids, int ids_i64, int64_t ids_row_stride, int32_t * ids_src1, int32_t * ids_dst,
+                       int32_t * bounds, int n_experts, int n_tok, int n_used, int nchannels_y, int sis1, void * stream) {
+    return guarded([&] {
+        ensure_init();
+        moe_route(ids, ids_i64 != 0, ids_row_stride, ids_src1, ids_dst, bounds, n_experts, n_tok, n_used, nchannels_y, sis1,
+                  (cudaStream_t) stream);
+    });
+}
+
+int bf16n_mm_ids(const bf16n_weight * w, const bf16n_weight * up, const void * x_bf16, int64_t x_row, const int32_t * ids_src1,
+                 const int32_t * ids_dst, const int32_t * bounds, void * dst, int dst_bf16, int64_t dst_col, int n_experts,
+                 int n_tok, int n_used, void * stream) {
+    return guarded([&] {
+        ensure_init();
+        check_weight(*w);
+        if (up) { check_weight(*up); }
+        require(prefill_supported(*w, up), "no batched kernel for this matrix");
+        require(n_experts > 0 && w->rows % n_experts == 0, "rows must split evenly into experts");
+        prefill_mm_ids(*w, up, x_bf16, x_row, ids_src1, ids_dst, bounds, dst, dst_bf16 != 0, dst_col, n_experts, n_tok, n_used,
+                       (cudaStream_t) stream);
+    });
+}
+
+int bf16n_moe_combine(const float * ys, const void * w, int w_bf16, void * y, int y_bf16, int n_tok, int n_used, int64_t n,
+                      void * stream) {
+    return guarded([&] {
+        ensure_init();
+        moe_combine(ys, w, w_bf16 != 0, y, y_bf16 != 0, n_tok, n_used, n, (cudaStream_t) stream);
+    });
+}
+
+int bf16n_swiglu(const float * g, const float * u, float * y, int64_t n, void * stream) {
+    return guarded([&] {
+        ensure_init();
+        moe_swiglu(g, u, y, n, (cudaStream_t) stream);
+    });
+}
+
+int bf16n_moe_topk(const float * logits, int n_tok, int n_experts, int k, int32_t * ids, float * weights, void * stream) {
+    return guarded([&] {
+        ensure_init();
+        moe_topk(logits, n_tok, n_experts, k, ids, weights, (cudaStream_t) stream);
+    });
+}
+
+} // extern "C"

@@ -1,0 +1,251 @@
+// Device-side building blocks shared by the BF16N kernels: bit-stream readers, weight assembly, reductions, output
+// stores and the column descriptor. Layout facts (format.h): a warp owns one row-chunk of 512 weights at a time, lane l
+// holds the 16 plane bytes of slots 0..15 (columns 128*(s>>2) + 4*l + (s&3)), i.e. one 32-bit plane word per column
+// quad j = s>>2, whose bytes are the columns 128*j + 4*l + {0,1,2,3}.
+#pragma once
+
+#include "format.h"
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace b16 {
+namespace dev {
+
+constexpr uint32_t FULL = 0xffffffffu;
+
+// ---------------------------------------------------------------- small PTX helpers
+
+__device__ __forceinline__ uint32_t byte_perm(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
+// (a & m) | (b & ~m) with m = 0x807F807F: sign and mantissa bits from a, exponent bits from b, for two BF16 halves
+__device__ __forceinline__ uint32_t merge_sm_exp(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("lop3.b32 %0, %1, %2, 0x807F807F, 0xE4;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+// plane bytes (lo, hi) = bytes {0,1} or {2,3} of a plane word, each spread to a BF16 half with its sign bit copied to
+// bit 15 (prmt sign-replication fills the upper byte); bits 7..14 are garbage and are masked by merge_sm_exp
+__device__ __forceinline__ uint32_t spread_lo(uint32_t plane_word) { return byte_perm(plane_word, 0, 0x9180u); }
+__device__ __forceinline__ uint32_t spread_hi(uint32_t plane_word) { return byte_perm(plane_word, 0, 0xB3A2u); }
+
+// streaming 16-byte load that does not allocate in L1 (each plane byte is read once)
+__device__ __forceinline__ uint4 ld_stream16(const void * p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ float bf16lo_f32(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16hi_f32(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) { v += __shfl_xor_sync(FULL, v, o); }
+    return v;
+}
+
+// silu with the fast exponential and division the reference's fast-math build uses (core/include/bf16n/compat.cuh:29-31)
+__device__ __forceinline__ float silu_f(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
+
+// ---------------------------------------------------------------- activations
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __uint_as_float((uint32_t) __bfloat16_as_ushort(v) << 16); }
+
+// x[i..i+3] as FP32 from global memory (i a multiple of 4; the caller guarantees 16-/8-byte alignment)
+__device__ __forceinline__ float4 ldg_x4(const float * x, int i) { return __ldg((const float4 *) (x + i)); }
+__device__ __forceinline__ float4 ldg_x4(const __nv_bfloat16 * x, int i) {
+    const uint2 v = __ldg((const uint2 *) (x + i));
+    return make_float4(bf16lo_f32(v.x), bf16hi_f32(v.x), bf16lo_f32(v.y), bf16hi_f32(v.y));
+}
+__device__ __forceinline__ float ldg_x1(const float * x, int i) { return __ldg(x + i); }
+__device__ __forceinline__ float ldg_x1(const __nv_bfloat16 * x, int i) {
+    return __uint_as_float((uint32_t) __ldg((const unsigned short *) x + i) << 16);
+}
+
+// ---------------------------------------------------------------- output
+
+struct OutVec { // one output column, FP32 or BF16 (round to nearest even)
+    char * p;
+    bool bf16;
+    __device__ __forceinline__ void put(int64_t i, float v) const {
+        if (bf16) { ((__nv_bfloat16 *) p)[i] = __float2bfloat16_rn(v); } else { ((float *) p)[i] = v; }
+    }
+};
+
+// ---------------------------------------------------------------- columns (tokens, or (token, expert slot) pairs)
+
+struct Cols {
+    const char * x; char * y;
+    int64_t x_tok, x_slot, y_tok, y_slot; // byte strides
+    const char * ids; int64_t ids_s0, ids_s1;
+    int n_used, x_per_slot;
+    int64_t rows_per_matrix, row0, nrows;
+    bool y_bf16;
+};
+
+// activation pointer, output column and first weight row of column `col`
+template <typename TX>
+__device__ __forceinline__ void column(const Cols & c, int col, const TX *& x, OutVec & out, int64_t & rbase) {
+    out.bf16 = c.y_bf16;
+    if (c.ids) {
+        const int t = col / c.n_used, s = col - t * c.n_used;
+        const int e = *(const int32_t *) (c.ids + t * c.ids_s1 + s * c.ids_s0);
+        x = (const TX *) (c.x + t * c.x_tok + (s % c.x_per_slot) * c.x_slot);
+        out.p = c.y + t * c.y_tok + s * c.y_slot;
+        rbase = c.row0 + (int64_t) e * c.rows_per_matrix;
+    } else {
+        x = (const TX *) (c.x + col * c.x_tok);
+        out.p = c.y + col * c.y_tok;
+        rbase = c.row0;
+    }
+}
+
+// ---------------------------------------------------------------- HUFPAIR lane stream
+
+struct PairView { // device pointers of one HUFPAIR matrix
+    const uint8_t * plane;
+    const uint32_t * lut;     // 4096 entries: e_odd << 23 | e_even << 7 | len
+    const uint32_t * ubase;   // per unit: first stream word
+    const uint16_t * lrel;    // per (unit, lane): word offset inside the unit
+    const uint32_t * stream;
+};
+
+// MSB-first reader of one lane's stream. `buf` holds `have` valid bits at the top; top_up() (call it before every
+// second lookup) keeps at least 32 of them, enough for two codes of up to 12 bits.
+struct PairReader {
+    const uint32_t * next;
+    uint64_t buf;
+    uint32_t ahead; // the word after the buffered ones, already loaded
+    int have;
+
+    __device__ __forceinline__ void open(const PairView & w, int64_t unit, int lane) {
+        next = w.stream + (__ldg(w.ubase + unit) + __ldg(w.lrel + unit * 32 + lane));
+        buf = (uint64_t) __ldg(next) << 32 | __ldg(next + 1);
+        ahead = __ldg(next + 2);
+        next += 3;
+        have = 64;
+    }
+    __device__ __forceinline__ void top_up() {
+        if (have <= 32) {
+            buf |= (uint64_t) ahead << (32 - have);
+            have += 32;
+            ahead = __ldg(next++);
+        }
+    }
+    // next table entry (the two exponents in place + code length); lut in shared memory
+    __device__ __forceinline__ uint32_t take(const uint32_t * lut) {
+        const uint32_t e = lut[(uint32_t) (buf >> (64 - HP_LMAX))];
+        const int n = e & 31;
+        buf <<= n;
+        have -= n;
+        return e;
+    }
+    // the 8 entries of one row-chunk (this lane's 16 weights)
+    __device__ __forceinline__ void take8(const uint32_t * lut, uint32_t (&e)[8]) {
+#pragma unroll
+        for (int q = 0; q < 8; q += 2) {
+            top_up();
+            e[q] = take(lut);
+            e[q + 1] = take(lut);
+        }
+    }
+};
+
+// the four BF16x2 words (column pairs {0,1} and {2,3} of quads j = 0..3 ... in slot order) of a row-chunk
+__device__ __forceinline__ void assemble8(const uint4 & sm, const uint32_t (&e)[8], uint32_t (&w)[8]) {
+    const uint32_t q[4] = {sm.x, sm.y, sm.z, sm.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        w[2 * j] = merge_sm_exp(spread_lo(q[j]), e[2 * j]);
+        w[2 * j + 1] = merge_sm_exp(spread_hi(q[j]), e[2 * j + 1]);
+    }
+}
+
+// ---------------------------------------------------------------- HUFFMAN (single exponent) lane stream
+
+struct HufView {
+    const uint8_t * plane;
+    const uint32_t * lut;      // 1024 entries: len | exponent << 7
+    const uint32_t * lane_off; // per (unit, lane): absolute word offset
+    const uint32_t * stream;
+};
+
+struct HufReader { // same scheme, codes <= 10 bits, top_up() before every third lookup
+    const uint32_t * next;
+    uint64_t buf;
+    uint32_t ahead;
+    int have;
+    __device__ __forceinline__ void open(const HufView & w, int64_t unit, int lane) {
+        next = w.stream + __ldg(w.lane_off + unit * 32 + lane);
+        buf = (uint64_t) __ldg(next) << 32 | __ldg(next + 1);
+        ahead = __ldg(next + 2);
+        next += 3;
+        have = 64;
+    }
+    __device__ __forceinline__ void top_up() {
+        if (have <= 32) {
+            buf |= (uint64_t) ahead << (32 - have);
+            have += 32;
+            ahead = __ldg(next++);
+        }
+    }
+    __device__ __forceinline__ uint32_t take(const uint32_t * lut) {
+        const uint32_t e = lut[(uint32_t) (buf >> (64 - HUF_LMAX))];
+        const int n = e & 31;
+        buf <<= n;
+        have -= n;
+        return e;
+    }
+    // 16 exponents of a row-chunk, returned as 8 pair entries in the HUFPAIR table layout (e_odd<<23 | e_even<<7)
+    __device__ __forceinline__ void take8(const uint32_t * lut, uint32_t (&e)[8]) {
+#pragma unroll
+        for (int s = 0; s < 16; s++) {
+            if (s % 3 == 0) { top_up(); }
+            const uint32_t ent = take(lut) & 0x7F80u;
+            if (s & 1) { e[s >> 1] |= ent << 16; } else { e[s >> 1] = ent; }
+        }
+    }
+};
+
+// ---------------------------------------------------------------- NIBBLE rows
+
+struct NibView {
+    const uint8_t * plane;
+    const uint8_t * codes;     // rows * K/2
+    const uint4 * row_lut;     // 16 exponent bytes per row
+    const uint32_t * esc_off;  // rows + 1
+    const uint32_t * esc;      // col | sign_mantissa << 12 | exponent << 20
+};
+
+// The 8 BF16x2 words of a NIBBLE row-chunk. Exponent bytes come from two prmt lookups per 4 weights: a selector
+// nibble 0..7 picks a byte of its 8-byte operand pair, 8..15 returns that byte's replicated sign bit, which is 0
+// because table entries are < 128. So codes 0..7 read {L.x, L.y} and contribute 0 from {L.z, L.w} (looked up with
+// the codes' bit 3 flipped), codes 8..15 the reverse, and the OR of both lookups is the exponent byte.
+__device__ __forceinline__ void nib_assemble8(const uint4 & sm, const uint2 & codes, const uint4 & L, uint32_t (&w)[8]) {
+    const uint32_t q[4] = {sm.x, sm.y, sm.z, sm.w};
+    const uint32_t cw[2] = {codes.x, codes.y};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const uint32_t sel = (j & 1) ? cw[j >> 1] >> 16 : cw[j >> 1]; // prmt reads the low four nibbles only
+        const uint32_t e4 = byte_perm(L.x, L.y, sel) | byte_perm(L.z, L.w, sel ^ 0x8888u);
+        w[2 * j] = (spread_lo(q[j]) & 0x807F807Fu) | (byte_perm(e4, 0, 0x4140u) << 7);
+        w[2 * j + 1] = (spread_hi(q[j]) & 0x807F807Fu) | (byte_perm(e4, 0, 0x4342u) << 7);
+    }
+}
+
+__device__ __forceinline__ uint32_t esc_bits(uint32_t rec) { // BF16 bit pattern of an escape record
+    const uint32_t sm = (rec >> 12) & 0xFFu, ex = rec >> 20;
+    return ((sm & 0x80u) << 8) | (ex << 7) | (sm & 0x7Fu);
+}
+
+} // namespace dev
+} // namespace b16

@@ -1,0 +1,52 @@
+// Internal interface between the C ABI (capi.cu) and the kernel translation units.
+#pragma once
+
+#include "../../include/bf16n_c.h"
+#include "format.h"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+
+namespace b16 {
+
+struct DeviceInfo { int sms = 0; int smem_optin = 0; };
+const DeviceInfo & device_info(); // filled by bf16n_init
+
+[[noreturn]] inline void fail_invalid(const std::string & m) { throw std::invalid_argument("bf16n: " + m); }
+inline void require(bool ok, const char * m) { if (!ok) { fail_invalid(m); } }
+inline void cuda_ok(cudaError_t e, const char * what) {
+    if (e != cudaSuccess) { throw std::runtime_error(std::string("bf16n: CUDA error ") + cudaGetErrorString(e) + " at " + what); }
+}
+inline void check_launch() { cuda_ok(cudaGetLastError(), "kernel launch"); }
+
+// gemv.cu
+void gemv_init();
+void gemv(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st, bool multi_col);
+void gemv_glu_merged(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st);
+void gemv_glu(const bf16n_weight & g, const bf16n_weight & u, const bf16n_mmv_args & a, cudaStream_t st);
+void expand_store(const bf16n_weight & w, int64_t row0, int64_t nrows, uint16_t * out, cudaStream_t st);
+void expand_compare(const bf16n_weight & w, int64_t row0, int64_t nrows, const uint16_t * src, unsigned long long * total,
+                    cudaStream_t st);
+void gather_rows(const bf16n_weight & w, const void * ids, int64_t ids_s0, int64_t n, void * dst, bool dst_bf16, int64_t dst_s1,
+                 int64_t row0, cudaStream_t st);
+
+// moe.cu
+void moe_init();
+void moe_topk(const float * logits, int n_tok, int n_experts, int k, int32_t * ids, float * weights, cudaStream_t st);
+void moe_combine(const float * ys, const void * w, bool w_bf16, void * y, bool y_bf16, int n_tok, int n_used, int64_t n, cudaStream_t st);
+void moe_swiglu(const float * g, const float * u, float * y, int64_t n, cudaStream_t st);
+void moe_route(const void * ids, bool ids_i64, int64_t ids_row_stride, int32_t * ids_src1, int32_t * ids_dst, int32_t * bounds,
+               int n_experts, int n_tok, int n_used, int nchannels_y, int sis1, cudaStream_t st);
+
+// prefill.cu
+void prefill_init();
+bool prefill_supported(const bf16n_weight & w, const bf16n_weight * up);
+void prefill_mm_ids(const bf16n_weight & w, const bf16n_weight * up, const void * x_bf16, int64_t x_row, const int32_t * ids_src1,
+                    const int32_t * ids_dst, const int32_t * bounds, void * dst, bool dst_bf16, int64_t dst_col, int n_experts,
+                    int n_tok, int n_used, cudaStream_t st);
+
+} // namespace b16

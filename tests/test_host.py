@@ -1,0 +1,118 @@
+"""Host side of the library through the C ABI (no GPU): encoder bytes against the oracle and the golden vectors,
+argument errors, header parse, shape policy, and the exported symbol list."""
+import ctypes as C
+import hashlib
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import ROOT, bits_of, to_bf16_tensor
+from oracle import cpu_oracle as o
+from orin_qwen_lossless_b200 import _lib, ops
+
+
+def enc(w, fmt, R, cm=False, fo=False):
+    plane, aux, meta = ops.encode(to_bf16_tensor(w), fmt, R, cm, fo)
+    return plane.numpy(), aux.numpy(), meta
+
+
+def test_library_exports_every_declared_symbol():
+    hdr = open(os.path.join(ROOT, "include", "bf16n_c.h")).read()
+    declared = set(re.findall(r"\b(bf16n_[A-Za-z0-9_]+)\s*\(", hdr))
+    lib = _lib.lib()
+    assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+    for name in declared:
+        assert hasattr(lib, name), name
+
+
+def test_encoder_matches_golden_vectors(golden_vectors):
+    meta, blobs = golden_vectors
+    for rec in meta:
+        w = blobs[rec["name"] + "__w"]
+        plane, aux, m = enc(w, rec["format"], rec["R"], rec["cm"], rec["fo"])
+        assert m.format == rec["format_out"]
+        assert hashlib.sha256(plane.tobytes()).hexdigest() == rec["plane_sha256"], rec["name"]
+        assert hashlib.sha256(aux.tobytes()).hexdigest() == rec["aux_sha256"], rec["name"]
+
+
+@pytest.mark.parametrize("K", [512, 1024, 2048, 4096])
+def test_encoder_byte_identical_to_oracle(K):
+    rows = 48
+    w = o.with_specials(o.weights_like(rows, K, 11 * K, outliers=True), K).reshape(rows, K)
+    cases = [(1, 0, 0, 0)] + [(f, R, 0, 0) for f in (2, 3) for R in (1, 2, 4, 8, 16)]
+    cases += [(3, R, 1, 0) for R in (4, 8, 16) if K > 512] + [(3, 16, 0, 1)]
+    for fmt, R, cm, fo in cases:
+        p0, a0, f0 = o.encode(w, fmt, R, cm, fo)
+        p1, a1, m = enc(w, fmt, R, cm, fo)
+        assert m.format == f0 and np.array_equal(p0, p1) and np.array_equal(a0, a1), (fmt, R, cm, fo)
+        assert np.array_equal(o.decode(p1, a1), w)
+
+
+def test_encoder_threads_large_tensor_round_trip():
+    w = o.weights_like(2048, 2048, 77)
+    p1, a1, m = enc(w, 3, 16)
+    p0, a0, _ = o.encode(w, 3, 16)
+    assert np.array_equal(a0, a1) and np.array_equal(p0, p1)
+    assert (m.format, m.R, m.K, m.rows) == (3, 16, 2048, 2048)
+
+
+@pytest.mark.parametrize("n", [4095, 4096, 4097])
+def test_pair_fallback(n):
+    w = o.with_pairs(16, 1024, n)
+    for cm in (False, True):
+        p, a, m = enc(w, 3, 4, cm)
+        assert m.format == (3 if n <= 4096 else 2) and m.chunk_major == (cm and n <= 4096)
+        assert np.array_equal(o.decode(p, a), w)
+
+
+def test_argument_errors_and_messages():
+    z = torch.zeros(64, 1024, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="multiple of R"):
+        ops.encode(z[:15], 3, 4, False)
+    with pytest.raises(ValueError, match="chunk-major"):
+        ops.encode(z[:16, :512].contiguous(), 3, 4, True)
+    with pytest.raises(ValueError, match="chunk-major"):
+        ops.encode(z[:16], 2, 4, True)
+    with pytest.raises(ValueError, match="fragment order|fragment-order"):
+        ops.encode(z[:16], 3, 8, False, True)
+    with pytest.raises(ValueError, match="NIBBLE"):
+        ops.encode(z[:16], 1, 4, False)
+    with pytest.raises(ValueError, match="unknown format"):
+        ops.encode(z[:16], 4, 4, False)
+    with pytest.raises(ValueError, match="K must be"):
+        ops.encode(torch.zeros(16, 500, dtype=torch.bfloat16), 3, 4, False)
+    with pytest.raises(RuntimeError):
+        ops.encode(z.float(), 3, 4, False)
+
+
+def test_parse_header_rejects_garbage():
+    with pytest.raises(ValueError):
+        ops.parse_header(torch.zeros(256, dtype=torch.uint8))
+    with pytest.raises(ValueError):
+        ops.parse_header(torch.zeros(16, dtype=torch.uint8))
+    _, aux, meta = ops.encode(to_bf16_tensor(o.weights_like(16, 1024, 1)), 3, 8, True)
+    h = o.parse_header(aux.numpy())
+    assert (meta.format, meta.K, meta.rows, meta.R, meta.chunk_major, meta.frag_order) == (3, 1024, 16, 8, True, False)
+    assert (meta.off_a, meta.off_b, meta.off_c, meta.off_d) == (h.off_a, h.off_b, h.off_c, h.off_d)
+    aux[16] = 9  # unknown flag bits live at byte 72
+    aux[72] = 4
+    with pytest.raises(ValueError):
+        ops.parse_header(aux)
+
+
+def test_policy_matches_reference_table(policy_table):
+    for rows, K, n, engine, mode, expert, dfo, want in policy_table:
+        got = ops.choose(rows, K, n, engine=engine, mode=mode, expert=bool(expert), dense_frag_order=bool(dfo))
+        assert (list(map(int, got)) if got else None) == want, (rows, K, n, engine, mode, expert, dfo)
+
+
+def test_policy_of_the_benchmark_shapes():
+    assert ops.choose(4096, 2048, engine="llama") == (3, 8, False, False)          # config 0
+    assert ops.choose(248320, 2048, engine="llama") == (3, 16, False, False)       # config 1: vocabulary projection
+    for rows, K in ((2048, 512), (512, 2048), (256, 2048)):                        # config 2: small matrices
+        assert ops.choose(rows, K, engine="llama") == (1, 0, False, False)
+    assert ops.choose(512, 2048, 256, engine="llama", expert=True) == (3, 8, True, False)    # expert gate / up
+    assert ops.choose(2048, 512, 256, engine="llama", expert=True) == (3, 16, False, False)  # expert down
