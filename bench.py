@@ -1,0 +1,315 @@
+"""Benchmark of the BF16N hot path on B200: the vocabulary projection (lm_head) decode+GEMV.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (the configuration the headline metric is quoted on): a 248320 x 2048 BF16 matrix, weights N(0, 0.02) rounded
+to BF16 (seeded, synthetic), pair-Huffman coded with R = 16 as the shape policy chooses, multiplied by one BF16 N(0,1)
+activation vector with FP32 accumulation and FP32 logits. With N > 1 ranks the rows are split into N shards (one
+process per GPU), each rank multiplies its shard and an NCCL all-gather assembles the logits.
+
+One JSON line on stdout (rank 0):
+  value    GB/s of compressed bytes (plane + aux + x + y) per second with everything resident in HBM
+  e2e      the same through ops.linear_host: the activation comes from pinned host memory and the logits go back to it
+           inside the timed region, every step
+  roofline achieved / measured copy bandwidth for the GEMV kernel (one launch per step)
+  cpu_baseline  the CPU oracle's decode+GEMV on this box's host threads (bounded sample)
+`--impl reference` times the CPU arm only (the reference ships no CPU GEMV, so this is the oracle's port of its decoder
+and summation; the encoder timed beside it is the reference's own when oracle/_ref is present).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ROWS, K, R = 248320, 2048, 16
+BLOCK_ROWS = 4096  # weights are generated in seeded blocks of rows so that every shard is reproducible on its own
+
+
+def gen_rows(r0: int, r1: int):
+    """BF16 weights of rows [r0, r1): N(0, 0.02) from torch's CPU generator, one seed per block of 4096 rows."""
+    import torch
+    out = torch.empty((r1 - r0, K), dtype=torch.bfloat16)
+    b0 = r0 // BLOCK_ROWS
+    for b in range(b0, (r1 + BLOCK_ROWS - 1) // BLOCK_ROWS):
+        g = torch.Generator().manual_seed(0xB16 + b)
+        blk = (torch.randn((BLOCK_ROWS, K), generator=g) * 0.02).to(torch.bfloat16)
+        lo, hi = max(r0, b * BLOCK_ROWS), min(r1, (b + 1) * BLOCK_ROWS)
+        out[lo - r0:hi - r0] = blk[lo - b * BLOCK_ROWS:hi - b * BLOCK_ROWS]
+    return out
+
+
+def gen_x():
+    import torch
+    g = torch.Generator().manual_seed(0xAC7)
+    return torch.randn((1, K), generator=g).to(torch.bfloat16)
+
+
+def shard_range(rank: int, world: int, rows: int):
+    units = rows // R
+    u0, u1 = units * rank // world, units * (rank + 1) // world
+    return u0 * R, u1 * R
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples while the timed region runs."""
+    Q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.samples, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz = [float(s[0]) for s in self.samples if len(s) >= 6 and s[0].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for s in self.samples if len(s) >= 6 for n, v in zip(names, s[2:6]) if v.startswith("Active")})
+        mx = [float(s[1]) for s in self.samples if len(s) >= 6 and s[1].replace(".", "").isdigit()]
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(mhz)}
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+def cpu_arm(rows_sample: int, reps: int):
+    """The CPU arm: encode (reference encoder when oracle/_ref is present, else the oracle's restatement) and the
+    oracle's decode+GEMV on all host threads, on the first `rows_sample` rows of the workload."""
+    from oracle import cpu_oracle as o
+    import torch
+    threads = os.cpu_count() or 1
+    w = gen_rows(0, rows_sample)
+    wb = w.view(torch.int16).numpy().view(np.uint16)
+    t0 = time.perf_counter()
+    plane, aux, _ = (o.ref_encode if o.have_ref() else o.encode)(wb, 3, R)
+    t_enc = time.perf_counter() - t0
+    x = o.bf16_bits_to_f32(gen_x().view(torch.int16).numpy().view(np.uint16)[0])
+    units = rows_sample // R
+    nbytes = plane.size + aux.size + K * 2 + rows_sample * 4
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        o.decode_gemv_mt(plane, aux, x, 0, units, threads)
+        times.append(time.perf_counter() - t0)
+    dt = statistics.median(times)
+    return {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"first {rows_sample} of {ROWS} rows ({nbytes / 1e6:.1f} MB compressed), median of {reps} passes of "
+                      f"{dt:.3f} s; encoder ({'reference' if o.have_ref() else 'oracle'}) {rows_sample * K * 2 / t_enc / 1e9:.2f} GB/s of BF16 input",
+            "ms_per_step": dt * 1e3, "encode_s": t_enc}, nbytes
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rows_sample = 16384
+    base, nbytes = cpu_arm(rows_sample, max(1, args.steps))
+    line = {"impl": "reference", "metric": "lm_head_248320x2048_bf16n_decode_gemv_compressed_GBps", "value": base["value"],
+            "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "lm_head 248320x2048 HUFPAIR R=16, batch-1 decode GEMV (CPU arm: bounded row sample)",
+                       "rows_sample": rows_sample},
+            "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from orin_qwen_lossless_b200 import ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (the library has no CPU path; use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    ops.init()
+    rows = args.rows
+    r0, r1 = shard_range(rank, world, rows)
+
+    t0 = time.perf_counter()
+    w = gen_rows(r0, r1)
+    t_gen = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    plane, aux, meta = ops.encode(w, ops.FMT_HUFPAIR, R, False)
+    t_enc = time.perf_counter() - t0
+    enc = ops.upload(plane, aux, meta, dev)
+    ok = ops.roundtrip_equal(enc, w)  # verify at load: bit-exact decode of the whole shard on the GPU
+    if not ok:
+        raise SystemExit("bench.py: GPU decode of the encoded shard is not bit-exact")
+    del w
+    shard_bytes = plane.numel() + aux.numel()
+    counts = torch.tensor([shard_bytes], dtype=torch.int64, device=dev)
+    if world > 1:
+        dist.all_reduce(counts)
+    total_weight_bytes = int(counts.item())
+    algo_bytes = total_weight_bytes + K * 2 + rows * 4          # all ranks: compressed weights + x (BF16) + logits (FP32)
+    shard_algo_bytes = shard_bytes + K * 2 + (r1 - r0) * 4      # one launch on this rank
+
+    x_host = gen_x().pin_memory()
+    x = x_host.to(dev)
+    logits = torch.empty((1, rows), dtype=torch.float32, device=dev)
+    # shards are padded to the widest one so that a single all-gather assembles the logits
+    per = [shard_range(i, world, rows) for i in range(world)]
+    width = max(b - a for a, b in per)
+    gathered = torch.empty((world, width), dtype=torch.float32, device=dev)
+    mine = gathered[rank, : r1 - r0].view(1, r1 - r0) if world > 1 else logits
+
+    def step():
+        ops.mmv(x, enc, out=mine)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered.view(-1), gathered[rank])
+
+    y_host = torch.empty((1, rows if world == 1 else world * width), dtype=torch.float32).pin_memory()
+    y_dev_full = logits if world == 1 else gathered.view(1, -1)
+
+    def step_e2e():
+        x.copy_(x_host, non_blocking=True)
+        step()
+        y_host.copy_(y_dev_full, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # a decode step consumes its logits on the host
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms_total = timed(step, args.steps)
+    # the GEMV launch alone (no collective), per launch, on the launching stream: the roofline figure
+    kernel_ms = timed(lambda: ops.mmv(x, enc, out=mine), args.steps) / args.steps
+    for _ in range(3):
+        step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+    clocks = sampler.stop() if sampler else None
+
+    # comparator on the same GPU: a stock BF16 GEMV (cuBLAS through torch) over the uncompressed shard
+    cublas_us = None
+    if args.cublas:
+        wd = gen_rows(r0, r1).to(dev)
+        yb = torch.empty((1, r1 - r0), dtype=torch.bfloat16, device=dev)
+        for _ in range(5):
+            torch.mm(x, wd.t(), out=yb)
+        cublas_us = timed(lambda: torch.mm(x, wd.t(), out=yb), args.steps) / args.steps * 1e3
+        del wd
+
+    # parity of what was timed, on a sample of rows, against the FP64 oracle (rank 0, its own shard)
+    parity = None
+    if rank == 0:
+        from oracle import cpu_oracle as o
+        n = min(2048, r1 - r0)
+        wb = gen_rows(r0, r0 + n).view(torch.int16).numpy().view(np.uint16)
+        xf = o.bf16_bits_to_f32(x_host.view(torch.int16).numpy().view(np.uint16)[0])
+        y64, s = o.gemv_f64(wb, xf)
+        got = mine[0, :n].float().cpu().numpy()
+        parity = {"rows_checked": n, "max_err_over_sum_abs": float((np.abs(got - y64) / s).max()), "roundtrip_bit_exact": bool(ok)}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    ms_step = ms_total / args.steps
+    peak, peak_src = measured_peak()
+    achieved = shard_algo_bytes / (kernel_ms * 1e-3) / 1e9
+    line = {
+        "metric": "lm_head_248320x2048_bf16n_decode_gemv_compressed_GBps",
+        "value": algo_bytes / (ms_step * 1e-3) / 1e9, "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"lm_head {rows}x{K} HUFPAIR R={R}, batch-1 decode GEMV, BF16 activation, FP32 logits"
+                               + (f", rows sharded over {world} GPUs + NCCL all-gather" if world > 1 else ""),
+                   "l2": "inputs larger than L2 (compressed matrix %.0f MB per GPU)" % (shard_bytes / 1e6),
+                   "compressed_bytes": total_weight_bytes, "bf16_bytes": rows * K * 2,
+                   "ratio": total_weight_bytes / (rows * K * 2)},
+        "us_per_step": ms_step * 1e3,
+        "bf16_equivalent_GBps": (rows * K * 2 + K * 2 + rows * 4) / (ms_step * 1e-3) / 1e9,
+        "frac_of_nominal_8TBps": algo_bytes / (ms_step * 1e-3) / 8e12 / world,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_source": peak_src, "kernel_us": kernel_ms * 1e3,
+                     "algorithmic_bytes_per_launch": shard_algo_bytes},
+        "e2e": {"value": algo_bytes / (ms_e2e / args.steps * 1e-3) / 1e9, "unit": "GB/s",
+                "h2d_bytes_per_step": K * 2, "d2h_bytes_per_step": int(y_host.numel() * 4), "us_per_step": ms_e2e / args.steps * 1e3},
+        "gpu_launches": args.steps,
+        "cublas_bf16_gemv_us": cublas_us,
+        "clocks": clocks, "parity": parity,
+        "host": {"gen_s": t_gen, "encode_s": t_enc, "encode_GBps_bf16": (r1 - r0) * K * 2 / t_enc / 1e9, "threads": os.cpu_count()},
+    }
+    if world == 1 and not args.no_cpu:
+        base, _ = cpu_arm(16384, 3)
+        line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rows", type=int, default=ROWS, help="rows of the matrix (default: the vocabulary projection)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--cublas", action="store_true", help="also time a stock BF16 GEMV of the uncompressed matrix")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -4,6 +4,7 @@
 // quad j = s>>2, whose bytes are the columns 128*j + 4*l + {0,1,2,3}.
 #pragma once
 
+#include "../../include/bf16n_c.h"
 #include "format.h"
 
 #include <cuda_bf16.h>
@@ -245,6 +246,35 @@ __device__ __forceinline__ void nib_assemble8(const uint4 & sm, const uint2 & co
 __device__ __forceinline__ uint32_t esc_bits(uint32_t rec) { // BF16 bit pattern of an escape record
     const uint32_t sm = (rec >> 12) & 0xFFu, ex = rec >> 20;
     return ((sm & 0x80u) << 8) | (ex << 7) | (sm & 0x7Fu);
+}
+
+// ---------------------------------------------------------------- host: views of a weight, column descriptor
+
+inline PairView pair_view(const bf16n_weight & w) {
+    return {w.plane, (const uint32_t *) (w.aux + w.off_a), (const uint32_t *) (w.aux + w.off_b),
+            (const uint16_t *) (w.aux + w.off_c), (const uint32_t *) (w.aux + w.off_d)};
+}
+inline HufView huf_view(const bf16n_weight & w) {
+    return {w.plane, (const uint32_t *) (w.aux + w.off_a), (const uint32_t *) (w.aux + w.off_b),
+            (const uint32_t *) (w.aux + w.off_c)};
+}
+inline NibView nib_view(const bf16n_weight & w, int64_t shift_rows = 0) {
+    // shifting every per-row array by `shift_rows` rows addresses the up half of a merged [gate; up] matrix: escape
+    // offsets are absolute indices into the escape list, so the list itself does not move
+    return {w.plane + shift_rows * w.K, w.aux + w.off_a + shift_rows * (w.K / 2), (const uint4 *) (w.aux + w.off_b) + shift_rows,
+            (const uint32_t *) (w.aux + w.off_c) + shift_rows, (const uint32_t *) (w.aux + w.off_d)};
+}
+
+inline Cols make_cols(const bf16n_mmv_args & a) {
+    Cols c = {};
+    c.x = (const char *) a.x; c.y = (char *) a.y;
+    c.x_tok = a.x_tok; c.y_tok = a.y_tok; c.x_slot = a.x_slot; c.y_slot = a.y_slot;
+    c.ids = (const char *) a.ids; c.ids_s0 = a.ids_s0; c.ids_s1 = a.ids_s1;
+    c.n_used = a.ids ? a.n_used : 1;
+    c.x_per_slot = a.x_per_slot > 0 ? a.x_per_slot : 1;
+    c.rows_per_matrix = a.rows_per_matrix; c.row0 = a.row0; c.nrows = a.nrows;
+    c.y_bf16 = a.y_bf16 != 0;
+    return c;
 }
 
 } // namespace dev

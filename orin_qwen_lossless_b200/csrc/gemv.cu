@@ -494,33 +494,6 @@ __global__ void __launch_bounds__(256) k_nib_rows(const NibView w, int C, const 
 
 // ---------------------------------------------------------------- views and geometry
 
-PairView pair_view(const bf16n_weight & w) {
-    return {w.plane, (const uint32_t *) (w.aux + w.off_a), (const uint32_t *) (w.aux + w.off_b),
-            (const uint16_t *) (w.aux + w.off_c), (const uint32_t *) (w.aux + w.off_d)};
-}
-HufView huf_view(const bf16n_weight & w) {
-    return {w.plane, (const uint32_t *) (w.aux + w.off_a), (const uint32_t *) (w.aux + w.off_b),
-            (const uint32_t *) (w.aux + w.off_c)};
-}
-NibView nib_view(const bf16n_weight & w, int64_t shift_rows = 0) {
-    // shifting every per-row array by `shift_rows` rows addresses the up half of a merged [gate; up] matrix: escape
-    // offsets are absolute indices into the escape list, so the list itself does not move
-    return {w.plane + shift_rows * w.K, w.aux + w.off_a + shift_rows * (w.K / 2), (const uint4 *) (w.aux + w.off_b) + shift_rows,
-            (const uint32_t *) (w.aux + w.off_c) + shift_rows, (const uint32_t *) (w.aux + w.off_d)};
-}
-
-Cols make_cols(const bf16n_mmv_args & a) {
-    Cols c = {};
-    c.x = (const char *) a.x; c.y = (char *) a.y;
-    c.x_tok = a.x_tok; c.y_tok = a.y_tok; c.x_slot = a.x_slot; c.y_slot = a.y_slot;
-    c.ids = (const char *) a.ids; c.ids_s0 = a.ids_s0; c.ids_s1 = a.ids_s1;
-    c.n_used = a.ids ? a.n_used : 1;
-    c.x_per_slot = a.x_per_slot > 0 ? a.x_per_slot : 1;
-    c.rows_per_matrix = a.rows_per_matrix; c.row0 = a.row0; c.nrows = a.nrows;
-    c.y_bf16 = a.y_bf16 != 0;
-    return c;
-}
-
 // warps per block and blocks for `units` warp-sized work items per column: spread few units over all SMs with small
 // blocks, fill the machine with 16-warp blocks otherwise
 void unit_geometry(int64_t units, int ncols, int max_warps, dim3 & grid, int & threads) {
@@ -568,6 +541,12 @@ void launch_gemv(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t 
                 }
 #undef MC
             }
+        } else if (gemv_rings_enabled() && gemv_rings_applies(w, a)) {
+            gemv_rings(w, a, st);
+            return;
+        } else if (gemv_staged_applies(w, a)) {
+            gemv_staged(w, a, st);
+            return;
         } else {
             unit_geometry(units, a.ncols, 16, grid, threads);
             const size_t shm = 4 * HP_MAX_PAIRS + w.K * 4;
@@ -663,6 +642,8 @@ void gemv_init() {
     ATTR((k_pair_glu<4, float>), 8 * HP_MAX_PAIRS + 4 * CHUNK * 4);
     ATTR((k_pair_glu<4, bf16>), 8 * HP_MAX_PAIRS + 4 * CHUNK * 4);
 #undef ATTR
+    gemv_staged_init();
+    gemv_rings_init();
 }
 
 void gemv(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st, bool multi_col) {

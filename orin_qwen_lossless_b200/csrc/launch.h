@@ -34,6 +34,17 @@ void expand_compare(const bf16n_weight & w, int64_t row0, int64_t nrows, const u
 void gather_rows(const bf16n_weight & w, const void * ids, int64_t ids_s0, int64_t n, void * dst, bool dst_bf16, int64_t dst_s1,
                  int64_t row0, cudaStream_t st);
 
+// gemv_staged.cu
+void gemv_staged_init();
+bool gemv_staged_applies(const bf16n_weight & w, const bf16n_mmv_args & a);
+void gemv_staged(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st);
+
+// gemv_rings.cu
+void gemv_rings_init();
+bool gemv_rings_enabled();
+bool gemv_rings_applies(const bf16n_weight & w, const bf16n_mmv_args & a);
+void gemv_rings(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st);
+
 // moe.cu
 void moe_init();
 void moe_topk(const float * logits, int n_tok, int n_experts, int k, int32_t * ids, float * weights, cudaStream_t st);
