@@ -133,6 +133,22 @@ int bf16n_swiglu(const float * g, const float * u, float * y, int64_t n, void * 
  * weights FP32 [n_tok, k]. */
 int bf16n_moe_topk(const float * logits, int n_tok, int n_experts, int k, int32_t * ids, float * weights, void * stream);
 
+/* One MoE decode step (1..64 tokens) of the routed experts, entirely on the device:
+ *   router (when router_logits != NULL: softmax top-n_used of n_experts logits per token into topk_ids / topk_weights;
+ *   otherwise those two arrays are inputs) -> gate and up products of every (token, slot) in one launch -> down product
+ *   reading silu(gate) * up directly -> weighted sum over the slots in slot order.
+ * It replaces the five-launch sequence of the reference's Python layer (engines/vllm/vllm_bf16n/ops.py:267-271:
+ * mmv, mmv, swiglu, mmv, moe_combine) and its host-side router; results are bit-identical to that sequence with an
+ * FP32 combine. gate/up: chunk-major HUFPAIR R = 8, K = 2048; down: row-major HUFPAIR R = 16, K = rows per expert of
+ * gate. Expert parallelism: the three weights hold experts [expert_lo, expert_lo + n_experts_local) of n_experts;
+ * slots routed elsewhere contribute exact zeros, so ranks' outputs add up to the full layer.
+ * scratch: device memory, bf16n_moe_decode_scratch_bytes(...) bytes, 16-byte aligned, owned by the caller. */
+size_t bf16n_moe_decode_scratch_bytes(int n_tok, int n_used, int64_t rows_gate_per_expert, int64_t rows_down_per_expert);
+int bf16n_moe_decode(const bf16n_weight * gate, const bf16n_weight * up, const bf16n_weight * down, const void * x, int x_bf16,
+                     int64_t x_tok, const float * router_logits, int n_experts, int32_t * topk_ids, float * topk_weights, int n_tok,
+                     int n_used, int expert_lo, int n_experts_local, float * scratch, size_t scratch_bytes, void * y, int y_bf16,
+                     void * stream);
+
 #ifdef __cplusplus
 }
 #endif

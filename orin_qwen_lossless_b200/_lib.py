@@ -54,6 +54,10 @@ SIGNATURES = {
     "bf16n_mm_ids": (C.c_int, [C.POINTER(Weight), C.POINTER(Weight), C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "bf16n_moe_combine": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_void_p]),
     "bf16n_swiglu": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
+    "bf16n_moe_decode_scratch_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int64, C.c_int64]),
+    "bf16n_moe_decode": (C.c_int, [C.POINTER(Weight), C.POINTER(Weight), C.POINTER(Weight), C.c_void_p, C.c_int, C.c_int64, C.c_void_p,
+                                   C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t,
+                                   C.c_void_p, C.c_int, C.c_void_p]),
     "bf16n_moe_topk": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
 }
 

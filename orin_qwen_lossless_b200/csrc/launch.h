@@ -53,6 +53,13 @@ void moe_swiglu(const float * g, const float * u, float * y, int64_t n, cudaStre
 void moe_route(const void * ids, bool ids_i64, int64_t ids_row_stride, int32_t * ids_src1, int32_t * ids_dst, int32_t * bounds,
                int n_experts, int n_tok, int n_used, int nchannels_y, int sis1, cudaStream_t st);
 
+// moe_decode.cu
+void moe_decode_init();
+bool moe_decode_supported(const bf16n_weight & gate, const bf16n_weight & up, const bf16n_weight & down);
+void moe_decode(const bf16n_weight & gate, const bf16n_weight & up, const bf16n_weight & down, const void * x, bool x_bf16,
+                int64_t x_tok, const int32_t * ids, const float * weights, int n_tok, int n_used, int n_experts_local, int e_lo,
+                float * scratch, void * y, bool y_bf16, cudaStream_t st);
+
 // prefill.cu
 void prefill_init();
 bool prefill_supported(const bf16n_weight & w, const bf16n_weight * up);

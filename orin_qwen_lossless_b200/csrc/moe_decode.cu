@@ -1,0 +1,261 @@
+// Routed-expert products of a MoE decode step (1..8 tokens): latency-oriented kernels for the stacked expert matrices.
+//
+// A column is one (token, slot) pair whose expert id is read on the device. Work is split as finely as the format
+// allows: one warp decodes one unit (R rows) of one matrix for one column, so a gate/up launch at 1 token is
+// 8 slots x 2 matrices x 64 units = 1024 independent warps. Every warp stages its unit's exponent streams with one bulk
+// async copy (bounded wait), keeps its activations in registers and walks the streams as in gemv_staged.cu.
+//   k_expert_units<C, R, CM, TX, GLU_IN>:
+//     CM      chunk-major units (gate / up, K > 512): per chunk the R rows share the lane's activations
+//     GLU_IN  the activation of the column is silu(g) * u formed while loading (the down product reads the gate and up
+//             outputs directly: no separate activation kernel and no third buffer)
+//   grid = (unit groups, columns, matrices): blockIdx.z picks gate or up so that one launch covers both.
+// Columns whose expert lies outside [e_lo, e_lo + e_n) (expert-parallel ranks own a slice of the experts) write zeros.
+// Summation order per row is the format's (chunk sums per row, then the xor butterfly), identical to the general
+// kernels, so results are bit-identical to bf16n_mmv on the same expert.
+#include "staged.cuh"
+#include "launch.h"
+
+namespace b16 {
+namespace {
+
+using namespace dev;
+
+struct ExpertMat { // one stacked expert matrix (n_experts * rows_per_expert rows)
+    PairView v;
+    const AuxHeader * hdr;
+    char * y;          // FP32 output [n_tok, n_used, rows_per_expert]
+};
+
+struct ExpertCols {
+    const char * x;  int64_t x_tok, x_slot;   // activations: per token (x_slot = 0) or per (token, slot)
+    const float * x2;                          // GLU_IN: second factor, same indexing as x (FP32)
+    const char * ids; int64_t ids_s0, ids_s1;
+    int n_used;
+    int64_t rows_per_expert;
+    int e_lo, e_n;                             // experts held by this weight: global ids [e_lo, e_lo + e_n)
+    uint32_t cap_bytes;
+};
+
+template <int C, int R, bool CM, typename TX, bool GLU_IN>
+__global__ void __launch_bounds__(256) k_expert_units(const ExpertMat m0, const ExpertMat m1, const ExpertCols p, const Opaque k) {
+    constexpr int K = C * CHUNK;
+    extern __shared__ __align__(128) unsigned char smem[];
+    uint32_t * lut = (uint32_t *) smem;
+    uint64_t * bars = (uint64_t *) (smem + 4 * HP_MAX_PAIRS);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    unsigned char * buf = smem + 4 * HP_MAX_PAIRS + 128 + (size_t) warp * p.cap_bytes;
+    const uint32_t bar = smem_u32(bars + warp);
+    const ExpertMat & m = blockIdx.z ? m1 : m0;
+
+    const int col = blockIdx.y, t = col / p.n_used, s = col - t * p.n_used;
+    const int e = *(const int32_t *) (p.ids + t * p.ids_s1 + s * p.ids_s0) - p.e_lo;
+    const int64_t units = p.rows_per_expert / R;
+    const int64_t u = (int64_t) blockIdx.x * nwarp + warp;
+    float * y = (float *) m.y + ((int64_t) t * p.n_used + s) * p.rows_per_expert;
+    if (e < 0 || e >= p.e_n) { // not this rank's expert: the combine adds exact zeros
+        if (u < units && lane < R) { y[u * R + lane] = 0.f; }
+        return;
+    }
+    for (int i = threadIdx.x; i < HP_MAX_PAIRS / 4; i += blockDim.x) { ((uint4 *) lut)[i] = __ldg((const uint4 *) m.v.lut + i); }
+    if (lane == 0) { mbar_init(bar, 1); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncthreads();
+    if (u >= units) { return; }
+
+    const int64_t gu = (int64_t) e * units + u;
+    const uint32_t w0 = __ldg(m.v.ubase + gu);
+    const uint32_t w1 = gu + 1 < (int64_t) m.hdr->n_a ? __ldg(m.v.ubase + gu + 1) : (uint32_t) m.hdr->n_b;
+    const uint32_t start = w0 & ~3u, bytes = ((w1 - start + 4u + 3u) & ~3u) * 4u;
+    const bool staged = bytes <= p.cap_bytes;
+    if (staged && lane == 0) {
+        mbar_expect_tx(bar, bytes);
+        bulk_g2s(smem_u32(buf), m.v.stream + start, bytes, bar);
+    }
+    const uint32_t my = w0 - start + __ldg(m.v.lrel + gu * 32 + lane);
+
+    // this lane's activations, in registers (FP32 values; BF16 inputs are widened exactly)
+    float4 xr[C * 4];
+    {
+        const char * xp = p.x + t * p.x_tok + s * p.x_slot;
+        const float * x2 = GLU_IN ? p.x2 + (xp - p.x) / 4 : nullptr;
+#pragma unroll
+        for (int i = 0; i < C * 4; i++) {
+            const int at = (i >> 2) * CHUNK + 128 * (i & 3) + 4 * lane;
+            float4 v = ldg_x4((const TX *) xp, at);
+            if (GLU_IN) {
+                const float4 g = v, w2 = __ldg((const float4 *) (x2 + at));
+                v = make_float4(silu_f(g.x) * w2.x, silu_f(g.y) * w2.y, silu_f(g.z) * w2.z, silu_f(g.w) * w2.w);
+            }
+            xr[i] = v;
+        }
+    }
+    const uint8_t * pl = m.v.plane + gu * R * K + 16 * lane;
+
+    auto rows = [&](auto & rd, uint32_t lut_arg) {
+        float mine = 0.f;
+        if (CM) {
+            float acc[R];
+#pragma unroll
+            for (int rr = 0; rr < R; rr++) { acc[rr] = 0.f; }
+#pragma unroll
+            for (int c = 0; c < C; c++) {
+                uint4 sm[R];
+#pragma unroll
+                for (int rr = 0; rr < R; rr++) { sm[rr] = ld_stream16(pl + (c * R + rr) * CHUNK); }
+#pragma unroll
+                for (int rr = 0; rr < R; rr++) {
+                    uint32_t en[8], wv[8];
+                    rd.take8(lut_arg, k, en);
+                    assemble8(sm[rr], en, wv);
+                    float a[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const float4 xv = xr[(C == 1 ? 0 : c) * 4 + j];
+                        a[0] = fmaf(bf16lo_f32(wv[2 * j]), xv.x, a[0]);
+                        a[1] = fmaf(bf16hi_f32(wv[2 * j]), xv.y, a[1]);
+                        a[2] = fmaf(bf16lo_f32(wv[2 * j + 1]), xv.z, a[2]);
+                        a[3] = fmaf(bf16hi_f32(wv[2 * j + 1]), xv.w, a[3]);
+                    }
+                    acc[rr] += (a[0] + a[1]) + (a[2] + a[3]);
+                }
+            }
+#pragma unroll
+            for (int rr = 0; rr < R; rr++) {
+                const float sum = warp_sum(acc[rr]);
+                if (lane == rr) { mine = sum; }
+            }
+        } else {
+            for (int rr = 0; rr < R; rr++) {
+                float a[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int c = 0; c < C; c++) {
+                    const uint4 sm = ld_stream16(pl + rr * K + c * CHUNK);
+                    uint32_t en[8], wv[8];
+                    rd.take8(lut_arg, k, en);
+                    assemble8(sm, en, wv);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const float4 xv = xr[c * 4 + j];
+                        a[0] = fmaf(bf16lo_f32(wv[2 * j]), xv.x, a[0]);
+                        a[1] = fmaf(bf16hi_f32(wv[2 * j]), xv.y, a[1]);
+                        a[2] = fmaf(bf16lo_f32(wv[2 * j + 1]), xv.z, a[2]);
+                        a[3] = fmaf(bf16hi_f32(wv[2 * j + 1]), xv.w, a[3]);
+                    }
+                }
+                const float sum = warp_sum((a[0] + a[1]) + (a[2] + a[3]));
+                if (lane == rr) { mine = sum; }
+            }
+        }
+        return mine;
+    };
+
+    float mine;
+    if (staged) {
+        const uint32_t landed = mbar_wait(bar, 0);
+        if (!landed) {
+            if (lane == 0) { atomicOr(&g_wait_expired, 1u); }
+            return;
+        }
+        StagedReader rd;
+        rd.open(smem_u32(buf) + 4 * my, landed);
+        mine = rows(rd, smem_u32(lut));
+    } else {
+        GlobalReader rd;
+        rd.lut = lut;
+        rd.rd.open(m.v, gu, lane);
+        mine = rows(rd, 0u);
+    }
+    if (lane < R) { y[u * R + lane] = mine; }
+}
+
+// y[t, i] = sum over slots, in slot order, of w[t, k] * ys[t, k, i]
+__global__ void k_combine_f32(const float * __restrict__ ys, const float * __restrict__ w, char * __restrict__ y, bool y_bf16, int n_used,
+                              int64_t n) {
+    const int t = blockIdx.y;
+    const OutVec out = {y + (int64_t) t * n * (y_bf16 ? 2 : 4), y_bf16};
+    for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) {
+        float acc = 0.f;
+        for (int kx = 0; kx < n_used; kx++) {
+            const int64_t s = (int64_t) t * n_used + kx;
+            acc = fmaf(w[s], ys[s * n + i], acc);
+        }
+        out.put(i, acc);
+    }
+}
+
+ExpertMat expert_mat(const bf16n_weight & w, float * y) { return {pair_view(w), (const AuxHeader *) w.aux, (char *) y}; }
+
+uint32_t unit_cap(const bf16n_weight & w) { return (uint32_t) ((w.R * w.K * 3 / 8 + 64 + 15) & ~15ll); }
+
+template <int C, int R, bool CM, typename TX, bool GLU_IN>
+void launch_units(const ExpertMat & m0, const ExpertMat & m1, int n_mats, const ExpertCols & p, int ncols, cudaStream_t st) {
+    const int64_t units = p.rows_per_expert / R;
+    // few tokens: small blocks so that the units of one column spread over many SMs
+    const int warps = ncols * n_mats * units >= (int64_t) device_info().sms * 16 ? 8 : 4;
+    const dim3 grid((unsigned) ((units + warps - 1) / warps), (unsigned) ncols, (unsigned) n_mats);
+    const size_t shm = 4 * HP_MAX_PAIRS + 128 + (size_t) warps * p.cap_bytes;
+    const Opaque k = {1u, 4u, ~0u, 32u};
+    static bool attr_done = false; // set once per instantiation, during bf16n_init's warm-up call (before any capture)
+    if (!attr_done) {
+        cuda_ok(cudaFuncSetAttribute(k_expert_units<C, R, CM, TX, GLU_IN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024),
+                "k_expert_units attribute");
+        attr_done = true;
+    }
+    if (ncols == 0) { return; }
+    k_expert_units<C, R, CM, TX, GLU_IN><<<grid, warps * 32, shm, st>>>(m0, m1, p, k);
+    check_launch();
+}
+
+using bf16 = __nv_bfloat16;
+
+bool gate_shape_ok(const bf16n_weight & w) {
+    return w.format == FMT_HUFPAIR && !w.fo && w.cm && w.K == 2048 && w.R == 8;
+}
+bool down_shape_ok(const bf16n_weight & w) {
+    return w.format == FMT_HUFPAIR && !w.fo && !w.cm && w.K == 512 && w.R == 16;
+}
+
+} // namespace
+
+bool moe_decode_supported(const bf16n_weight & gate, const bf16n_weight & up, const bf16n_weight & down) {
+    return gate_shape_ok(gate) && gate_shape_ok(up) && down_shape_ok(down) && gate.rows == up.rows;
+}
+
+void moe_decode_init() {
+    // instantiate and set the shared-memory attribute of every variant outside of any stream capture
+    ExpertMat none = {};
+    ExpertCols p = {};
+    p.rows_per_expert = 16; p.cap_bytes = 16;
+    launch_units<4, 8, true, bf16, false>(none, none, 2, p, 0, nullptr);
+    launch_units<4, 8, true, float, false>(none, none, 2, p, 0, nullptr);
+    launch_units<1, 16, false, float, true>(none, none, 1, p, 0, nullptr);
+}
+
+// gate/up (chunk-major R = 8, K = 2048) -> silu(g) * u -> down (row-major R = 16, K = 512) -> weighted sum over slots.
+// scratch: FP32 [2 * n_tok * n_used * N + n_tok * n_used * H] (N, H = rows per expert of gate and down).
+void moe_decode(const bf16n_weight & gate, const bf16n_weight & up, const bf16n_weight & down, const void * x, bool x_bf16,
+                int64_t x_tok, const int32_t * ids, const float * weights, int n_tok, int n_used, int n_experts_local, int e_lo,
+                float * scratch, void * y, bool y_bf16, cudaStream_t st) {
+    const int64_t N = gate.rows / n_experts_local, H = down.rows / n_experts_local;
+    const int ncols = n_tok * n_used;
+    float * g = scratch, * u = g + (int64_t) ncols * N, * ys = u + (int64_t) ncols * N;
+    ExpertCols p = {};
+    p.x = (const char *) x; p.x_tok = x_tok; p.x_slot = 0;
+    p.ids = (const char *) ids; p.ids_s0 = 4; p.ids_s1 = 4ll * n_used;
+    p.n_used = n_used; p.rows_per_expert = N; p.e_lo = e_lo; p.e_n = n_experts_local;
+    p.cap_bytes = unit_cap(gate);
+    if (x_bf16) {
+        launch_units<4, 8, true, bf16, false>(expert_mat(gate, g), expert_mat(up, u), 2, p, ncols, st);
+    } else {
+        launch_units<4, 8, true, float, false>(expert_mat(gate, g), expert_mat(up, u), 2, p, ncols, st);
+    }
+    ExpertCols q = p;
+    q.x = (const char *) g; q.x2 = u; q.x_tok = 4ll * n_used * N; q.x_slot = 4ll * N;
+    q.rows_per_expert = H; q.cap_bytes = unit_cap(down);
+    launch_units<1, 16, false, float, true>(expert_mat(down, ys), expert_mat(down, ys), 1, q, ncols, st);
+    const dim3 grid((unsigned) std::min<int64_t>((H + 255) / 256, 64), (unsigned) n_tok);
+    k_combine_f32<<<grid, 256, 0, st>>>(ys, weights, (char *) y, y_bf16, n_used, H);
+    check_launch();
+}
+
+} // namespace b16

@@ -467,3 +467,46 @@ def moe_experts(x: torch.Tensor, gate: Weight, up: Weight, down: Weight, topk_we
         u = mmv(x, up, topk_ids, N)
         ys = mmv(swiglu(g, u), down, topk_ids, H)
     return moe_combine(ys, topk_weights, torch.bfloat16)
+
+
+def moe_decode_scratch(n_tok: int, n_used: int, gate: Weight, down: Weight, n_experts_local: int, device) -> torch.Tensor:
+    """Scratch buffer for moe_decode (gate, up and per-slot down outputs, FP32)."""
+    n = lib().bf16n_moe_decode_scratch_bytes(n_tok, n_used, gate.meta.rows // n_experts_local, down.meta.rows // n_experts_local)
+    return torch.empty(max(n, 16) // 4, dtype=torch.float32, device=device)
+
+
+def moe_decode(x: torch.Tensor, gate: Weight, up: Weight, down: Weight, n_experts: int, top_k: int, *,
+               router_logits: torch.Tensor | None = None, topk_weights: torch.Tensor | None = None,
+               topk_ids: torch.Tensor | None = None, expert_lo: int = 0, n_experts_local: int | None = None,
+               scratch: torch.Tensor | None = None, out: torch.Tensor | None = None,
+               out_dtype: torch.dtype = torch.float32):
+    """One MoE decode step of the routed experts in four launches (router, gate+up, down with SwiGLU on load,
+    combine). Either router_logits (FP32 [T, n_experts]) or topk_weights / topk_ids (FP32 / int32 [T, top_k]) is given.
+    The weights hold experts [expert_lo, expert_lo + n_experts_local); other slots add zeros (expert parallelism).
+    Returns (y [T, H], topk_weights, topk_ids)."""
+    cg, cu, cd = gate.c(), up.c(), down.c()
+    _check_x(x, gate.meta.K)
+    if x.dim() != 2:
+        raise RuntimeError("bf16n.moe_decode: x must be [tokens, K]")
+    T = x.shape[0]
+    n_local = n_experts if n_experts_local is None else n_experts_local
+    H = down.meta.rows // n_local
+    dev = x.device
+    if router_logits is not None:
+        if not (router_logits.is_cuda and router_logits.dtype == torch.float32 and router_logits.is_contiguous()
+                and tuple(router_logits.shape) == (T, n_experts)):
+            raise RuntimeError("bf16n.moe_decode: router_logits must be contiguous f32 [tokens, n_experts]")
+        topk_ids = torch.empty((T, top_k), dtype=torch.int32, device=dev) if topk_ids is None else topk_ids
+        topk_weights = torch.empty((T, top_k), dtype=torch.float32, device=dev) if topk_weights is None else topk_weights
+    if not (topk_ids is not None and topk_ids.dtype == torch.int32 and topk_ids.is_contiguous()
+            and topk_weights is not None and topk_weights.dtype == torch.float32 and topk_weights.is_contiguous()):
+        raise RuntimeError("bf16n.moe_decode: topk_ids int32 / topk_weights f32, contiguous [tokens, top_k]")
+    if scratch is None:
+        scratch = moe_decode_scratch(T, top_k, gate, down, n_local, dev)
+    y = torch.empty((T, H), dtype=out_dtype, device=dev) if out is None else out
+    with torch.cuda.device(dev):
+        check(lib().bf16n_moe_decode(C.byref(cg), C.byref(cu), C.byref(cd), x.data_ptr(), int(x.dtype == torch.bfloat16),
+                                     x.stride(0) * x.element_size(), router_logits.data_ptr() if router_logits is not None else None,
+                                     n_experts, topk_ids.data_ptr(), topk_weights.data_ptr(), T, top_k, expert_lo, n_local,
+                                     scratch.data_ptr(), scratch.numel() * 4, y.data_ptr(), int(y.dtype == torch.bfloat16), _stream()))
+    return y, topk_weights, topk_ids

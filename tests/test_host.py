@@ -116,3 +116,34 @@ def test_policy_of_the_benchmark_shapes():
         assert ops.choose(rows, K, engine="llama") == (1, 0, False, False)
     assert ops.choose(512, 2048, 256, engine="llama", expert=True) == (3, 8, True, False)    # expert gate / up
     assert ops.choose(2048, 512, 256, engine="llama", expert=True) == (3, 16, False, False)  # expert down
+
+
+def test_cpp_wrapper_headers_compile_and_link(tmp_path):
+    """include/bf16n/*.h give the reference's C++ surface (namespace, structs, exceptions) over the C ABI."""
+    import shutil
+    import subprocess
+    if shutil.which("g++") is None:
+        pytest.skip("no g++")
+    src = tmp_path / "t.cpp"
+    src.write_text('''
+#include "bf16n/encode.h"
+#include "bf16n/policy.h"
+#include "bf16n/launch.h"
+#include <cstdio>
+int main() {
+    std::vector<uint16_t> w(16 * 512, 0x3c00);
+    const bf16n::encoded e = bf16n::encode(w.data(), 16, 512, bf16n::FMT_HUFPAIR, 4, false);
+    const auto c = bf16n::choose(248320, 2048);
+    bool threw = false;
+    try { bf16n::encode(w.data(), 15, 512, bf16n::FMT_HUFPAIR, 4, false); } catch (const std::invalid_argument &) { threw = true; }
+    bf16n::weight wv; bf16n::mmv_args a; (void) wv; (void) a;
+    std::printf("%zu %d %d %d\\n", e.plane.size(), e.format, c ? c->R : -1, (int) threw);
+    return 0;
+}
+''')
+    lib = _lib._build.LIB
+    exe = tmp_path / "t"
+    subprocess.run(["g++", "-std=c++17", "-I", os.path.join(ROOT, "include"), "-I", "/usr/local/cuda/include", str(src), "-o", str(exe),
+                    lib, "-Wl,-rpath," + os.path.dirname(lib)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    assert out == ["8192", "3", "16", "1"]
