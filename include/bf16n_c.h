@@ -149,6 +149,30 @@ int bf16n_moe_decode(const bf16n_weight * gate, const bf16n_weight * up, const b
                      int n_used, int expert_lo, int n_experts_local, float * scratch, size_t scratch_bytes, void * y, int y_bf16,
                      void * stream);
 
+/* bf16n_moe_decode for callers that cannot allocate device memory. It has no counterpart in the reference.
+ *
+ * Who needs it: code that runs a decode step at a point where cudaMalloc is not an option - an engine whose device
+ * memory was all committed to a fixed arena when the model was loaded, or a serving loop that must stay clear of the
+ * allocator because an allocation synchronises the device. bf16n_moe_decode asks such a caller for a scratch buffer it
+ * cannot provide; this entry point uses a buffer that is part of the library image instead and calls neither
+ * cudaMalloc nor cudaFree nor any allocating library routine.
+ *
+ * Same arguments, checks and results as bf16n_moe_decode (bit for bit), without scratch / scratch_bytes. Limits:
+ *   - the step must fit the built-in buffer: n_tok * n_used * (2 * rows_gate_per_expert + rows_down_per_expert) <=
+ *     BF16N_MOE_DECODE_STATIC_MAX_FLOATS (8 tokens x 8 slots of 512-row gate/up and 2048-row down experts); larger steps
+ *     are rejected with BF16N_EINVAL and a message naming both sizes;
+ *   - the buffer (768 KB) is held by every GPU that loads the library until the process exits;
+ *   - the first call on a device looks up the buffer's device address (the device must be current); make that first
+ *     call before any stream capture begins;
+ *   - all calls on a device share the one buffer, which keeps whatever the last call wrote. Nothing in it needs to be
+ *     cleared (each launch overwrites what the next one reads), but two calls whose kernels overlap on the GPU -
+ *     different streams, or graphs replayed concurrently - race on it: serialise them, or use bf16n_moe_decode with
+ *     one scratch buffer per stream. */
+#define BF16N_MOE_DECODE_STATIC_MAX_FLOATS 196608
+int bf16n_moe_decode_static(const bf16n_weight * gate, const bf16n_weight * up, const bf16n_weight * down, const void * x, int x_bf16,
+                            int64_t x_tok, const float * router_logits, int n_experts, int32_t * topk_ids, float * topk_weights,
+                            int n_tok, int n_used, int expert_lo, int n_experts_local, void * y, int y_bf16, void * stream);
+
 #ifdef __cplusplus
 }
 #endif

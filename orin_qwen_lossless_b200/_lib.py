@@ -58,6 +58,9 @@ SIGNATURES = {
     "bf16n_moe_decode": (C.c_int, [C.POINTER(Weight), C.POINTER(Weight), C.POINTER(Weight), C.c_void_p, C.c_int, C.c_int64, C.c_void_p,
                                    C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t,
                                    C.c_void_p, C.c_int, C.c_void_p]),
+    "bf16n_moe_decode_static": (C.c_int, [C.POINTER(Weight), C.POINTER(Weight), C.POINTER(Weight), C.c_void_p, C.c_int, C.c_int64,
+                                          C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                                          C.c_int, C.c_void_p]),
     "bf16n_moe_topk": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
 }
 

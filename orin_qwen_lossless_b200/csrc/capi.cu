@@ -300,4 +300,30 @@ int bf16n_moe_decode(const bf16n_weight * gate, const bf16n_weight * up, const b
     });
 }
 
+int bf16n_moe_decode_static(const bf16n_weight * gate, const bf16n_weight * up, const bf16n_weight * down, const void * x, int x_bf16,
+                            int64_t x_tok, const float * router_logits, int n_experts, int32_t * topk_ids, float * topk_weights,
+                            int n_tok, int n_used, int expert_lo, int n_experts_local, void * y, int y_bf16, void * stream) {
+    return guarded([&] {
+        ensure_init();
+        check_weight(*gate); check_weight(*up); check_weight(*down);
+        require(moe_decode_supported(*gate, *up, *down),
+                "moe_decode: gate/up must be chunk-major HUFPAIR R = 8 K = 2048 and down row-major HUFPAIR R = 16 K = 512");
+        require(n_tok >= 0 && n_tok <= 64 && n_used > 0 && n_used <= 32, "moe_decode: 0..64 tokens, 1..32 slots");
+        require(n_experts_local > 0 && expert_lo >= 0 && expert_lo + n_experts_local <= n_experts, "moe_decode: expert slice out of range");
+        require(gate->rows % n_experts_local == 0 && down->rows % n_experts_local == 0, "rows must split evenly into experts");
+        const int64_t N = gate->rows / n_experts_local, H = down->rows / n_experts_local;
+        require(N == down->K && H % down->R == 0 && N % gate->R == 0, "moe_decode: down's K must equal the gate/up rows per expert");
+        const size_t need = bf16n_moe_decode_scratch_bytes(n_tok, n_used, N, H) / sizeof(float);
+        if (need > moe_decode_static_capacity_floats()) {
+            fail_invalid("moe_decode_static: the step needs " + std::to_string(need) + " floats of scratch, the built-in buffer holds " +
+                         std::to_string(moe_decode_static_capacity_floats()) + " (BF16N_MOE_DECODE_STATIC_MAX_FLOATS); use bf16n_moe_decode");
+        }
+        require((uintptr_t) x % 16 == 0 && x_tok % 16 == 0, "moe_decode: x and its row stride must be 16-byte aligned");
+        if (n_tok == 0) { return; }
+        if (router_logits) { moe_topk(router_logits, n_tok, n_experts, n_used, topk_ids, topk_weights, (cudaStream_t) stream); }
+        moe_decode_static(*gate, *up, *down, x, x_bf16 != 0, x_tok, topk_ids, topk_weights, n_tok, n_used, n_experts_local, expert_lo,
+                          y, y_bf16 != 0, (cudaStream_t) stream);
+    });
+}
+
 } // extern "C"

@@ -15,6 +15,8 @@
 #include "staged.cuh"
 #include "launch.h"
 
+#include <mutex>
+
 namespace b16 {
 namespace {
 
@@ -256,6 +258,51 @@ void moe_decode(const bf16n_weight & gate, const bf16n_weight & up, const bf16n_
     const dim3 grid((unsigned) std::min<int64_t>((H + 255) / 256, 64), (unsigned) n_tok);
     k_combine_f32<<<grid, 256, 0, st>>>(ys, weights, (char *) y, y_bf16, n_used, H);
     check_launch();
+}
+
+
+// ---------------------------------------------------------------- the same step without caller-provided scratch
+
+// Some callers are not allowed to allocate device memory at the point where they run a decode step: an engine that
+// handed out all of its device memory to a fixed arena when the model was loaded, or a decode loop that must not reach
+// cudaMalloc because an allocation synchronises the whole device. For them the intermediate buffers of the step (gate
+// and up outputs and the per-slot down outputs, FP32) live in this array, which is part of the library image: every
+// GPU that loads the library holds these 768 KB until the process exits.
+constexpr size_t STATIC_SCRATCH_FLOATS = (size_t) BF16N_MOE_DECODE_STATIC_MAX_FLOATS;
+static __device__ __align__(256) float g_static_scratch[STATIC_SCRATCH_FLOATS];
+
+namespace {
+
+// Device address of g_static_scratch on the current device. In host code the array's name is only a handle, not a
+// pointer a kernel could use, so the address is asked for once per device (with that device current) and remembered.
+float * static_scratch_of_current_device() {
+    constexpr int MAX_DEVICES = 64;
+    static std::mutex lock;
+    static float * address[MAX_DEVICES] = {};
+    int dev = 0;
+    cuda_ok(cudaGetDevice(&dev), "cudaGetDevice");
+    require(dev >= 0 && dev < MAX_DEVICES, "moe_decode_static: device index out of range");
+    std::lock_guard<std::mutex> guard(lock);
+    if (!address[dev]) {
+        float * p = nullptr;
+        cuda_ok(cudaGetSymbolAddress((void **) &p, g_static_scratch), "cudaGetSymbolAddress(static MoE scratch)");
+        address[dev] = p;
+    }
+    return address[dev];
+}
+
+} // namespace
+
+size_t moe_decode_static_capacity_floats() { return STATIC_SCRATCH_FLOATS; }
+
+// moe_decode with the library's own scratch. Nothing in the array has to start at zero: the gate/up launch writes every
+// element the down launch reads (zeros for slots of other ranks' experts) and the down launch every element the
+// combine reads, so whatever an earlier call left behind is overwritten before it is used.
+void moe_decode_static(const bf16n_weight & gate, const bf16n_weight & up, const bf16n_weight & down, const void * x, bool x_bf16,
+                       int64_t x_tok, const int32_t * ids, const float * weights, int n_tok, int n_used, int n_experts_local,
+                       int e_lo, void * y, bool y_bf16, cudaStream_t st) {
+    moe_decode(gate, up, down, x, x_bf16, x_tok, ids, weights, n_tok, n_used, n_experts_local, e_lo,
+               static_scratch_of_current_device(), y, y_bf16, st);
 }
 
 } // namespace b16
