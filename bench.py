@@ -295,6 +295,136 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------ secondary workloads (configs 2, 3, 4 of the baseline)
+
+def _enc(ops, rows, K, fmt, R, cm, seed, dev):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    w = torch.empty((rows, K), dtype=torch.bfloat16)
+    step = 1 << 16
+    for r0 in range(0, rows, step):
+        n = min(step, rows - r0)
+        w[r0:r0 + n] = (torch.randn((n, K), generator=g) * 0.02).to(torch.bfloat16)
+    plane, aux, meta = ops.encode(w, fmt, R, cm)
+    return ops.upload(plane, aux, meta, dev)
+
+
+def _time_graph(torch, fn, reps, inner=1):
+    """Median-free mean over `reps` replays of a CUDA graph of `fn`; returns microseconds per inner step."""
+    s = torch.cuda.Stream()
+    fn()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(s):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            fn()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / reps / inner
+
+
+def run_small(args):
+    """Config 2: 48 layers x {2048x512, 512x2048, 256x2048} NIBBLE, batch-1 GEMVs, one CUDA graph of 144 launches."""
+    import torch
+    from orin_qwen_lossless_b200 import ops
+    dev = torch.device("cuda", 0)
+    ops.init()
+    layers, nbytes = [], 0
+    for l in range(48):
+        ws = [_enc(ops, 2048, 512, 1, 0, False, 3 * l, dev), _enc(ops, 512, 2048, 1, 0, False, 3 * l + 1, dev),
+              _enc(ops, 256, 2048, 1, 0, False, 3 * l + 2, dev)]
+        nbytes += sum(w.nbytes for w in ws)
+        layers.append(ws)
+    x512 = torch.randn(1, 512, device=dev).to(torch.bfloat16)
+    x2048 = torch.randn(1, 2048, device=dev).to(torch.bfloat16)
+    outs = [[torch.empty(1, w.meta.rows, device=dev) for w in ws] for ws in layers]
+
+    def step():
+        for ws, ys in zip(layers, outs):
+            ops.mmv(x512, ws[0], out=ys[0]); ops.mmv(x2048, ws[1], out=ys[1]); ops.mmv(x2048, ws[2], out=ys[2])
+
+    us = _time_graph(torch, step, args.steps)
+    peak, _ = measured_peak()
+    print(json.dumps({"workload": "small matrices: 48 layers x {2048x512, 512x2048, 256x2048} NIBBLE, batch-1, one CUDA graph of 144 GEMVs",
+                      "us_per_graph": us, "us_per_gemv": us / 144, "compressed_bytes": nbytes, "GBps": nbytes / us / 1e3,
+                      "frac_of_measured_hbm": nbytes / us / 1e3 / peak, "l2": "191 MB of weights per replay > L2"}), flush=True)
+
+
+def _moe_weights(ops, dev, n_experts):
+    gate = _enc(ops, n_experts * 512, 2048, 3, 8, True, 101, dev)
+    up = _enc(ops, n_experts * 512, 2048, 3, 8, True, 102, dev)
+    down = _enc(ops, n_experts * 2048, 512, 3, 16, False, 103, dev)
+    return gate, up, down
+
+
+def run_moe_decode(args):
+    """Config 3: hidden 2048, 256 routed experts (gate|up 512x2048 each, down 2048x512) + shared expert (NIBBLE), softmax
+    top-8 on the GPU, 1 / 2 / 4 tokens. A graph holds 16 steps with 16 different routings so that consecutive steps hit
+    different experts (the 1.08 GB of expert weights do not fit L2; one step touches 34 MB per token)."""
+    import torch
+    from orin_qwen_lossless_b200 import ops
+    dev = torch.device("cuda", 0)
+    ops.init()
+    E, k = 256, 8
+    gate, up, down = _moe_weights(ops, dev, E)
+    sh_gu = _enc(ops, 1024, 2048, 1, 0, False, 104, dev)
+    sh_down = _enc(ops, 2048, 512, 1, 0, False, 105, dev)
+    peak, _ = measured_peak()
+    for T in (1, 2, 4):
+        steps = 16
+        xs = [torch.randn(T, 2048, device=dev).to(torch.bfloat16) for _ in range(steps)]
+        logits = [torch.randn(T, E, device=dev) for _ in range(steps)]
+        scratch = ops.moe_decode_scratch(T, k, gate, down, E, dev)
+        ids = [torch.empty(T, k, dtype=torch.int32, device=dev) for _ in range(steps)]
+        wts = [torch.empty(T, k, device=dev) for _ in range(steps)]
+        y = torch.empty(T, 2048, device=dev)
+        ysh = torch.empty(T, 2048, device=dev)
+        a = torch.empty(T, 512, device=dev)
+
+        def step():
+            for i in range(steps):
+                ops.moe_decode(xs[i], gate, up, down, E, k, router_logits=logits[i], topk_weights=wts[i], topk_ids=ids[i],
+                               scratch=scratch, out=y)
+                ops._mmv_common(xs[i], sh_gu, None, 0, False, True, True, a)   # shared expert: merged gate|up GLU
+                ops.mmv(a, sh_down, out=ysh)
+                y.add_(ysh)
+
+        us = _time_graph(torch, step, max(args.steps // 16, 5), inner=steps)
+        distinct = sum(len(torch.unique(i)) for i in ids) / steps
+        per_expert = (gate.nbytes + up.nbytes + down.nbytes) / E
+        nbytes = distinct * per_expert + sh_gu.nbytes + sh_down.nbytes
+        print(json.dumps({"workload": f"MoE decode layer, {T} token(s), 256 experts top-8 + shared expert", "us_per_layer": us,
+                          "distinct_experts": distinct, "compressed_bytes": nbytes, "GBps": nbytes / us / 1e3,
+                          "frac_of_measured_hbm": nbytes / us / 1e3 / peak, "launches_per_layer": 7}), flush=True)
+
+
+def run_moe_prefill(args):
+    """Config 4: the same expert weights with 2048 and 8192 tokens: routing sort, batched gate/up + SwiGLU (BF16 out),
+    batched down (FP32 out), combine."""
+    import torch
+    from orin_qwen_lossless_b200 import ops
+    dev = torch.device("cuda", 0)
+    ops.init()
+    E, k = 256, 8
+    gate, up, down = _moe_weights(ops, dev, E)
+    for T in (2048, 8192):
+        x = torch.randn(T, 2048, device=dev).to(torch.bfloat16)
+        wts, ids = ops.moe_topk(torch.randn(T, E, device=dev), k)
+        us = _time_graph(torch, lambda: ops.moe_experts(x, gate, up, down, wts, ids, E), max(args.steps // 100, 5))
+        flops = 6.0 * 512 * 2048 * k * T
+        nbytes = gate.nbytes + up.nbytes + down.nbytes
+        print(json.dumps({"workload": f"MoE prefill layer, {T} tokens, 256 experts top-8", "us_per_layer": us,
+                          "TFLOPs": flops / us / 1e6, "weight_GBps": nbytes / us / 1e3,
+                          "frac_of_bf16_peak_1679": flops / us / 1e6 / 1679.3}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -304,7 +434,11 @@ def main():
     ap.add_argument("--rows", type=int, default=ROWS, help="rows of the matrix (default: the vocabulary projection)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cublas", action="store_true", help="also time a stock BF16 GEMV of the uncompressed matrix")
+    ap.add_argument("--workload", default="lm_head", choices=["lm_head", "small", "moe_decode", "moe_prefill"],
+                    help="lm_head is the headline contract line; the others print extra lines for the other baseline configs (1 GPU)")
     args = ap.parse_args()
+    if args.workload != "lm_head":
+        return {"small": run_small, "moe_decode": run_moe_decode, "moe_prefill": run_moe_prefill}[args.workload](args)
     if args.impl == "reference":
         run_reference(args)
     else:

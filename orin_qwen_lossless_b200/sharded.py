@@ -1,0 +1,199 @@
+"""Multi-GPU forms of the path (new: the reference is single-GPU). One process per GPU; torch.distributed carries the
+collectives (NCCL over NVLink on the GPUs, gloo in the CPU tests).
+
+* the vocabulary projection shards by rows on unit boundaries: `shard_rows` cuts one encoded tensor (one code for the
+  whole tensor) into per-rank tensors with valid headers; `lm_head_allgather` multiplies the local shard and gathers
+  the logits;
+* the MoE decode step is expert-parallel: every rank routes all tokens (cheap, deterministic), multiplies only the
+  slots whose expert it holds and the partial [T, H] outputs are all-reduced;
+* the MoE prefill layer is expert-parallel with an all-to-all token dispatch: tokens are split over the ranks, each
+  routed (token, slot) row travels to the rank that holds its expert and its result travels back.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import ops
+from .ops import FLAG_CHUNK_MAJOR, FLAG_FRAG_ORDER, FMT_HUFFMAN, FMT_HUFPAIR, FMT_NIBBLE, HEADER, MAGIC, Meta
+
+HP_TAIL_WORDS, HUF_TAIL_WORDS = 32, 16
+
+
+def unit_range(rank: int, world: int, rows: int, unit_rows: int) -> tuple[int, int]:
+    """Rows [r0, r1) of `rank`: whole units, sizes differing by at most one unit."""
+    units = rows // unit_rows
+    return units * rank // world * unit_rows, units * (rank + 1) // world * unit_rows
+
+
+def _header(fmt, K, R, rows, off, n_a, n_b, flags) -> bytes:
+    return HEADER.pack(MAGIC, fmt, K, R, rows, off[0], off[1], off[2], off[3], n_a, n_b, flags, 0).ljust(256, b"\0")
+
+
+def shard_rows(plane: torch.Tensor, aux: torch.Tensor, r0: int, r1: int) -> tuple[torch.Tensor, torch.Tensor, Meta]:
+    """Rows [r0, r1) of an encoded matrix (CPU tensors) as an encoded matrix of its own: same code tables, plane rows
+    and per-unit / per-row arrays sliced, stream offsets rebased, a fresh header. r0 and r1 must be unit boundaries.
+    Fragment-order tensors are not supported."""
+    a = aux.numpy()
+    magic, fmt, K, R, rows, oa, ob, oc, od, n_a, n_b, flags, _ = HEADER.unpack(bytes(a[:HEADER.size]))
+    if magic != MAGIC or flags & FLAG_FRAG_ORDER:
+        raise ValueError("bf16n shard_rows: bad header or fragment-order tensor")
+    unit = 1 if fmt == FMT_NIBBLE else R
+    if not (0 <= r0 <= r1 <= rows) or r0 % unit or r1 % unit:
+        raise ValueError("bf16n shard_rows: rows must be a range of whole units")
+    n = r1 - r0
+    p = plane.reshape(rows, K)[r0:r1].contiguous()
+    if fmt == FMT_NIBBLE:
+        codes = a[oa + r0 * K // 2: oa + r1 * K // 2]
+        luts = a[ob + r0 * 16: ob + r1 * 16]
+        eo = a[oc: oc + 4 * (rows + 1)].view(np.uint32)
+        esc = a[od: od + 4 * max(int(n_a), 1)].view(np.uint32)
+        e0, e1 = int(eo[r0]), int(eo[r1])
+        new_eo = (eo[r0:r1 + 1] - e0).astype(np.uint32)
+        new_esc = esc[e0:e1] if e1 > e0 else np.zeros(1, np.uint32)
+        off = [256, 256 + codes.size, 256 + codes.size + luts.size, 256 + codes.size + luts.size + new_eo.size * 4]
+        body = [codes, luts, new_eo.view(np.uint8), new_esc.view(np.uint8)]
+        hdr = _header(fmt, K, 0, n, off, e1 - e0, 0, 0)
+    elif fmt == FMT_HUFPAIR:
+        u0, u1 = r0 // R, r1 // R
+        lut = a[oa: oa + 4 * 4096]
+        ubase = a[ob: ob + 4 * n_a].view(np.uint32)
+        lrel = a[oc: oc + 2 * 32 * n_a].view(np.uint16)
+        w0 = int(ubase[u0]) if u0 < n_a else int(n_b)
+        w1 = int(ubase[u1]) if u1 < n_a else int(n_b)
+        new_ub = (ubase[u0:u1] - w0).astype(np.uint32)
+        new_lr = lrel[32 * u0: 32 * u1]
+        stream = a[od + 4 * w0: od + 4 * w1]
+        o_b = 256 + lut.size
+        o_c = o_b + new_ub.size * 4
+        o_d = (o_c + new_lr.size * 2 + 15) & ~15
+        off = [256, o_b, o_c, o_d]
+        pad = np.zeros(o_d - (o_c + new_lr.size * 2), np.uint8)
+        body = [lut, new_ub.view(np.uint8), new_lr.view(np.uint8), pad, stream, np.zeros(4 * HP_TAIL_WORDS, np.uint8)]
+        hdr = _header(fmt, K, R, n, off, u1 - u0, w1 - w0, flags)
+    else:
+        u0, u1 = r0 // R, r1 // R
+        lut = a[oa: oa + 4 * 1024]
+        lane_off = a[ob: ob + 4 * 32 * n_a].view(np.uint32)
+        w0 = int(lane_off[32 * u0]) if u0 < n_a else int(n_b)
+        w1 = int(lane_off[32 * u1]) if u1 < n_a else int(n_b)
+        new_lo = (lane_off[32 * u0: 32 * u1] - w0).astype(np.uint32)
+        stream = a[oc + 4 * w0: oc + 4 * w1]
+        o_b = 256 + lut.size
+        o_c = o_b + new_lo.size * 4
+        off = [256, o_b, o_c, 0]
+        body = [lut, new_lo.view(np.uint8), stream, np.zeros(4 * HUF_TAIL_WORDS, np.uint8)]
+        hdr = _header(fmt, K, R, n, off, u1 - u0, w1 - w0, 0)
+    new_aux = torch.from_numpy(np.concatenate([np.frombuffer(hdr, np.uint8)] + [np.ascontiguousarray(b).view(np.uint8) for b in body]))
+    return p, new_aux, ops.parse_header(new_aux)
+
+
+# ------------------------------------------------------------------ vocabulary projection: rows sharded + all-gather
+
+class ShardedLinear:
+    """Row shard of a projection on this rank plus the buffers of the gathered result."""
+
+    def __init__(self, weight: ops.Weight, rows_total: int, unit_rows: int, group=None):
+        self.w, self.group = weight, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.ranges = [unit_range(r, self.world, rows_total, unit_rows) for r in range(self.world)]
+        self.width = max(b - a for a, b in self.ranges)  # shards padded to the widest: one all-gather assembles them
+        self.rows_total = rows_total
+
+    def buffers(self, T: int, device) -> torch.Tensor:
+        return torch.empty((self.world, T, self.width), dtype=torch.float32, device=device)
+
+    def __call__(self, x: torch.Tensor, gathered: torch.Tensor) -> torch.Tensor:
+        """x [T, K] (replicated) -> gathered[world, T, width] with rank r's logits in gathered[r, :, :rows_r]."""
+        a, b = self.ranges[self.rank]
+        mine = gathered[self.rank]
+        if self.width == b - a:
+            ops.mmv(x, self.w, out=mine)
+        else:
+            mine[:, : b - a].copy_(ops.mmv(x, self.w))
+        if self.world > 1:
+            dist.all_gather_into_tensor(gathered.view(-1), mine.reshape(-1), group=self.group)
+        return gathered
+
+    def assemble(self, gathered: torch.Tensor) -> torch.Tensor:
+        """[T, rows_total] logits from the gathered shards."""
+        return torch.cat([gathered[r, :, : b - a] for r, (a, b) in enumerate(self.ranges)], dim=1)
+
+
+# ------------------------------------------------------------------ MoE decode: expert-parallel + all-reduce
+
+def moe_decode_ep(x, gate, up, down, n_experts, top_k, router_logits, group=None, scratch=None):
+    """Expert-parallel decode step: this rank's weights hold experts [rank*E/G, (rank+1)*E/G). Returns the full
+    [T, H] FP32 output on every rank (sum of the ranks' partial outputs; the summation order differs from the
+    single-GPU slot order, so results agree to FP32 rounding, not bitwise)."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    n_local = n_experts // world
+    y, wts, ids = ops.moe_decode(x, gate, up, down, n_experts, top_k, router_logits=router_logits, expert_lo=rank * n_local,
+                                 n_experts_local=n_local, scratch=scratch)
+    if world > 1:
+        dist.all_reduce(y, group=group)
+    return y, wts, ids
+
+
+# ------------------------------------------------------------------ MoE prefill: expert-parallel + all-to-all dispatch
+
+def dispatch_plan(topk_ids: torch.Tensor, n_experts: int, world: int):
+    """For this rank's tokens: the routed (token, slot) pairs ordered by owner rank (then token, slot).
+    Returns (order [P] indices into the flattened pairs, send_counts [world], local expert id of each ordered pair)."""
+    n_local = n_experts // world
+    flat = topk_ids.reshape(-1).to(torch.int64)
+    owner = flat // n_local
+    order = torch.argsort(owner, stable=True)
+    send_counts = torch.bincount(owner, minlength=world)
+    return order, send_counts, (flat - owner * n_local)[order]
+
+
+def moe_prefill_ep(x, topk_weights, topk_ids, gate, up, down, n_experts, group=None, experts_fn=None):
+    """Expert-parallel prefill layer. x [T_local, H] BF16 and its routing are this rank's tokens; gate/up/down hold this
+    rank's experts. Every routed row is sent to its expert's rank (all-to-all), multiplied there with the batched
+    kernels (as single-slot tokens), sent back and combined in slot order. `experts_fn(rows, local_ids)` -> [n, H]
+    replaces the device kernels in the CPU tests of the exchange."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    T, k = topk_ids.shape
+    H = x.shape[1]
+    order, send_counts, local_e = dispatch_plan(topk_ids, n_experts, world)
+    tok = torch.div(order, k, rounding_mode="floor")
+    send_rows = x[tok]                                             # [P, H] ordered by owner
+    if world > 1:
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=group)
+        sc, rc = send_counts.tolist(), recv_counts.tolist()
+        recv_rows = x.new_empty((sum(rc), H))
+        dist.all_to_all_single(recv_rows, send_rows, rc, sc, group=group)
+        recv_e = local_e.new_empty(sum(rc))
+        dist.all_to_all_single(recv_e, local_e, rc, sc, group=group)
+    else:
+        sc = rc = send_counts.tolist()
+        recv_rows, recv_e = send_rows, local_e
+    if experts_fn is None:
+        n_local = n_experts // world
+        ids1 = recv_e.to(torch.int32).view(-1, 1)
+        if recv_rows.shape[0]:
+            a = ops.moe_mm_ids(recv_rows.contiguous(), ids1, gate, n_local, up=up, out_dtype=torch.bfloat16)   # [n, 1, N]
+            out_rows = ops.moe_mm_ids(a, ids1, down, n_local, out_dtype=torch.float32)[:, 0]                   # [n, H]
+        else:
+            out_rows = torch.empty((0, down.meta.rows // n_local), dtype=torch.float32, device=x.device)
+    else:
+        out_rows = experts_fn(recv_rows, recv_e)
+    if world > 1:
+        back = out_rows.new_empty((sum(sc), out_rows.shape[1]))
+        dist.all_to_all_single(back, out_rows.contiguous(), sc, rc, group=group)
+    else:
+        back = out_rows
+    ys = back.new_empty((T * k, back.shape[1]))
+    ys[order] = back                                                # undo the owner ordering: [T*k, H] in (token, slot) order
+    ys = ys.view(T, k, -1)
+    if experts_fn is None:
+        return ops.moe_combine(ys.contiguous(), topk_weights.contiguous(), torch.bfloat16)
+    acc = torch.zeros((T, ys.shape[2]), dtype=ys.dtype)
+    for s in range(k):
+        acc = acc + topk_weights[:, s:s + 1].to(ys.dtype) * ys[:, s]
+    return acc

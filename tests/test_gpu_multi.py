@@ -1,0 +1,89 @@
+"""Two-GPU runs of the sharded paths over NCCL (skipped with fewer than two GPUs): row-sharded projection + all-gather,
+expert-parallel MoE decode + all-reduce, expert-parallel MoE prefill + all-to-all, each against the single-GPU result."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import to_bf16_tensor
+from oracle import cpu_oracle as o
+
+pytestmark = pytest.mark.gpu
+E, TOPK, H, N = 8, 4, 2048, 512
+
+
+def _worker(rank, world, port, ret):
+    import torch.distributed as dist
+    from orin_qwen_lossless_b200 import ops, sharded
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        ops.init()
+        dev = torch.device("cuda", rank)
+
+        def enc(bits, R, cm):
+            p, a, m = ops.encode(to_bf16_tensor(bits), 3, R, cm)
+            return p, a, m
+
+        # 1. projection: one encoded tensor, sliced on unit boundaries
+        rows, K, R = 16 * 2049, 2048, 16
+        wb = o.weights_like(rows, K, 7)
+        p, a, m = enc(wb, R, False)
+        r0, r1 = sharded.unit_range(rank, world, rows, R)
+        sp, sa, sm = sharded.shard_rows(p, a, r0, r1)
+        lin = sharded.ShardedLinear(ops.upload(sp, sa, sm, dev), rows, R)
+        x = to_bf16_tensor(o.f32_to_bf16_bits(np.random.default_rng(3).standard_normal((2, K)).astype(np.float32))).to(dev)
+        y = lin.assemble(lin(x, lin.buffers(2, dev)))
+        full = ops.mmv(x, ops.upload(p, a, m, dev))
+        ok1 = bool(torch.equal(y, full))  # every row is computed by the same kernel code: bitwise
+
+        # 2. MoE decode, experts split over the ranks
+        bits = {"gate": o.weights_like(E * N, H, 11), "up": o.weights_like(E * N, H, 12), "down": o.weights_like(E * H, N, 13)}
+        n_local = E // world
+
+        def up_slice(name, R, cm, lo, n):
+            rpe = bits[name].shape[0] // E
+            return ops.upload(*enc(bits[name][lo * rpe:(lo + n) * rpe], R, cm), dev)
+
+        g, u, d = (up_slice("gate", 8, True, 0, E), up_slice("up", 8, True, 0, E), up_slice("down", 16, False, 0, E))
+        gl, ul, dl = (up_slice("gate", 8, True, rank * n_local, n_local), up_slice("up", 8, True, rank * n_local, n_local),
+                      up_slice("down", 16, False, rank * n_local, n_local))
+        T = 4
+        xt = to_bf16_tensor(o.f32_to_bf16_bits(np.random.default_rng(5).standard_normal((T, H)).astype(np.float32))).to(dev)
+        logits = torch.from_numpy(np.random.default_rng(6).standard_normal((T, E)).astype(np.float32)).to(dev)
+        y_ep, _, _ = sharded.moe_decode_ep(xt, gl, ul, dl, E, TOPK, logits)
+        y_1, wts, ids = ops.moe_decode(xt, g, u, d, E, TOPK, router_logits=logits)
+        ok2 = bool(torch.allclose(y_ep, y_1, rtol=0, atol=2.0 ** -17 * float(y_1.abs().max()) * TOPK))
+
+        # 3. MoE prefill: tokens split over the ranks, all-to-all dispatch to the experts' ranks
+        Tp = 40 + 8 * rank
+        xp = to_bf16_tensor(o.f32_to_bf16_bits(np.random.default_rng(20 + rank).standard_normal((Tp, H)).astype(np.float32))).to(dev)
+        lg = torch.from_numpy(np.random.default_rng(30 + rank).standard_normal((Tp, E)).astype(np.float32)).to(dev)
+        w_p, i_p = ops.moe_topk(lg, TOPK)
+        y_a2a = sharded.moe_prefill_ep(xp, w_p, i_p, gl, ul, dl, E)
+        y_loc = ops.moe_experts(xp, g, u, d, w_p, i_p, E)
+        err = float((y_a2a.float() - y_loc.float()).abs().max())
+        ok3 = err <= 2.0 ** -7 * float(y_loc.float().abs().max())
+        ret[rank] = (ok1, ok2, ok3)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpu_paths():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    ret = ctx.Manager().dict()
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, ret)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(600)
+        assert p.exitcode == 0
+    assert [ret[r] for r in range(2)] == [(True, True, True)] * 2
