@@ -120,8 +120,8 @@ struct PairView { // device pointers of one HUFPAIR matrix
     const uint32_t * stream;
 };
 
-// MSB-first reader of one lane's stream. `buf` holds `have` valid bits at the top; top_up() (call it before every
-// second lookup) keeps at least 32 of them, enough for two codes of up to 12 bits.
+// MSB-first reader of one lane's stream straight from global memory. `buf` holds `have` valid bits at the top; top_up()
+// (call it before every second lookup) keeps at least 32 of them, enough for two codes of up to 12 bits.
 struct PairReader {
     const uint32_t * next;
     uint64_t buf;
@@ -140,6 +140,47 @@ struct PairReader {
             buf |= (uint64_t) ahead << (32 - have);
             have += 32;
             ahead = __ldg(next++);
+        }
+    }
+    __device__ __forceinline__ uint32_t take(const uint32_t * lut) {
+        const uint32_t e = lut[(uint32_t) (buf >> (64 - HP_LMAX))];
+        const int n = e & 31;
+        buf <<= n;
+        have -= n;
+        return e;
+    }
+    // the 8 entries of one row-chunk (this lane's 16 weights)
+    __device__ __forceinline__ void take8(const uint32_t * lut, uint32_t (&e)[8]) {
+#pragma unroll
+        for (int q = 0; q < 8; q += 2) {
+            top_up();
+            e[q] = take(lut);
+            e[q + 1] = take(lut);
+        }
+    }
+};
+
+// The same reader with four words kept loaded ahead of the buffer: a lane crosses into a new 128-byte line every 32 words and the 32 lanes of a
+// warp do so at different times, so without the queue nearly every refill of a warp would wait for some lane's miss.
+struct DeepPairReader {
+    const uint32_t * next;
+    uint64_t buf;
+    uint32_t q0, q1, q2, q3; // the words after the buffered ones, oldest first
+    int have;
+
+    __device__ __forceinline__ void open(const PairView & w, int64_t unit, int lane) {
+        next = w.stream + (__ldg(w.ubase + unit) + __ldg(w.lrel + unit * 32 + lane));
+        buf = (uint64_t) __ldg(next) << 32 | __ldg(next + 1);
+        q0 = __ldg(next + 2); q1 = __ldg(next + 3); q2 = __ldg(next + 4); q3 = __ldg(next + 5);
+        next += 6;
+        have = 64;
+    }
+    __device__ __forceinline__ void top_up() {
+        if (have <= 32) {
+            buf |= (uint64_t) q0 << (32 - have);
+            have += 32;
+            q0 = q1; q1 = q2; q2 = q3;
+            q3 = __ldg(next++);
         }
     }
     // next table entry (the two exponents in place + code length); lut in shared memory

@@ -15,8 +15,9 @@
 //      mbarrier that releases the B buffer.
 // After the last chunk the accumulators are read back with tcgen05.ld (warp w reads TMEM lanes 32*(w%4)..+31) and
 // scattered through ids_dst; the SwiGLU variant first moves the up half next to the gate half through shared memory.
-// Every wait on an mbarrier is bounded: thread 0 polls, the verdict is shared through a block barrier, and on expiry
-// the block records the fault, frees its TMEM and returns. No cluster launch, no multicast.
+// The gathered activation tiles run STAGES deep so that the gather latency is hidden behind the MMAs of earlier tiles.
+// Every wait on an mbarrier is bounded: a thread whose wait expires clears a flag in shared memory, the block reads the
+// flag after its next barrier, records the fault, frees its TMEM and returns. No cluster launch, no multicast.
 #include "decode.cuh"
 #include "launch.h"
 
@@ -103,17 +104,9 @@ struct PrefillArgs {
     int64_t rows_per_expert;
 };
 
-// block-uniform bounded wait: thread 0 polls, everybody learns the verdict
-__device__ __forceinline__ bool block_wait(uint32_t bar, uint32_t parity, volatile int * verdict) {
-    if (threadIdx.x == 0) { *verdict = mbar_poll(bar, parity) ? 1 : 0; }
-    __syncthreads();
-    const bool ok = *verdict != 0;
-    __syncthreads();
-    return ok;
-}
-
-// C chunks per row, R rows per unit, CM chunk-major units, GLU fused gate/up + SwiGLU, NT tokens per pass
-template <int C, int R, bool CM, bool GLU, int NT>
+// C chunks per row, R rows per unit, CM chunk-major units, GLU fused gate/up + SwiGLU, NT tokens per pass, STAGES
+// gathered activation tiles in flight
+template <int C, int R, bool CM, bool GLU, int NT, int STAGES>
 __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const PrefillArgs p) {
     constexpr int K = C * CHUNK;
     constexpr int B_TILE_BYTES = NT * 128;
@@ -122,13 +115,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const PrefillArgs p) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char * smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u); // operand tiles need 1024-byte alignment
     unsigned char * a_slab = smem;                                   // 128 KB
-    unsigned char * b_buf = smem + A_SLAB_BYTES;                     // 2 x NT x 128 B
-    uint32_t * lut0 = (uint32_t *) (b_buf + 2 * B_TILE_BYTES);
+    unsigned char * b_buf = smem + A_SLAB_BYTES;                     // STAGES x NT x 128 B
+    uint32_t * lut0 = (uint32_t *) (b_buf + STAGES * B_TILE_BYTES);
     uint32_t * lut1 = lut0 + (GLU ? HP_MAX_PAIRS : 0);
     int32_t * tok_src = (int32_t *) (lut1 + HP_MAX_PAIRS);            // activation row of each token of the pass
     int32_t * tok_dst = tok_src + NT;
-    uint64_t * bars = (uint64_t *) (tok_dst + NT);                    // [0,1]: B buffer released, [2]: spare
-    uint32_t * tmem_slot = (uint32_t *) (bars + 4);
+    uint64_t * bars = (uint64_t *) (tok_dst + NT);                    // one per B stage: its MMAs are complete
+    uint32_t * tmem_slot = (uint32_t *) (bars + STAGES);
     volatile int * verdict = (volatile int *) (tmem_slot + 1);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -137,16 +130,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const PrefillArgs p) {
         if (GLU) { ((uint4 *) lut1)[i] = __ldg((const uint4 *) p.w1.lut + i); }
     }
     if (tid == 0) {
-        mbar_init(smem_u32(bars + 0), 1);
-        mbar_init(smem_u32(bars + 1), 1);
+        for (int i = 0; i < STAGES; i++) { mbar_init(smem_u32(bars + i), 1); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (tid == 0) { *verdict = 1; }
     if (warp == 0) { tmem_alloc(smem_u32(tmem_slot), NT); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    uint32_t uses[2] = {0, 0}; // commits so far on each B buffer's barrier
+    uint32_t uses[STAGES]; // commits so far on each B stage's barrier
+#pragma unroll
+    for (int i = 0; i < STAGES; i++) { uses[i] = 0; }
     bool ok = true;
 
     const int m_blocks = (int) (p.rows_per_expert / ROWS_OUT);
@@ -169,7 +164,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const PrefillArgs p) {
             const int uw = GLU ? (second ? warp - UNITS / 2 : warp) : warp; // unit inside this item's row block
             const int64_t gu = (int64_t) e * units_per_expert + (int64_t) mb * (GLU ? UNITS / 2 : UNITS) + uw;
             const int row_base = (second ? M_TILE / 2 : 0) + uw * R;
-            PairReader rd;
+            DeepPairReader rd;
             const uint8_t * pl = nullptr;
             if (decoder) {
                 rd.open(wv, gu, lane);
@@ -180,7 +175,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const PrefillArgs p) {
             // gather of B tile g (global tile counter over the item) into buffer g & 1
             auto load_b = [&](int g) {
                 const int kcol = g * KB;
-                unsigned char * dstb = b_buf + (g & 1) * B_TILE_BYTES;
+                unsigned char * dstb = b_buf + (g % STAGES) * B_TILE_BYTES;
                 for (int i = tid; i < (int) n_mma * 8; i += NTHREADS) {
                     const int t = i >> 3, piece = i & 7;
                     const bf16 * src = p.x + (int64_t) tok_src[t] * p.x_row + kcol + piece * 8;
@@ -188,10 +183,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const PrefillArgs p) {
                 }
                 cp_async_commit();
             };
-            load_b(0);
+            constexpr int TILES = C * 8;
+#pragma unroll
+            for (int g = 0; g < STAGES - 1; g++) {
+                if (g < TILES) { load_b(g); } else { cp_async_commit(); }
+            }
             for (int c = 0; ok && c < C; c++) {
-                // 1. decode chunk c of the unit's rows into the A slab (all MMAs that read the slab are complete: the
-                //    last wait of the previous chunk covered them)
+                // 1. decode chunk c of the unit's rows into the A slab (the wait that ended the previous chunk made
+                //    sure every MMA that read the slab is complete)
                 if (decoder) {
                     for (int rr = 0; rr < R; rr++) {
                         const int64_t off = CM ? (int64_t) (c * R + rr) * CHUNK : (int64_t) rr * K + (int64_t) c * CHUNK;
@@ -207,46 +206,42 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const PrefillArgs p) {
                         }
                     }
                 }
-                // row-major units (C = 1 only here) keep all their rows in one chunk; chunk-major readers continue
-                proxy_fence();
-                __syncthreads();
-                // 2. the eight 64-column tiles of the chunk
-                for (int kb = 0; ok && kb < 8; kb++) {
-                    const int g = c * 8 + kb, buf = g & 1;
-                    const bool more = g + 1 < C * 8;
-                    if (more) {
-                        // buffer (g+1)&1 was read by the MMAs of tile g-1: wait for their commit before overwriting
+                // 2. the eight 64-column tiles of the chunk; the block barrier of the first tile also publishes the slab
+                for (int kb = 0; kb < 8; kb++) {
+                    const int g = c * 8 + kb, st = g % STAGES;
+                    // tile g + STAGES - 1 goes into the stage tile g - 1 used: its MMAs must be complete
+                    if (g + STAGES - 1 < TILES) {
                         if (g >= 1) {
-                            ok = block_wait(smem_u32(bars + ((g + 1) & 1)), (uses[(g + 1) & 1] - 1) & 1, verdict);
-                            if (!ok) { break; }
+                            const int ps = (g - 1) % STAGES;
+                            if (!mbar_poll(smem_u32(bars + ps), (uses[ps] - 1) & 1)) { *verdict = 0; }
                         }
-                        load_b(g + 1);
-                        cp_async_wait<1>();
+                        load_b(g + STAGES - 1);
                     } else {
-                        cp_async_wait<0>();
+                        cp_async_commit(); // keeps the group count in step
                     }
+                    cp_async_wait<STAGES - 1>(); // tile g has landed (this thread's copies)
                     proxy_fence();
                     __syncthreads();
+                    if (*verdict == 0) { ok = false; break; }
                     if (tid == 0) {
                         tc_fence_after();
                         const uint32_t idesc = instr_desc(n_mma);
-                        const uint32_t a0 = smem_u32(a_slab + kb * A_TILE_BYTES), b0 = smem_u32(b_buf + buf * B_TILE_BYTES);
+                        const uint32_t a0 = smem_u32(a_slab + kb * A_TILE_BYTES), b0 = smem_u32(b_buf + st * B_TILE_BYTES);
 #pragma unroll
-                        for (int s = 0; s < 4; s++) {
-                            umma_bf16(tmem, tile_desc(a0 + s * 32), tile_desc(b0 + s * 32), idesc, (g | s) != 0);
+                        for (int s2 = 0; s2 < 4; s2++) {
+                            umma_bf16(tmem, tile_desc(a0 + s2 * 32), tile_desc(b0 + s2 * 32), idesc, (g | s2) != 0);
                         }
-                        umma_commit(smem_u32(bars + buf));
+                        umma_commit(smem_u32(bars + st));
                     }
-                    uses[buf]++;
+                    uses[st]++;
                 }
                 if (!ok) { break; }
-                // all MMAs of this chunk done before the slab is rewritten / the accumulators are read
+                // all MMAs of this chunk complete before the slab is rewritten / the accumulators are read
                 {
-                    const int last = c * 8 + 7;
-                    ok = block_wait(smem_u32(bars + (last & 1)), (uses[last & 1] - 1) & 1, verdict);
-                    if (ok && last >= 1 && C * 8 > 1) {
-                        // the other buffer's last commit is older and already complete (commits complete in order)
-                    }
+                    const int ls = (c * 8 + 7) % STAGES;
+                    if (!mbar_poll(smem_u32(bars + ls), (uses[ls] - 1) & 1)) { *verdict = 0; }
+                    __syncthreads();
+                    if (*verdict == 0) { ok = false; }
                 }
             }
             if (!ok) { break; }
@@ -307,16 +302,16 @@ PairView view_of(const bf16n_weight & w) {
             (const uint16_t *) (w.aux + w.off_c), (const uint32_t *) (w.aux + w.off_d)};
 }
 
-template <bool GLU, int NT> constexpr size_t smem_bytes() {
-    return A_SLAB_BYTES + 2 * NT * 128 + (GLU ? 2 : 1) * 4 * HP_MAX_PAIRS + 2 * NT * 4 + 4 * 8 + 16 + 1024;
+template <bool GLU, int NT, int STAGES> constexpr size_t smem_bytes() {
+    return A_SLAB_BYTES + STAGES * NT * 128 + (GLU ? 2 : 1) * 4 * HP_MAX_PAIRS + 2 * NT * 4 + STAGES * 8 + 16 + 1024;
 }
 
 } // namespace
 
 void prefill_init() {
-    cuda_ok(cudaFuncSetAttribute(k_prefill<4, 8, true, true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes<true, 128>()), "k_prefill glu");
-    cuda_ok(cudaFuncSetAttribute(k_prefill<4, 8, true, false, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes<false, 256>()), "k_prefill gate");
-    cuda_ok(cudaFuncSetAttribute(k_prefill<1, 16, false, false, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes<false, 256>()), "k_prefill down");
+    cuda_ok(cudaFuncSetAttribute(k_prefill<4, 8, true, true, 128, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes<true, 128, 4>()), "k_prefill glu");
+    cuda_ok(cudaFuncSetAttribute(k_prefill<4, 8, true, false, 256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes<false, 256, 2>()), "k_prefill gate");
+    cuda_ok(cudaFuncSetAttribute(k_prefill<1, 16, false, false, 256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes<false, 256, 2>()), "k_prefill down");
 }
 
 bool prefill_supported(const bf16n_weight & w, const bf16n_weight * up) {
@@ -344,11 +339,11 @@ void prefill_mm_ids(const bf16n_weight & w, const bf16n_weight * up, const void 
     require(a.rows_per_expert % rows_out == 0, "rows per expert must be a multiple of the batched kernel's row block");
     const unsigned grid = (unsigned) std::min<int64_t>(device_info().sms, (int64_t) n_experts * (a.rows_per_expert / rows_out));
     if (up) {
-        k_prefill<4, 8, true, true, 128><<<grid, NTHREADS, smem_bytes<true, 128>(), st>>>(a);
+        k_prefill<4, 8, true, true, 128, 4><<<grid, NTHREADS, smem_bytes<true, 128, 4>(), st>>>(a);
     } else if (w.K == 2048) {
-        k_prefill<4, 8, true, false, 256><<<grid, NTHREADS, smem_bytes<false, 256>(), st>>>(a);
+        k_prefill<4, 8, true, false, 256, 2><<<grid, NTHREADS, smem_bytes<false, 256, 2>(), st>>>(a);
     } else {
-        k_prefill<1, 16, false, false, 256><<<grid, NTHREADS, smem_bytes<false, 256>(), st>>>(a);
+        k_prefill<1, 16, false, false, 256, 2><<<grid, NTHREADS, smem_bytes<false, 256, 2>(), st>>>(a);
     }
     check_launch();
 }
