@@ -1,23 +1,30 @@
 // Batched (prefill) routed product on the 5th-generation tensor cores: dst[t, slot, :] = W_e x_t for every routed
 // (token, slot) pair, optionally fused gate/up + SwiGLU. Replaces the reference's persistent mma.sync kernel
-// (core/include/bf16n/kernels.cuh:1162-1505) with a tcgen05 / TMEM design.
+// (core/include/bf16n/kernels.cuh:1162-1505) with a warp-specialised tcgen05 / TMEM design.
 //
-// One persistent block of 16 warps per SM walks work items (expert, block of 128 weight rows, pass of up to NT of the
-// expert's tokens). For an item it loops over the 512-column chunks of K:
-//   1. decode: each warp owns one unit and decodes this chunk of its rows straight into the A operand tile in shared
-//      memory, in the canonical K-major 128-byte-swizzled layout the tensor core reads (8 tiles of 128 rows x 64 columns;
-//      a lane's 4 consecutive weights are one 8-byte store: the lane-major plane maps lanes 0..15 / 16..31 of column
-//      quad j to the 64-column tiles 2j / 2j+1). The bit-stream state stays in registers across chunks, which is what
-//      chunk-major units are for. With SwiGLU the tile holds 64 gate rows and the 64 matching up rows.
-//   2. multiply: per 64-column tile the routed activation rows are gathered (cp.async, zero-filled padding) into a
-//      double-buffered swizzled B tile while the previous tile is multiplied: one elected thread issues four
-//      tcgen05.mma (M = 128, N = tokens rounded to 16, K = 16) per tile, accumulating in TMEM, and commits to an
-//      mbarrier that releases the B buffer.
-// After the last chunk the accumulators are read back with tcgen05.ld (warp w reads TMEM lanes 32*(w%4)..+31) and
-// scattered through ids_dst; the SwiGLU variant first moves the up half next to the gate half through shared memory.
-// The gathered activation tiles run STAGES deep so that the gather latency is hidden behind the MMAs of earlier tiles.
-// Every wait on an mbarrier is bounded: a thread whose wait expires clears a flag in shared memory, the block reads the
-// flag after its next barrier, records the fault, frees its TMEM and returns. No cluster launch, no multicast.
+// One persistent block per SM walks work items (expert, block of weight rows, pass of up to G x 128 of the expert's
+// tokens). Its 20 warps have three roles that run concurrently and meet only through mbarriers:
+//
+//   * 16 decoder warps. Each owns one unit of the item (SwiGLU: 8 gate units + the 8 matching up units) and walks its
+//     exponent streams once, four rows at a time: a "weight tile" is 64 weight rows (4 per decoder warp) x one 512-column
+//     chunk, written straight into shared memory in the canonical K-major 128-byte-swizzled operand layout (8 k-tiles of
+//     64 rows x 64 columns; a lane's 4 consecutive weights are one 8-byte store: the lane-major plane maps lanes 0..15 /
+//     16..31 of column quad j to k-tiles 2j / 2j+1). Two weight tiles alternate, so decoding runs up to two tiles ahead
+//     of the tensor core. The bit-stream state stays in registers across chunks, which is what chunk-major units are for.
+//   * 3 gather warps. They copy the routed activation rows of the pass (cp.async, 16-byte pieces, a full 128-byte line
+//     per 8 threads) into a ring of 128-token x 64-column operand slots; each slot's mbarrier completes when the
+//     copies of all gather threads have landed (cp.async.mbarrier.arrive), so the threads never wait for their copies.
+//   * 1 MMA warp. One thread waits for a slot and (at each tile's first k-tile) for the weight tile, then issues four
+//     tcgen05.mma (M = 128 tokens, N = 64 weight rows, K = 16) that accumulate D[token, weight row] in TMEM;
+//     tcgen05.commit releases the slot and the weight tile to their producers and announces the finished accumulators.
+//
+// After the last chunk of a pass the four non-decoder warps read the accumulators back (tcgen05.ld: warp w reads TMEM
+// lanes 32w..32w+31 = tokens) and scatter them through ids_dst. A thread holds gate and up of the same (token, row), so
+// SwiGLU needs no exchange. Activations are the M operand, so an expert with few tokens costs no extra decoding and one
+// with many is decoded once per G x 128 tokens; experts without tokens are skipped.
+// Every wait is bounded. A wait that expires sets a block-wide flag; from then on every role runs through the rest of
+// its loops without waiting, multiplying or decoding, so that all barriers still see all their threads; the block then
+// lets the tensor core drain, records the fault, frees its TMEM and returns. No cluster launch, no multicast.
 #include "decode.cuh"
 #include "launch.h"
 
@@ -29,12 +36,19 @@ using bf16 = __nv_bfloat16;
 
 __device__ unsigned int g_prefill_fault; // a bounded wait expired (diagnostic)
 
-constexpr int NTHREADS = 512;
-constexpr int M_TILE = 128;              // weight rows per item (GLU: 64 gate + 64 up)
-constexpr int KB = 64;                   // columns per operand tile (128 bytes of BF16: one swizzle row)
-constexpr int A_TILE_BYTES = M_TILE * 128;
-constexpr int A_SLAB_BYTES = 8 * A_TILE_BYTES; // one 512-column chunk
+constexpr int DEC_WARPS = 16, GATHER_WARPS = 3, GATHERERS = GATHER_WARPS * 32;
+constexpr int MMA_WARP = DEC_WARPS + GATHER_WARPS;   // the last warp
+constexpr int HELPERS = (GATHER_WARPS + 1) * 32;     // the epilogue is done by the gather warps and the MMA warp
+constexpr int NTHREADS = DEC_WARPS * 32 + HELPERS;
+constexpr int SUB = 4;                           // rows a decoder warp adds to a weight tile
+constexpr int N_TILE = DEC_WARPS * SUB;          // weight rows per tile = N of the MMA
+constexpr int M_TOK = 128;                       // tokens per group = M of the MMA
+constexpr int W_KTILE_BYTES = N_TILE * 128;      // 64 rows x 64 columns of BF16
+constexpr int W_TILE_BYTES = 8 * W_KTILE_BYTES;  // one 512-column chunk
+constexpr int X_SLOT_BYTES = M_TOK * 128;        // 128 tokens x 64 columns
+constexpr int TMEM_COLS = 512;
 constexpr uint32_t POLL_LIMIT = 1u << 20;
+static_assert(HELPERS == 128, "four warps read the 128 TMEM lanes");
 
 __device__ __forceinline__ uint32_t smem_u32(const void * p) { return (uint32_t) __cvta_generic_to_shared(p); }
 
@@ -42,14 +56,29 @@ __device__ __forceinline__ uint32_t smem_u32(const void * p) { return (uint32_t)
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(bar) : "memory");
+}
+// bounded wait: gives up after POLL_LIMIT probes or two seconds, whichever comes first
 __device__ __forceinline__ bool mbar_poll(uint32_t bar, uint32_t parity) {
+    uint64_t t0 = 0;
     for (uint32_t i = 0; i < POLL_LIMIT; i++) {
         uint32_t done;
         asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
                      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
         if (done) { return true; }
+        if ((i & 255u) == 255u) {
+            uint64_t now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (t0 == 0) { t0 = now; } else if (now - t0 > 2000000000ull) { return false; }
+        }
     }
     return false;
+}
+// the wait every role uses: nothing is waited for once the block has failed, and an expired wait fails the block
+__device__ __forceinline__ void wait_on(uint64_t * bar, uint32_t parity, volatile int * failed) {
+    if (*failed) { return; }
+    if (!mbar_poll(smem_u32(bar), parity)) { *failed = 1; }
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(cols) : "memory");
@@ -62,12 +91,13 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
     asm volatile("{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }"
                  ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+__device__ __forceinline__ void umma_commit(uint64_t * bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void helper_bar() { asm volatile("bar.sync 1, %0;" ::"n"(HELPERS) : "memory"); }
 __device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&v)[32]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
                  "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -78,51 +108,74 @@ __device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&v)[32]) {
                  : "r"(addr) : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
-// 16-byte async copy global -> shared; bytes = 0 writes zeros (padding rows)
-__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void * src, uint32_t bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void * src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// asynchronous arrival on an mbarrier, triggered when all earlier cp.async of this thread are complete; the arrival is
+// one of the count the barrier was initialised with
+__device__ __forceinline__ void cp_async_arrive(uint64_t * bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 // shared-memory matrix descriptor of a K-major, 128-byte-swizzled tile: rows 128 bytes apart, 8-row groups 1024 bytes
 // apart (stride byte offset), descriptor version 1, layout type 2; `addr` may point 32*k bytes into the first row
 __device__ __forceinline__ uint64_t tile_desc(uint32_t addr) {
     return (uint64_t) ((addr >> 4) & 0x3FFFu) | (uint64_t) 1 << 16 | (uint64_t) (1024 >> 4) << 32 | (uint64_t) 1 << 46 | (uint64_t) 2 << 61;
 }
-// kind::f16 instruction descriptor: FP32 accumulate, BF16 A and B, both K-major, M = 128, N = n
-__device__ __forceinline__ uint32_t instr_desc(uint32_t n) {
-    return 1u << 4 | 1u << 7 | 1u << 10 | (n >> 3) << 17 | (uint32_t) (M_TILE >> 4) << 24;
-}
+// kind::f16 instruction descriptor: FP32 accumulate, BF16 A and B, both K-major, M = 128, N = 64
+constexpr uint32_t INSTR_DESC = 1u << 4 | 1u << 7 | 1u << 10 | (uint32_t) (N_TILE >> 3) << 17 | (uint32_t) (M_TOK >> 4) << 24;
 
 struct PrefillArgs {
     PairView w0, w1;                    // w1: the up matrix (GLU)
     const bf16 * x; int64_t x_row;      // activations: row ids_src1[j] * x_row
     const int32_t * ids_src1; const int32_t * ids_dst; const int32_t * bounds;
     char * dst; int64_t dst_col; bool dst_bf16;
+    bool vec_ok;                        // dst rows allow 4-element vector stores
     int n_experts;
     int64_t rows_per_expert;
 };
 
-// C chunks per row, R rows per unit, CM chunk-major units, GLU fused gate/up + SwiGLU, NT tokens per pass, STAGES
-// gathered activation tiles in flight
-template <int C, int R, bool CM, bool GLU, int NT, int STAGES>
+// four consecutive output elements of one (token, slot) row
+__device__ __forceinline__ void store4(const PrefillArgs & p, int64_t at, float a, float b, float c, float d) {
+    if (p.dst_bf16) {
+        bf16 * o = (bf16 *) p.dst + at;
+        if (p.vec_ok) {
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+            *(uint2 *) o = make_uint2(*(const uint32_t *) &lo, *(const uint32_t *) &hi);
+        } else {
+            o[0] = __float2bfloat16_rn(a); o[1] = __float2bfloat16_rn(b); o[2] = __float2bfloat16_rn(c); o[3] = __float2bfloat16_rn(d);
+        }
+    } else {
+        float * o = (float *) p.dst + at;
+        if (p.vec_ok) { *(float4 *) o = make_float4(a, b, c, d); }
+        else { o[0] = a; o[1] = b; o[2] = c; o[3] = d; }
+    }
+}
+
+// C chunks per row, R rows per unit, CM chunk-major units, GLU fused gate/up + SwiGLU, G token groups of 128 per pass,
+// SLOTS activation operand slots in the ring
+template <int C, int R, bool CM, bool GLU, int G, int SLOTS>
 __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const PrefillArgs p) {
+    static_assert(CM || C == 1, "row-major units are walked in row order: one chunk per row only");
+    static_assert(R % SUB == 0, "unit rows are split into groups of SUB");
     constexpr int K = C * CHUNK;
-    constexpr int B_TILE_BYTES = NT * 128;
-    constexpr int UNITS = M_TILE / R;                  // units decoded per item (GLU: half gate, half up)
-    constexpr int ROWS_OUT = GLU ? M_TILE / 2 : M_TILE; // output rows per item
+    constexpr int Q = R / SUB;                                 // weight tiles per chunk
+    constexpr int TILES = C * Q;                               // weight tiles per pass
+    constexpr int UNITS_PER_MAT = GLU ? DEC_WARPS / 2 : DEC_WARPS;
+    constexpr int ROWS_OUT = UNITS_PER_MAT * R;                // output rows per item
+    static_assert(G * Q * N_TILE <= TMEM_COLS, "accumulators of a pass must fit TMEM");
     extern __shared__ unsigned char smem_raw[];
     unsigned char * smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u); // operand tiles need 1024-byte alignment
-    unsigned char * a_slab = smem;                                   // 128 KB
-    unsigned char * b_buf = smem + A_SLAB_BYTES;                     // STAGES x NT x 128 B
-    uint32_t * lut0 = (uint32_t *) (b_buf + STAGES * B_TILE_BYTES);
+    unsigned char * wbuf = smem;                                     // 2 weight tiles
+    unsigned char * xbuf = wbuf + 2 * W_TILE_BYTES;                  // SLOTS activation slots
+    uint32_t * lut0 = (uint32_t *) (xbuf + SLOTS * X_SLOT_BYTES);
     uint32_t * lut1 = lut0 + (GLU ? HP_MAX_PAIRS : 0);
-    int32_t * tok_src = (int32_t *) (lut1 + HP_MAX_PAIRS);            // activation row of each token of the pass
-    int32_t * tok_dst = tok_src + NT;
-    uint64_t * bars = (uint64_t *) (tok_dst + NT);                    // one per B stage: its MMAs are complete
-    uint32_t * tmem_slot = (uint32_t *) (bars + STAGES);
-    volatile int * verdict = (volatile int *) (tmem_slot + 1);
+    uint64_t * bars = (uint64_t *) (lut1 + HP_MAX_PAIRS);
+    uint64_t * w_full = bars, * w_empty = bars + 2, * x_full = bars + 4, * x_free = x_full + SLOTS;
+    uint64_t * acc_done = x_free + SLOTS, * drained = acc_done + 1;
+    uint32_t * tmem_slot = (uint32_t *) (drained + 1);
+    volatile int * failed = (volatile int *) (tmem_slot + 1);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int i = tid; i < HP_MAX_PAIRS / 4; i += NTHREADS) {
@@ -130,171 +183,206 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const PrefillArgs p) {
         if (GLU) { ((uint4 *) lut1)[i] = __ldg((const uint4 *) p.w1.lut + i); }
     }
     if (tid == 0) {
-        for (int i = 0; i < STAGES; i++) { mbar_init(smem_u32(bars + i), 1); }
+        for (int i = 0; i < 2; i++) { mbar_init(smem_u32(w_full + i), DEC_WARPS); mbar_init(smem_u32(w_empty + i), 1); }
+        for (int i = 0; i < SLOTS; i++) { mbar_init(smem_u32(x_full + i), GATHERERS); mbar_init(smem_u32(x_free + i), 1); }
+        mbar_init(smem_u32(acc_done), 1);
+        mbar_init(smem_u32(drained), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        *failed = 0;
     }
-    if (tid == 0) { *verdict = 1; }
-    if (warp == 0) { tmem_alloc(smem_u32(tmem_slot), NT); }
+    if (warp == 0) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    uint32_t uses[STAGES]; // commits so far on each B stage's barrier
-#pragma unroll
-    for (int i = 0; i < STAGES; i++) { uses[i] = 0; }
-    bool ok = true;
 
     const int m_blocks = (int) (p.rows_per_expert / ROWS_OUT);
     const int64_t units_per_expert = p.rows_per_expert / R;
-    for (int item = blockIdx.x; ok && item < p.n_experts * m_blocks; item += gridDim.x) {
-        const int e = item / m_blocks, mb = item - e * m_blocks;
-        const int j0 = p.bounds[e], j1 = p.bounds[e + 1];
-        for (int jp = j0; ok && jp < j1; jp += NT) {
-            const int ntok = min(NT, j1 - jp);
-            const uint32_t n_mma = (uint32_t) ((ntok + 15) & ~15);
-            for (int i = tid; i < NT; i += NTHREADS) {
-                tok_src[i] = i < ntok ? p.ids_src1[jp + i] : 0;
-                tok_dst[i] = i < ntok ? p.ids_dst[jp + i] : 0;
-            }
-            // this warp's unit: its matrix, table, first row inside the A tile
-            const bool second = GLU && warp >= UNITS / 2;                 // up half
-            const bool decoder = warp < UNITS;
-            const PairView & wv = second ? p.w1 : p.w0;
-            const uint32_t * lut = second ? lut1 : lut0;
-            const int uw = GLU ? (second ? warp - UNITS / 2 : warp) : warp; // unit inside this item's row block
-            const int64_t gu = (int64_t) e * units_per_expert + (int64_t) mb * (GLU ? UNITS / 2 : UNITS) + uw;
-            const int row_base = (second ? M_TILE / 2 : 0) + uw * R;
-            DeepPairReader rd;
-            const uint8_t * pl = nullptr;
-            if (decoder) {
-                rd.open(wv, gu, lane);
-                pl = wv.plane + gu * R * K + 16 * lane;
-            }
-            __syncthreads(); // tok_src / tok_dst visible
+    const int n_items = p.n_experts * m_blocks;
 
-            // gather of B tile g (global tile counter over the item) into buffer g & 1
-            auto load_b = [&](int g) {
-                const int kcol = g * KB;
-                unsigned char * dstb = b_buf + (g % STAGES) * B_TILE_BYTES;
-                for (int i = tid; i < (int) n_mma * 8; i += NTHREADS) {
-                    const int t = i >> 3, piece = i & 7;
-                    const bf16 * src = p.x + (int64_t) tok_src[t] * p.x_row + kcol + piece * 8;
-                    cp_async16_zfill(smem_u32(dstb + t * 128 + ((piece ^ (t & 7)) << 4)), src, t < ntok ? 16u : 0u);
-                }
-                cp_async_commit();
-            };
-            constexpr int TILES = C * 8;
+    if (warp < DEC_WARPS) {
+        // ------------------------------------------------------------------ decoders
+        const bool second = GLU && warp >= DEC_WARPS / 2;                // up half
+        const PairView & wv = second ? p.w1 : p.w0;
+        const uint32_t * lut = second ? lut1 : lut0;
+        const int uw = second ? warp - DEC_WARPS / 2 : warp;             // unit inside this item's row block
+        const int n_row0 = GLU ? (second ? N_TILE / 2 : 0) + uw * SUB : warp * SUB; // first of this warp's rows in a weight tile
+        const uint32_t lane_part = (uint32_t) (lane >> 4) * W_KTILE_BYTES + (uint32_t) (lane & 1) * 8;
+        const uint32_t piece = (uint32_t) (lane & 15) >> 1;
+        uint32_t n = 0;                                                  // weight tiles produced
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+            const int e = item / m_blocks, mb = item - e * m_blocks;
+            const int j0 = p.bounds[e], j1 = p.bounds[e + 1];
+            const int64_t gu = (int64_t) e * units_per_expert + (int64_t) mb * UNITS_PER_MAT + uw;
+            for (int jp = j0; jp < j1; jp += G * M_TOK) {
+                if (*failed) { n += TILES; continue; }
+                DeepPairReader rd;
+                rd.open(wv, gu, lane);
+                const uint8_t * pl = wv.plane + gu * R * K + 16 * lane;
+                uint4 cur[SUB];
 #pragma unroll
-            for (int g = 0; g < STAGES - 1; g++) {
-                if (g < TILES) { load_b(g); } else { cp_async_commit(); }
-            }
-            for (int c = 0; ok && c < C; c++) {
-                // 1. decode chunk c of the unit's rows into the A slab (the wait that ended the previous chunk made
-                //    sure every MMA that read the slab is complete)
-                if (decoder) {
-                    for (int rr = 0; rr < R; rr++) {
-                        const int64_t off = CM ? (int64_t) (c * R + rr) * CHUNK : (int64_t) rr * K + (int64_t) c * CHUNK;
-                        const uint4 sm = ld_stream16(pl + off);
-                        uint32_t en[8], wv8[8];
+                for (int r = 0; r < SUB; r++) { cur[r] = ld_stream16(pl + r * CHUNK); }
+                for (int t = 0; t < TILES; t++) {
+                    // rows t*SUB .. t*SUB+3 of the unit in stream order (chunk-major: chunk t / Q, rows (t % Q) * SUB ..)
+                    uint4 nxt[SUB];
+                    if (t + 1 < TILES) {
+#pragma unroll
+                        for (int r = 0; r < SUB; r++) { nxt[r] = ld_stream16(pl + ((t + 1) * SUB + r) * CHUNK); }
+                    }
+                    const uint32_t b = n & 1, use = n >> 1;
+                    if (use >= 1) { // the MMAs that read this buffer's previous contents must be complete
+                        if (lane == 0) { wait_on(w_empty + b, (use - 1) & 1, failed); }
+                        __syncwarp();
+                    }
+                    unsigned char * wb = wbuf + b * W_TILE_BYTES + lane_part;
+#pragma unroll
+                    for (int r = 0; r < SUB; r++) {
+                        uint32_t en[8], w8[8];
                         rd.take8(lut, en);
-                        assemble8(sm, en, wv8);
-                        const int row = row_base + rr;
-                        unsigned char * rp = a_slab + row * 128 + (((lane & 15) >> 1) ^ (row & 7)) * 16 + (lane & 1) * 8;
+                        assemble8(cur[r], en, w8);
+                        const uint32_t row = (uint32_t) (n_row0 + r);
+                        unsigned char * rp = wb + row * 128 + ((piece ^ (row & 7)) << 4);
 #pragma unroll
-                        for (int j = 0; j < 4; j++) {
-                            *(uint2 *) (rp + (2 * j + (lane >> 4)) * A_TILE_BYTES) = make_uint2(wv8[2 * j], wv8[2 * j + 1]);
-                        }
+                        for (int j = 0; j < 4; j++) { *(uint2 *) (rp + 2 * j * W_KTILE_BYTES) = make_uint2(w8[2 * j], w8[2 * j + 1]); }
                     }
-                }
-                // 2. the eight 64-column tiles of the chunk; the block barrier of the first tile also publishes the slab
-                for (int kb = 0; kb < 8; kb++) {
-                    const int g = c * 8 + kb, st = g % STAGES;
-                    // tile g + STAGES - 1 goes into the stage tile g - 1 used: its MMAs must be complete
-                    if (g + STAGES - 1 < TILES) {
-                        if (g >= 1) {
-                            const int ps = (g - 1) % STAGES;
-                            if (!mbar_poll(smem_u32(bars + ps), (uses[ps] - 1) & 1)) { *verdict = 0; }
-                        }
-                        load_b(g + STAGES - 1);
-                    } else {
-                        cp_async_commit(); // keeps the group count in step
-                    }
-                    cp_async_wait<STAGES - 1>(); // tile g has landed (this thread's copies)
                     proxy_fence();
-                    __syncthreads();
-                    if (*verdict == 0) { ok = false; break; }
-                    if (tid == 0) {
-                        tc_fence_after();
-                        const uint32_t idesc = instr_desc(n_mma);
-                        const uint32_t a0 = smem_u32(a_slab + kb * A_TILE_BYTES), b0 = smem_u32(b_buf + st * B_TILE_BYTES);
+                    __syncwarp();
+                    if (lane == 0) { mbar_arrive(smem_u32(w_full + b)); }
+                    n++;
+                    if (t + 1 < TILES) {
 #pragma unroll
-                        for (int s2 = 0; s2 < 4; s2++) {
-                            umma_bf16(tmem, tile_desc(a0 + s2 * 32), tile_desc(b0 + s2 * 32), idesc, (g | s2) != 0);
-                        }
-                        umma_commit(smem_u32(bars + st));
+                        for (int r = 0; r < SUB; r++) { cur[r] = nxt[r]; }
                     }
-                    uses[st]++;
-                }
-                if (!ok) { break; }
-                // all MMAs of this chunk complete before the slab is rewritten / the accumulators are read
-                {
-                    const int ls = (c * 8 + 7) % STAGES;
-                    if (!mbar_poll(smem_u32(bars + ls), (uses[ls] - 1) & 1)) { *verdict = 0; }
-                    __syncthreads();
-                    if (*verdict == 0) { ok = false; }
                 }
             }
-            if (!ok) { break; }
-            // 3. epilogue: TMEM -> registers -> dst
-            tc_fence_after();
-            const int q = warp & 3, cg = warp >> 2;            // TMEM lane quadrant, column group
-            constexpr int COLS_PER_WARP = NT / 4;
-            const int m = 32 * q + lane;                       // row of the A tile held by this thread
-            float * xchg = (float *) b_buf;                    // GLU: up half moved next to the gate half
-            for (int c0 = cg * COLS_PER_WARP; c0 < (cg + 1) * COLS_PER_WARP; c0 += 32) {
-                if (c0 >= (int) n_mma) { break; }
-                uint32_t v[32];
-                tmem_ld32(tmem + ((uint32_t) (32 * q) << 16) + (uint32_t) c0, v);
-                if (!GLU) {
-                    const int64_t row = (int64_t) mb * ROWS_OUT + m;
+        }
+    } else {
+        // ------------------------------------------------------------------ gather warps, MMA warp; epilogue by all four
+        const int ht = tid - DEC_WARPS * 32, hw = warp - DEC_WARPS;
+        const bool mma_warp = warp == MMA_WARP;
+        uint32_t n = 0;        // weight tiles consumed
+        uint32_t vv = 0;       // activation slots used
+        uint32_t passes = 0;
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+            const int e = item / m_blocks, mb = item - e * m_blocks;
+            const int j0 = p.bounds[e], j1 = p.bounds[e + 1];
+            for (int jp = j0; jp < j1; jp += G * M_TOK) {
+                const int ntok = min(G * M_TOK, j1 - jp), ng = (ntok + M_TOK - 1) / M_TOK;
+                const int total = TILES * 8 * ng; // slots of the pass: for each weight tile, for each k-tile, each token group
+                int64_t my_dst[G];
 #pragma unroll
-                    for (int i = 0; i < 32; i++) {
-                        if (c0 + i < ntok) {
-                            const int64_t at = (int64_t) tok_dst[c0 + i] * p.dst_col + row;
-                            if (p.dst_bf16) { ((bf16 *) p.dst)[at] = __float2bfloat16_rn(__uint_as_float(v[i])); }
-                            else { ((float *) p.dst)[at] = __uint_as_float(v[i]); }
+                for (int tg = 0; tg < G; tg++) {
+                    const int ti = tg * M_TOK + ht;
+                    my_dst[tg] = ti < ntok ? (int64_t) p.ids_dst[jp + ti] : -1;
+                }
+                if (!mma_warp) {
+                    // ---- gather: this thread copies 16-byte piece pc of rows r0, r0 + 12, ... of every slot
+                    const int pc = ht & 7, r0 = ht >> 3;
+                    constexpr int RSTEP = GATHERERS / 8, RMAX = (M_TOK + RSTEP - 1) / RSTEP;
+                    const bf16 * src[G][RMAX]; // the rows' activations at piece pc (nullptr: no such token)
+#pragma unroll
+                    for (int tg = 0; tg < G; tg++) {
+#pragma unroll
+                        for (int i = 0; i < RMAX; i++) {
+                            const int row = r0 + i * RSTEP, ti = tg * M_TOK + row;
+                            src[tg][i] = (row < M_TOK && ti < ntok) ? p.x + (int64_t) p.ids_src1[jp + ti] * p.x_row + pc * 8 : nullptr;
                         }
                     }
-                } else if (q >= 2) {
+                    for (int si = 0; si < total; si++) {
+                        const int tile = si / ng, tg = si - tile * ng;
+                        const int kcol = ((tile >> 3) / Q * 8 + (tile & 7)) * 64;
+                        const uint32_t vs = vv + (uint32_t) si, slot = vs % SLOTS, use = vs / SLOTS;
+                        if (use >= 1) { wait_on(x_free + slot, (use - 1) & 1, failed); }
+                        const uint32_t dst0 = smem_u32(xbuf + slot * X_SLOT_BYTES) + (uint32_t) r0 * 128;
 #pragma unroll
-                    for (int i = 0; i < 32; i++) { xchg[(c0 + i) * 64 + (m - 64)] = __uint_as_float(v[i]); }
+                        for (int g2 = 0; g2 < G; g2++) {
+                            if (g2 == tg) {
+#pragma unroll
+                                for (int i = 0; i < RMAX; i++) {
+                                    const int row = r0 + i * RSTEP;
+                                    if (src[g2][i]) { cp_async16(dst0 + i * RSTEP * 128 + ((pc ^ (row & 7)) << 4), src[g2][i] + kcol); }
+                                }
+                            }
+                        }
+                        cp_async_arrive(x_full + slot); // arrives once this thread's copies so far have landed
+                    }
+                } else if (lane == 0) {
+                    // ---- MMA issue
+                    for (int si = 0; si < total; si++) {
+                        const int tile = si / ng, tg = si - tile * ng, kb = tile & 7, cq = tile >> 3, c = cq / Q, q = cq - c * Q;
+                        const bool last_of_tile = kb == 7 && tg == ng - 1;
+                        const uint32_t b = n & 1;
+                        const uint32_t vs = vv + (uint32_t) si, slot = vs % SLOTS, use = vs / SLOTS;
+                        if (kb == 0 && tg == 0) { wait_on(w_full + b, (n >> 1) & 1, failed); }
+                        wait_on(x_full + slot, use & 1, failed);
+                        if (!*failed) {
+                            proxy_fence(); // the copies (generic proxy) before the tensor core's reads (async proxy)
+                            tc_fence_after();
+                            const uint32_t a0 = smem_u32(xbuf + slot * X_SLOT_BYTES);
+                            const uint32_t b0 = smem_u32(wbuf + b * W_TILE_BYTES + kb * W_KTILE_BYTES);
+                            const uint32_t d = tmem + (uint32_t) ((tg * Q + q) * N_TILE);
+#pragma unroll
+                            for (int s2 = 0; s2 < 4; s2++) {
+                                umma_bf16(d, tile_desc(a0 + s2 * 32), tile_desc(b0 + s2 * 32), INSTR_DESC, (c | kb | s2) != 0);
+                            }
+                        }
+                        umma_commit(x_free + slot);
+                        if (last_of_tile) { umma_commit(w_empty + b); n++; }
+                        if (si == total - 1) { umma_commit(acc_done); }
+                    }
                 }
-                if (GLU) {
-                    // gate warps wait for the matching up warps (same column group): named barrier per column group
-                    asm volatile("bar.sync %0, 128;" ::"r"(1 + cg) : "memory");
-                    if (q < 2) {
-                        const int64_t row = (int64_t) mb * ROWS_OUT + m;
+                if (!mma_warp || lane != 0) { n += TILES; } // the issuing thread counted its tiles itself
+                vv += (uint32_t) total;
+                __syncwarp();
+                // ---- epilogue: TMEM -> registers -> dst
+                wait_on(acc_done, passes & 1, failed);
+                passes++;
+                tc_fence_after();
+                for (int tg = 0; tg < ng; tg++) {
+                    const int64_t drow = my_dst[tg];
+#pragma unroll 1
+                    for (int q = 0; q < Q; q++) {
+                        __syncwarp(); // the TMEM loads are warp-wide: rejoin the lanes that skipped the stores
+                        const uint32_t taddr = tmem + ((uint32_t) (32 * hw) << 16) + (uint32_t) ((tg * Q + q) * N_TILE);
+                        uint32_t v0[32], v1[32];
+                        tmem_ld32(taddr, v0);
+                        tmem_ld32(taddr + 32, v1);
+                        if (drow < 0 || *failed) { continue; }
+                        const int64_t at0 = drow * p.dst_col + (int64_t) mb * ROWS_OUT + q * SUB;
+                        if (GLU) { // v0: gate rows of units 0..7, v1: the matching up rows
 #pragma unroll
-                        for (int i = 0; i < 32; i++) {
-                            if (c0 + i < ntok) {
-                                const float gte = __uint_as_float(v[i]), up = xchg[(c0 + i) * 64 + m];
-                                const float r = silu_f(gte) * up;
-                                const int64_t at = (int64_t) tok_dst[c0 + i] * p.dst_col + row;
-                                if (p.dst_bf16) { ((bf16 *) p.dst)[at] = __float2bfloat16_rn(r); } else { ((float *) p.dst)[at] = r; }
+                            for (int u = 0; u < 8; u++) {
+                                float r4[4];
+#pragma unroll
+                                for (int r = 0; r < 4; r++) { r4[r] = silu_f(__uint_as_float(v0[u * 4 + r])) * __uint_as_float(v1[u * 4 + r]); }
+                                store4(p, at0 + u * R, r4[0], r4[1], r4[2], r4[3]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int u = 0; u < 8; u++) {
+                                store4(p, at0 + u * R, __uint_as_float(v0[u * 4]), __uint_as_float(v0[u * 4 + 1]),
+                                       __uint_as_float(v0[u * 4 + 2]), __uint_as_float(v0[u * 4 + 3]));
+                                store4(p, at0 + (u + 8) * R, __uint_as_float(v1[u * 4]), __uint_as_float(v1[u * 4 + 1]),
+                                       __uint_as_float(v1[u * 4 + 2]), __uint_as_float(v1[u * 4 + 3]));
                             }
                         }
                     }
-                    asm volatile("bar.sync %0, 128;" ::"r"(1 + cg) : "memory");
                 }
+                tc_fence_before();
+                helper_bar(); // the accumulators are read: the next pass may overwrite them
             }
-            tc_fence_before();
-            __syncthreads(); // accumulators read, exchange area free: the next pass may overwrite both
+        }
+        cp_async_wait_all();
+        if (mma_warp && lane == 0 && *failed) {
+            // MMAs may still be in flight: wait (bounded) until the tensor core has drained before TMEM is freed
+            umma_commit(drained);
+            mbar_poll(smem_u32(drained), 0);
+            atomicOr(&g_prefill_fault, 1u);
         }
     }
-    if (!ok && tid == 0) { atomicOr(&g_prefill_fault, 1u); }
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) { tmem_free(tmem, NT); }
+    if (warp == 0) { tmem_free(tmem, TMEM_COLS); }
 }
 
 PairView view_of(const bf16n_weight & w) {
@@ -302,16 +390,22 @@ PairView view_of(const bf16n_weight & w) {
             (const uint16_t *) (w.aux + w.off_c), (const uint32_t *) (w.aux + w.off_d)};
 }
 
-template <bool GLU, int NT, int STAGES> constexpr size_t smem_bytes() {
-    return A_SLAB_BYTES + STAGES * NT * 128 + (GLU ? 2 : 1) * 4 * HP_MAX_PAIRS + 2 * NT * 4 + STAGES * 8 + 16 + 1024;
+template <bool GLU, int SLOTS> constexpr size_t smem_bytes() {
+    return 2 * W_TILE_BYTES + SLOTS * X_SLOT_BYTES + (GLU ? 2 : 1) * 4 * HP_MAX_PAIRS + 256 + 1024;
 }
+
+constexpr int G_TOK = 2;                      // token groups per pass
+constexpr int SLOTS_GLU = 3, SLOTS_ONE = 4;   // what fits beside two tables / one table
 
 } // namespace
 
 void prefill_init() {
-    cuda_ok(cudaFuncSetAttribute(k_prefill<4, 8, true, true, 128, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes<true, 128, 4>()), "k_prefill glu");
-    cuda_ok(cudaFuncSetAttribute(k_prefill<4, 8, true, false, 256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes<false, 256, 2>()), "k_prefill gate");
-    cuda_ok(cudaFuncSetAttribute(k_prefill<1, 16, false, false, 256, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem_bytes<false, 256, 2>()), "k_prefill down");
+    cuda_ok(cudaFuncSetAttribute(k_prefill<4, 8, true, true, G_TOK, SLOTS_GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int) smem_bytes<true, SLOTS_GLU>()), "k_prefill glu");
+    cuda_ok(cudaFuncSetAttribute(k_prefill<4, 8, true, false, G_TOK, SLOTS_ONE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int) smem_bytes<false, SLOTS_ONE>()), "k_prefill gate");
+    cuda_ok(cudaFuncSetAttribute(k_prefill<1, 16, false, false, G_TOK, SLOTS_ONE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int) smem_bytes<false, SLOTS_ONE>()), "k_prefill down");
 }
 
 bool prefill_supported(const bf16n_weight & w, const bf16n_weight * up) {
@@ -332,18 +426,19 @@ void prefill_mm_ids(const bf16n_weight & w, const bf16n_weight * up, const void 
     a.x = (const bf16 *) x_bf16; a.x_row = x_row;
     a.ids_src1 = ids_src1; a.ids_dst = ids_dst; a.bounds = bounds;
     a.dst = (char *) dst; a.dst_col = dst_col; a.dst_bf16 = dst_bf16;
+    a.vec_ok = ((uintptr_t) dst % 16) == 0 && dst_col % 4 == 0;
     a.n_experts = n_experts;
     a.rows_per_expert = w.rows / n_experts;
     require(((uintptr_t) x_bf16 % 16) == 0 && (x_row * 2) % 16 == 0, "batched activations must be 16-byte aligned rows");
-    const int rows_out = up ? M_TILE / 2 : M_TILE;
+    const int rows_out = (up ? DEC_WARPS / 2 : DEC_WARPS) * w.R;
     require(a.rows_per_expert % rows_out == 0, "rows per expert must be a multiple of the batched kernel's row block");
     const unsigned grid = (unsigned) std::min<int64_t>(device_info().sms, (int64_t) n_experts * (a.rows_per_expert / rows_out));
     if (up) {
-        k_prefill<4, 8, true, true, 128, 4><<<grid, NTHREADS, smem_bytes<true, 128, 4>(), st>>>(a);
+        k_prefill<4, 8, true, true, G_TOK, SLOTS_GLU><<<grid, NTHREADS, smem_bytes<true, SLOTS_GLU>(), st>>>(a);
     } else if (w.K == 2048) {
-        k_prefill<4, 8, true, false, 256, 2><<<grid, NTHREADS, smem_bytes<false, 256, 2>(), st>>>(a);
+        k_prefill<4, 8, true, false, G_TOK, SLOTS_ONE><<<grid, NTHREADS, smem_bytes<false, SLOTS_ONE>(), st>>>(a);
     } else {
-        k_prefill<1, 16, false, false, 256, 2><<<grid, NTHREADS, smem_bytes<false, 256, 2>(), st>>>(a);
+        k_prefill<1, 16, false, false, G_TOK, SLOTS_ONE><<<grid, NTHREADS, smem_bytes<false, SLOTS_ONE>(), st>>>(a);
     }
     check_launch();
 }
