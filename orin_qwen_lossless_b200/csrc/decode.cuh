@@ -160,30 +160,47 @@ struct PairReader {
     }
 };
 
-// The same reader with four words kept loaded ahead of the buffer: a lane crosses into a new 128-byte line every 32 words and the 32 lanes of a
-// warp do so at different times, so without the queue nearly every refill of a warp would wait for some lane's miss.
-struct DeepPairReader {
-    const uint32_t * next;
+// The same reader fed by 16-byte loads: a lane's stream is read as aligned groups of four words (one load request per
+// group instead of one per word, which matters when the L1 cache is too small to keep every lane's line). `q0..q3`
+// hold the `cnt` words not yet shifted into `buf`, oldest first; `pre` is the group after them, already loaded.
+struct WidePairReader {
+    const uint4 * next;
     uint64_t buf;
-    uint32_t q0, q1, q2, q3; // the words after the buffered ones, oldest first
-    int have;
+    uint32_t q0, q1, q2, q3;
+    uint4 pre;
+    int have, cnt;
 
+    __device__ __forceinline__ uint32_t pop() {
+        const uint32_t w = q0;
+        q0 = q1; q1 = q2; q2 = q3;
+        if (--cnt == 0) {
+            q0 = pre.x; q1 = pre.y; q2 = pre.z; q3 = pre.w;
+            cnt = 4;
+            pre = __ldg(next++);
+        }
+        return w;
+    }
     __device__ __forceinline__ void open(const PairView & w, int64_t unit, int lane) {
-        next = w.stream + (__ldg(w.ubase + unit) + __ldg(w.lrel + unit * 32 + lane));
-        buf = (uint64_t) __ldg(next) << 32 | __ldg(next + 1);
-        q0 = __ldg(next + 2); q1 = __ldg(next + 3); q2 = __ldg(next + 4); q3 = __ldg(next + 5);
-        next += 6;
+        const uint32_t * first = w.stream + (__ldg(w.ubase + unit) + __ldg(w.lrel + unit * 32 + lane));
+        const int skip = (int) (((uintptr_t) first >> 2) & 3); // words of the first aligned group before the stream
+        next = (const uint4 *) (first - skip);
+        const uint4 a = __ldg(next);
+        pre = __ldg(next + 1);
+        next += 2;
+        q0 = a.x; q1 = a.y; q2 = a.z; q3 = a.w;
+        if (skip & 1) { q0 = q1; q1 = q2; q2 = q3; }
+        if (skip & 2) { q0 = q2; q1 = q3; }
+        cnt = 4 - skip;
+        const uint32_t hi = pop();
+        buf = (uint64_t) hi << 32 | pop();
         have = 64;
     }
     __device__ __forceinline__ void top_up() {
         if (have <= 32) {
-            buf |= (uint64_t) q0 << (32 - have);
+            buf |= (uint64_t) pop() << (32 - have);
             have += 32;
-            q0 = q1; q1 = q2; q2 = q3;
-            q3 = __ldg(next++);
         }
     }
-    // next table entry (the two exponents in place + code length); lut in shared memory
     __device__ __forceinline__ uint32_t take(const uint32_t * lut) {
         const uint32_t e = lut[(uint32_t) (buf >> (64 - HP_LMAX))];
         const int n = e & 31;

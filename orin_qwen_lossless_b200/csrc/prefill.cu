@@ -116,6 +116,10 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void * src) {
 __device__ __forceinline__ void cp_async_arrive(uint64_t * bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// asks the L2 cache for `bytes` (a multiple of 16) at a 16-byte aligned address; nothing waits for it
+__device__ __forceinline__ void bulk_prefetch_l2(const void * src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 // shared-memory matrix descriptor of a K-major, 128-byte-swizzled tile: rows 128 bytes apart, 8-row groups 1024 bytes
@@ -123,8 +127,11 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 __device__ __forceinline__ uint64_t tile_desc(uint32_t addr) {
     return (uint64_t) ((addr >> 4) & 0x3FFFu) | (uint64_t) 1 << 16 | (uint64_t) (1024 >> 4) << 32 | (uint64_t) 1 << 46 | (uint64_t) 2 << 61;
 }
-// kind::f16 instruction descriptor: FP32 accumulate, BF16 A and B, both K-major, M = 128, N = 64
-constexpr uint32_t INSTR_DESC = 1u << 4 | 1u << 7 | 1u << 10 | (uint32_t) (N_TILE >> 3) << 17 | (uint32_t) (M_TOK >> 4) << 24;
+// kind::f16 instruction descriptor: FP32 accumulate, BF16 A and B, both K-major, N = 64, M = 128 or 64. With M = 64 the
+// accumulator row m lives in TMEM lane 32 * (m / 16) + m % 16 (measured: the other lanes are not written).
+__host__ __device__ constexpr uint32_t instr_desc(int m) {
+    return 1u << 4 | 1u << 7 | 1u << 10 | (uint32_t) (N_TILE >> 3) << 17 | (uint32_t) (m >> 4) << 24;
+}
 
 struct PrefillArgs {
     PairView w0, w1;                    // w1: the up matrix (GLU)
@@ -214,9 +221,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const PrefillArgs p) {
             const int e = item / m_blocks, mb = item - e * m_blocks;
             const int j0 = p.bounds[e], j1 = p.bounds[e + 1];
             const int64_t gu = (int64_t) e * units_per_expert + (int64_t) mb * UNITS_PER_MAT + uw;
+            // the unit this warp decodes next: its plane and streams are requested into L2 now, a whole item ahead, so that
+            // the short read-ahead of the stream reader only has to cover L2 latency
+            int64_t gun = -1;
+            uint32_t ns0 = 0, ns1 = 0;
+            if (j1 > j0 && item + (int) gridDim.x < n_items) {
+                const int e2 = (item + (int) gridDim.x) / m_blocks, mb2 = item + (int) gridDim.x - e2 * m_blocks;
+                if (p.bounds[e2 + 1] > p.bounds[e2]) {
+                    gun = (int64_t) e2 * units_per_expert + (int64_t) mb2 * UNITS_PER_MAT + uw;
+                    if (lane == 0) { bulk_prefetch_l2(wv.plane + gun * R * K, R * K); }
+                    ns0 = __ldg(wv.ubase + gun);
+                    ns1 = gun + 1 < (int64_t) p.n_experts * units_per_expert ? __ldg(wv.ubase + gun + 1) : ns0; // the very last unit: skipped
+                }
+            }
             for (int jp = j0; jp < j1; jp += G * M_TOK) {
                 if (*failed) { n += TILES; continue; }
-                DeepPairReader rd;
+                WidePairReader rd;
                 rd.open(wv, gu, lane);
                 const uint8_t * pl = wv.plane + gu * R * K + 16 * lane;
                 uint4 cur[SUB];
@@ -249,6 +269,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const PrefillArgs p) {
                     __syncwarp();
                     if (lane == 0) { mbar_arrive(smem_u32(w_full + b)); }
                     n++;
+                    if (t == 0 && jp == j0 && gun >= 0 && lane == 0) { // by now the two offsets have arrived
+                        // codes are at most 12 bits per pair: a unit's streams hold at most R*K*3/16 words plus one partial word per lane
+                        const uint32_t first = ns0 & ~3u, words = min(ns1 - first, (uint32_t) (R * K * 3 / 16 + 64));
+                        if (ns1 > ns0) { bulk_prefetch_l2(wv.stream + first, ((words + 3u) & ~3u) * 4u); }
+                    }
                     if (t + 1 < TILES) {
 #pragma unroll
                         for (int r = 0; r < SUB; r++) { cur[r] = nxt[r]; }
@@ -268,11 +293,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const PrefillArgs p) {
             const int j0 = p.bounds[e], j1 = p.bounds[e + 1];
             for (int jp = j0; jp < j1; jp += G * M_TOK) {
                 const int ntok = min(G * M_TOK, j1 - jp), ng = (ntok + M_TOK - 1) / M_TOK;
-                const int total = TILES * 8 * ng; // slots of the pass: for each weight tile, for each k-tile, each token group
-                int64_t my_dst[G];
+                // up to 64 tokens: M = 64 and a slot holds two k-tiles of 64 rows, so that the ring stays densely filled
+                const bool small = ntok <= M_TOK / 2;
+                const int kslots = small ? 4 : 8;        // slots per weight tile and token group
+                const int total = TILES * kslots * ng;   // slots of the pass: for each weight tile, each k position, each token group
+                int64_t my_dst[G];                       // output row of the token whose accumulators this thread reads
 #pragma unroll
                 for (int tg = 0; tg < G; tg++) {
-                    const int ti = tg * M_TOK + ht;
+                    const int ti = small ? (lane < 16 ? 16 * hw + lane : ntok) : tg * M_TOK + ht;
                     my_dst[tg] = ti < ntok ? (int64_t) p.ids_dst[jp + ti] : -1;
                 }
                 if (!mma_warp) {
@@ -289,8 +317,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const PrefillArgs p) {
                         }
                     }
                     for (int si = 0; si < total; si++) {
-                        const int tile = si / ng, tg = si - tile * ng;
-                        const int kcol = ((tile >> 3) / Q * 8 + (tile & 7)) * 64;
+                        const int tile = si / ng, tg = si - tile * ng, kpos = tile % kslots, c = tile / kslots / Q;
+                        const int kcol = (c * 8 + (small ? 2 * kpos : kpos)) * 64;
                         const uint32_t vs = vv + (uint32_t) si, slot = vs % SLOTS, use = vs / SLOTS;
                         if (use >= 1) { wait_on(x_free + slot, (use - 1) & 1, failed); }
                         const uint32_t dst0 = smem_u32(xbuf + slot * X_SLOT_BYTES) + (uint32_t) r0 * 128;
@@ -300,7 +328,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const PrefillArgs p) {
 #pragma unroll
                                 for (int i = 0; i < RMAX; i++) {
                                     const int row = r0 + i * RSTEP;
-                                    if (src[g2][i]) { cp_async16(dst0 + i * RSTEP * 128 + ((pc ^ (row & 7)) << 4), src[g2][i] + kcol); }
+                                    if (src[g2][i]) {
+                                        const uint32_t at = dst0 + i * RSTEP * 128 + ((pc ^ (row & 7)) << 4);
+                                        cp_async16(at, src[g2][i] + kcol);
+                                        if (small) { cp_async16(at + X_SLOT_BYTES / 2, src[g2][i] + kcol + 64); } // rows < 64: second k-tile
+                                    }
                                 }
                             }
                         }
@@ -309,21 +341,25 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const PrefillArgs p) {
                 } else if (lane == 0) {
                     // ---- MMA issue
                     for (int si = 0; si < total; si++) {
-                        const int tile = si / ng, tg = si - tile * ng, kb = tile & 7, cq = tile >> 3, c = cq / Q, q = cq - c * Q;
-                        const bool last_of_tile = kb == 7 && tg == ng - 1;
+                        const int tile = si / ng, tg = si - tile * ng, kpos = tile % kslots, cq = tile / kslots, c = cq / Q, q = cq - c * Q;
+                        const bool last_of_tile = kpos == kslots - 1 && tg == ng - 1;
                         const uint32_t b = n & 1;
                         const uint32_t vs = vv + (uint32_t) si, slot = vs % SLOTS, use = vs / SLOTS;
-                        if (kb == 0 && tg == 0) { wait_on(w_full + b, (n >> 1) & 1, failed); }
+                        if (kpos == 0 && tg == 0) { wait_on(w_full + b, (n >> 1) & 1, failed); }
                         wait_on(x_full + slot, use & 1, failed);
                         if (!*failed) {
                             proxy_fence(); // the copies (generic proxy) before the tensor core's reads (async proxy)
                             tc_fence_after();
-                            const uint32_t a0 = smem_u32(xbuf + slot * X_SLOT_BYTES);
-                            const uint32_t b0 = smem_u32(wbuf + b * W_TILE_BYTES + kb * W_KTILE_BYTES);
                             const uint32_t d = tmem + (uint32_t) ((tg * Q + q) * N_TILE);
+                            const uint32_t idesc = small ? instr_desc(M_TOK / 2) : instr_desc(M_TOK);
+                            for (int j = 0; j < (small ? 2 : 1); j++) {
+                                const int kb = small ? 2 * kpos + j : kpos;
+                                const uint32_t a0 = smem_u32(xbuf + slot * X_SLOT_BYTES + j * (X_SLOT_BYTES / 2));
+                                const uint32_t b0 = smem_u32(wbuf + b * W_TILE_BYTES + kb * W_KTILE_BYTES);
 #pragma unroll
-                            for (int s2 = 0; s2 < 4; s2++) {
-                                umma_bf16(d, tile_desc(a0 + s2 * 32), tile_desc(b0 + s2 * 32), INSTR_DESC, (c | kb | s2) != 0);
+                                for (int s2 = 0; s2 < 4; s2++) {
+                                    umma_bf16(d, tile_desc(a0 + s2 * 32), tile_desc(b0 + s2 * 32), idesc, (c | kb | s2) != 0);
+                                }
                             }
                         }
                         umma_commit(x_free + slot);
