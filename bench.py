@@ -393,12 +393,20 @@ def run_moe_decode(args):
         ysh = torch.empty(T, 2048, device=dev)
         a = torch.empty(T, 512, device=dev)
 
+        side = torch.cuda.Stream()
+
         def step():
+            # the shared expert does not depend on the routed experts: it runs on a second stream (a parallel branch of
+            # the captured graph) and joins before the final add
             for i in range(steps):
+                main = torch.cuda.current_stream()
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    ops._mmv_common(xs[i], sh_gu, None, 0, False, True, True, a)   # shared expert: merged gate|up GLU
+                    ops.mmv(a, sh_down, out=ysh)
                 ops.moe_decode(xs[i], gate, up, down, E, k, router_logits=logits[i], topk_weights=wts[i], topk_ids=ids[i],
                                scratch=scratch, out=y)
-                ops._mmv_common(xs[i], sh_gu, None, 0, False, True, True, a)   # shared expert: merged gate|up GLU
-                ops.mmv(a, sh_down, out=ysh)
+                main.wait_stream(side)
                 y.add_(ysh)
 
         us = _time_graph(torch, step, max(args.steps // 16, 5), inner=steps)

@@ -23,6 +23,28 @@ inline void cuda_ok(cudaError_t e, const char * what) {
 }
 inline void check_launch() { cuda_ok(cudaGetLastError(), "kernel launch"); }
 
+#ifdef __CUDACC__
+// Launch of a kernel that may start while the kernel before it on the stream is still draining (programmatic dependent
+// launch): such a kernel calls grid_dependency_wait() before it touches anything an earlier kernel wrote or still reads,
+// and does only independent work (tables, barriers) above that line. Works under stream capture as well.
+template <typename... KArgs, typename... Args>
+void launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t shm, cudaStream_t st, Args &&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = shm; cfg.stream = st;
+    cudaLaunchAttribute attr = {};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr; cfg.numAttrs = 1;
+    cuda_ok(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...), "kernel launch");
+}
+// Blocks until every kernel this one depends on has completed and its writes are visible; then lets the next kernel on
+// the stream begin its own prologue.
+__device__ __forceinline__ void grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+#endif
+
 // gemv.cu
 void gemv_init();
 void gemv(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st, bool multi_col);

@@ -16,6 +16,7 @@ constexpr int TOPK_MAX_PER_LANE = 32;
 
 __global__ void __launch_bounds__(32) k_topk(const float * __restrict__ logits, int n_experts, int k, int32_t * __restrict__ ids,
                                              float * __restrict__ weights) {
+    grid_dependency_wait(); // the logits come from an earlier kernel
     const int t = blockIdx.x, lane = threadIdx.x;
     const float * z = logits + (int64_t) t * n_experts;
     float v[TOPK_MAX_PER_LANE];
@@ -151,8 +152,7 @@ void moe_topk(const float * logits, int n_tok, int n_experts, int k, int32_t * i
     require(n_tok >= 0 && n_experts > 0 && n_experts <= 32 * TOPK_MAX_PER_LANE, "moe_topk: 1..1024 experts");
     require(k > 0 && k <= 32 && k <= n_experts, "moe_topk: k must be in 1..min(32, n_experts)");
     if (n_tok == 0) { return; }
-    k_topk<<<n_tok, 32, 0, st>>>(logits, n_experts, k, ids, weights);
-    check_launch();
+    launch_chained(k_topk, dim3(n_tok), dim3(32), 0, st, logits, n_experts, k, ids, weights);
 }
 
 void moe_combine(const float * ys, const void * w, bool w_bf16, void * y, bool y_bf16, int n_tok, int n_used, int64_t n,

@@ -15,6 +15,7 @@
 #include "staged.cuh"
 #include "launch.h"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace b16 {
@@ -38,16 +39,25 @@ struct ExpertCols {
     uint32_t cap_bytes;
 };
 
-template <int C, int R, bool CM, typename TX, bool GLU_IN>
+template <int C, int R, bool CM, typename TX, bool GLU_IN, bool PLANE_STAGED>
 __global__ void __launch_bounds__(256) k_expert_units(const ExpertMat m0, const ExpertMat m1, const ExpertCols p, const Opaque k) {
     constexpr int K = C * CHUNK;
     extern __shared__ __align__(128) unsigned char smem[];
     uint32_t * lut = (uint32_t *) smem;
     uint64_t * bars = (uint64_t *) (smem + 4 * HP_MAX_PAIRS);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
-    unsigned char * buf = smem + 4 * HP_MAX_PAIRS + 128 + (size_t) warp * p.cap_bytes;
+    constexpr uint32_t PLANE_BYTES = PLANE_STAGED ? (uint32_t) (R * K) : 0u;   // the unit's sign|mantissa bytes, staged with its streams
+    unsigned char * buf = smem + 4 * HP_MAX_PAIRS + 128 + (size_t) warp * (p.cap_bytes + PLANE_BYTES);
+    const unsigned char * plane_s = buf + p.cap_bytes;
     const uint32_t bar = smem_u32(bars + warp);
     const ExpertMat & m = blockIdx.z ? m1 : m0;
+
+    // independent prologue: the table and the barrier do not depend on earlier kernels
+    for (int i = threadIdx.x; i < HP_MAX_PAIRS / 4; i += blockDim.x) { ((uint4 *) lut)[i] = __ldg((const uint4 *) m.v.lut + i); }
+    if (lane == 0) { mbar_init(bar, 1); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncthreads();
+    grid_dependency_wait(); // expert ids, activations and the output buffers belong to earlier kernels up to here
 
     const int col = blockIdx.y, t = col / p.n_used, s = col - t * p.n_used;
     const int e = *(const int32_t *) (p.ids + t * p.ids_s1 + s * p.ids_s0) - p.e_lo;
@@ -58,10 +68,6 @@ __global__ void __launch_bounds__(256) k_expert_units(const ExpertMat m0, const 
         if (u < units && lane < R) { y[u * R + lane] = 0.f; }
         return;
     }
-    for (int i = threadIdx.x; i < HP_MAX_PAIRS / 4; i += blockDim.x) { ((uint4 *) lut)[i] = __ldg((const uint4 *) m.v.lut + i); }
-    if (lane == 0) { mbar_init(bar, 1); }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    __syncthreads();
     if (u >= units) { return; }
 
     const int64_t gu = (int64_t) e * units + u;
@@ -69,9 +75,11 @@ __global__ void __launch_bounds__(256) k_expert_units(const ExpertMat m0, const 
     const uint32_t w1 = gu + 1 < (int64_t) m.hdr->n_a ? __ldg(m.v.ubase + gu + 1) : (uint32_t) m.hdr->n_b;
     const uint32_t start = w0 & ~3u, bytes = ((w1 - start + 4u + 3u) & ~3u) * 4u;
     const bool staged = bytes <= p.cap_bytes;
+    const bool plane_staged = PLANE_STAGED && staged;
     if (staged && lane == 0) {
-        mbar_expect_tx(bar, bytes);
+        mbar_expect_tx(bar, bytes + (plane_staged ? PLANE_BYTES : 0u));
         bulk_g2s(smem_u32(buf), m.v.stream + start, bytes, bar);
+        if (plane_staged) { bulk_g2s(smem_u32(plane_s), m.v.plane + gu * R * K, PLANE_BYTES, bar); }
     }
     const uint32_t my = w0 - start + __ldg(m.v.lrel + gu * 32 + lane);
 
@@ -92,6 +100,11 @@ __global__ void __launch_bounds__(256) k_expert_units(const ExpertMat m0, const 
         }
     }
     const uint8_t * pl = m.v.plane + gu * R * K + 16 * lane;
+    // one lane's 16 bytes of a row-chunk: from the staged copy (after the wait below) or straight from global memory
+    auto plane16 = [&](int64_t off) -> uint4 {
+        if (plane_staged) { return *(const uint4 *) (plane_s + 16 * lane + off); }
+        return ld_stream16(pl + off);
+    };
 
     auto rows = [&](auto & rd, uint32_t lut_arg) {
         float mine = 0.f;
@@ -103,7 +116,7 @@ __global__ void __launch_bounds__(256) k_expert_units(const ExpertMat m0, const 
             for (int c = 0; c < C; c++) {
                 uint4 sm[R];
 #pragma unroll
-                for (int rr = 0; rr < R; rr++) { sm[rr] = ld_stream16(pl + (c * R + rr) * CHUNK); }
+                for (int rr = 0; rr < R; rr++) { sm[rr] = plane16((c * R + rr) * CHUNK); }
 #pragma unroll
                 for (int rr = 0; rr < R; rr++) {
                     uint32_t en[8], wv[8];
@@ -131,7 +144,7 @@ __global__ void __launch_bounds__(256) k_expert_units(const ExpertMat m0, const 
                 float a[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int c = 0; c < C; c++) {
-                    const uint4 sm = ld_stream16(pl + rr * K + c * CHUNK);
+                    const uint4 sm = plane16(rr * K + c * CHUNK);
                     uint32_t en[8], wv[8];
                     rd.take8(lut_arg, k, en);
                     assemble8(sm, en, wv);
@@ -173,6 +186,7 @@ __global__ void __launch_bounds__(256) k_expert_units(const ExpertMat m0, const 
 // y[t, i] = sum over slots, in slot order, of w[t, k] * ys[t, k, i]
 __global__ void k_combine_f32(const float * __restrict__ ys, const float * __restrict__ w, char * __restrict__ y, bool y_bf16, int n_used,
                               int64_t n) {
+    grid_dependency_wait();
     const int t = blockIdx.y;
     const OutVec out = {y + (int64_t) t * n * (y_bf16 ? 2 : 4), y_bf16};
     for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) {
@@ -189,22 +203,35 @@ ExpertMat expert_mat(const bf16n_weight & w, float * y) { return {pair_view(w), 
 
 uint32_t unit_cap(const bf16n_weight & w) { return (uint32_t) ((w.R * w.K * 3 / 8 + 64 + 15) & ~15ll); }
 
+int g_plane_staged_warps_per_sm = 8; // stage the plane too while the launch has at most this many warps per SM
+
 template <int C, int R, bool CM, typename TX, bool GLU_IN>
 void launch_units(const ExpertMat & m0, const ExpertMat & m1, int n_mats, const ExpertCols & p, int ncols, cudaStream_t st) {
     const int64_t units = p.rows_per_expert / R;
+    const int64_t all_warps = ncols * n_mats * units;
     // few tokens: small blocks so that the units of one column spread over many SMs
-    const int warps = ncols * n_mats * units >= (int64_t) device_info().sms * 16 ? 8 : 4;
+    const int warps = all_warps >= (int64_t) device_info().sms * 16 ? 8 : 4;
+    // When the launch leaves most of an SM idle anyway, every warp also stages its unit's plane bytes, so that it waits
+    // for memory once instead of once per chunk; with more warps per SM the shared memory is better spent on residency.
+    const bool plane = all_warps <= (int64_t) device_info().sms * g_plane_staged_warps_per_sm;
     const dim3 grid((unsigned) ((units + warps - 1) / warps), (unsigned) ncols, (unsigned) n_mats);
-    const size_t shm = 4 * HP_MAX_PAIRS + 128 + (size_t) warps * p.cap_bytes;
+    const size_t shm = 4 * HP_MAX_PAIRS + 128 + (size_t) warps * (p.cap_bytes + (plane ? R * C * CHUNK : 0));
     const Opaque k = {1u, 4u, ~0u, 32u};
     static bool attr_done = false; // set once per instantiation, during bf16n_init's warm-up call (before any capture)
     if (!attr_done) {
-        cuda_ok(cudaFuncSetAttribute(k_expert_units<C, R, CM, TX, GLU_IN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024),
+        cuda_ok(cudaFuncSetAttribute(k_expert_units<C, R, CM, TX, GLU_IN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024),
+                "k_expert_units attribute");
+        cuda_ok(cudaFuncSetAttribute(k_expert_units<C, R, CM, TX, GLU_IN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024),
                 "k_expert_units attribute");
         attr_done = true;
     }
     if (ncols == 0) { return; }
-    k_expert_units<C, R, CM, TX, GLU_IN><<<grid, warps * 32, shm, st>>>(m0, m1, p, k);
+    if (plane && shm <= 128 * 1024) {
+        launch_chained(k_expert_units<C, R, CM, TX, GLU_IN, true>, grid, dim3(warps * 32), shm, st, m0, m1, p, k);
+    } else {
+        launch_chained(k_expert_units<C, R, CM, TX, GLU_IN, false>, grid, dim3(warps * 32), 4 * HP_MAX_PAIRS + 128 + (size_t) warps * p.cap_bytes, st,
+                       m0, m1, p, k);
+    }
     check_launch();
 }
 
@@ -225,6 +252,7 @@ bool moe_decode_supported(const bf16n_weight & gate, const bf16n_weight & up, co
 
 void moe_decode_init() {
     // instantiate and set the shared-memory attribute of every variant outside of any stream capture
+    if (const char * e = getenv("BF16N_PLANE_STAGED_WARPS")) { g_plane_staged_warps_per_sm = atoi(e); } // tuning knob, read once
     ExpertMat none = {};
     ExpertCols p = {};
     p.rows_per_expert = 16; p.cap_bytes = 16;
@@ -256,7 +284,7 @@ void moe_decode(const bf16n_weight & gate, const bf16n_weight & up, const bf16n_
     q.rows_per_expert = H; q.cap_bytes = unit_cap(down);
     launch_units<1, 16, false, float, true>(expert_mat(down, ys), expert_mat(down, ys), 1, q, ncols, st);
     const dim3 grid((unsigned) std::min<int64_t>((H + 255) / 256, 64), (unsigned) n_tok);
-    k_combine_f32<<<grid, 256, 0, st>>>(ys, weights, (char *) y, y_bf16, n_used, H);
+    launch_chained(k_combine_f32, grid, dim3(256), 0, st, ys, weights, (char *) y, y_bf16, n_used, H);
     check_launch();
 }
 
