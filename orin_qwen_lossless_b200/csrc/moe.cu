@@ -14,17 +14,17 @@ using namespace dev;
 // ones, which equals softmax followed by renormalisation. Lane l holds experts l, l+32, ...; up to 1024 experts.
 constexpr int TOPK_MAX_PER_LANE = 32;
 
+template <int PER> // experts per lane: the register array and every scan are this long
 __global__ void __launch_bounds__(32) k_topk(const float * __restrict__ logits, int n_experts, int k, int32_t * __restrict__ ids,
                                              float * __restrict__ weights) {
     grid_dependency_wait(); // the logits come from an earlier kernel
     const int t = blockIdx.x, lane = threadIdx.x;
     const float * z = logits + (int64_t) t * n_experts;
-    float v[TOPK_MAX_PER_LANE];
-    const int per = (n_experts + 31) / 32;
+    float v[PER];
 #pragma unroll
-    for (int i = 0; i < TOPK_MAX_PER_LANE; i++) {
+    for (int i = 0; i < PER; i++) {
         const int e = i * 32 + lane;
-        v[i] = (i < per && e < n_experts) ? z[e] : -INFINITY;
+        v[i] = e < n_experts ? z[e] : -INFINITY;
     }
     float zmax = 0.f, denom = 0.f;
     for (int s = 0; s < k; s++) {
@@ -32,8 +32,8 @@ __global__ void __launch_bounds__(32) k_topk(const float * __restrict__ logits, 
         float best = -INFINITY;
         int bi = 0x7fffffff;
 #pragma unroll
-        for (int i = 0; i < TOPK_MAX_PER_LANE; i++) {
-            if (i < per && v[i] > best) { best = v[i]; bi = i * 32 + lane; }
+        for (int i = 0; i < PER; i++) {
+            if (v[i] > best) { best = v[i]; bi = i * 32 + lane; }
         }
         // warp arg-max with the same tie rule
 #pragma unroll
@@ -51,7 +51,7 @@ __global__ void __launch_bounds__(32) k_topk(const float * __restrict__ logits, 
         }
         if ((bi & 31) == lane) { // retire the winner
 #pragma unroll
-            for (int i = 0; i < TOPK_MAX_PER_LANE; i++) {
+            for (int i = 0; i < PER; i++) {
                 if (i == (bi >> 5)) { v[i] = -INFINITY; }
             }
         }
@@ -152,7 +152,11 @@ void moe_topk(const float * logits, int n_tok, int n_experts, int k, int32_t * i
     require(n_tok >= 0 && n_experts > 0 && n_experts <= 32 * TOPK_MAX_PER_LANE, "moe_topk: 1..1024 experts");
     require(k > 0 && k <= 32 && k <= n_experts, "moe_topk: k must be in 1..min(32, n_experts)");
     if (n_tok == 0) { return; }
-    launch_chained(k_topk, dim3(n_tok), dim3(32), 0, st, logits, n_experts, k, ids, weights);
+    if (n_experts <= 256) {
+        launch_chained(k_topk<8>, dim3(n_tok), dim3(32), 0, st, logits, n_experts, k, ids, weights);
+    } else {
+        launch_chained(k_topk<TOPK_MAX_PER_LANE>, dim3(n_tok), dim3(32), 0, st, logits, n_experts, k, ids, weights);
+    }
 }
 
 void moe_combine(const float * ys, const void * w, bool w_bf16, void * y, bool y_bf16, int n_tok, int n_used, int64_t n,

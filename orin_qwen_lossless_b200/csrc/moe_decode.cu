@@ -81,6 +81,7 @@ __global__ void __launch_bounds__(256) k_expert_units(const ExpertMat m0, const 
         bulk_g2s(smem_u32(buf), m.v.stream + start, bytes, bar);
         if (plane_staged) { bulk_g2s(smem_u32(plane_s), m.v.plane + gu * R * K, PLANE_BYTES, bar); }
     }
+    if (!plane_staged && lane == 0) { bulk_prefetch_l2(m.v.plane + gu * R * K, (uint32_t) (R * K)); } // later chunks then hit L2
     const uint32_t my = w0 - start + __ldg(m.v.lrel + gu * 32 + lane);
 
     // this lane's activations, in registers (FP32 values; BF16 inputs are widened exactly)
