@@ -362,11 +362,34 @@ def run_small(args):
                       "frac_of_measured_hbm": nbytes / us / 1e3 / peak, "l2": "191 MB of weights per replay > L2"}), flush=True)
 
 
-def _moe_weights(ops, dev, n_experts):
-    gate = _enc(ops, n_experts * 512, 2048, 3, 8, True, 101, dev)
-    up = _enc(ops, n_experts * 512, 2048, 3, 8, True, 102, dev)
-    down = _enc(ops, n_experts * 2048, 512, 3, 16, False, 103, dev)
+def _moe_weights(ops, dev, n_experts, rank=0):
+    """Routed expert weights of one rank (every rank draws its own experts: seeds differ per rank)."""
+    gate = _enc(ops, n_experts * 512, 2048, 3, 8, True, 101 + 10 * rank, dev)
+    up = _enc(ops, n_experts * 512, 2048, 3, 8, True, 102 + 10 * rank, dev)
+    down = _enc(ops, n_experts * 2048, 512, 3, 16, False, 103 + 10 * rank, dev)
     return gate, up, down
+
+
+def _dist_setup(torch):
+    """(rank, world, device): one process per GPU under torchrun, NCCL process group when world > 1."""
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    return rank, world, dev
+
+
+def _max_over_ranks(torch, us, world, dev):
+    if world == 1:
+        return us
+    import torch.distributed as dist
+    t = torch.tensor([us], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
 
 
 def run_moe_decode(args):
@@ -374,19 +397,22 @@ def run_moe_decode(args):
     top-8 on the GPU, 1 / 2 / 4 tokens. A graph holds 16 steps with 16 different routings so that consecutive steps hit
     different experts (the 1.08 GB of expert weights do not fit L2; one step touches 34 MB per token)."""
     import torch
+    import torch.distributed as dist
     from orin_qwen_lossless_b200 import ops
-    dev = torch.device("cuda", 0)
+    rank, world, dev = _dist_setup(torch)
     ops.init()
     E, k = 256, 8
-    gate, up, down = _moe_weights(ops, dev, E)
-    sh_gu = _enc(ops, 1024, 2048, 1, 0, False, 104, dev)
+    n_local = E // world                      # expert-parallel: rank r holds experts [r * n_local, (r + 1) * n_local)
+    gate, up, down = _moe_weights(ops, dev, n_local, rank)
+    sh_gu = _enc(ops, 1024, 2048, 1, 0, False, 104, dev)      # the shared expert is replicated; rank 0's result is used
     sh_down = _enc(ops, 2048, 512, 1, 0, False, 105, dev)
     peak, _ = measured_peak()
     for T in (1, 2, 4):
         steps = 16
-        xs = [torch.randn(T, 2048, device=dev).to(torch.bfloat16) for _ in range(steps)]
-        logits = [torch.randn(T, E, device=dev) for _ in range(steps)]
-        scratch = ops.moe_decode_scratch(T, k, gate, down, E, dev)
+        g = torch.Generator(device=dev).manual_seed(1234 + T)   # the same tokens and routing on every rank
+        xs = [torch.randn(T, 2048, device=dev, generator=g).to(torch.bfloat16) for _ in range(steps)]
+        logits = [torch.randn(T, E, device=dev, generator=g) for _ in range(steps)]
+        scratch = ops.moe_decode_scratch(T, k, gate, down, n_local, dev)
         ids = [torch.empty(T, k, dtype=torch.int32, device=dev) for _ in range(steps)]
         wts = [torch.empty(T, k, device=dev) for _ in range(steps)]
         y = torch.empty(T, 2048, device=dev)
@@ -405,37 +431,75 @@ def run_moe_decode(args):
                     ops._mmv_common(xs[i], sh_gu, None, 0, False, True, True, a)   # shared expert: merged gate|up GLU
                     ops.mmv(a, sh_down, out=ysh)
                 ops.moe_decode(xs[i], gate, up, down, E, k, router_logits=logits[i], topk_weights=wts[i], topk_ids=ids[i],
-                               scratch=scratch, out=y)
+                               scratch=scratch, out=y, expert_lo=rank * n_local, n_experts_local=n_local)
                 main.wait_stream(side)
-                y.add_(ysh)
+                if world > 1:
+                    if rank == 0:
+                        y.add_(ysh)
+                    dist.all_reduce(y)      # the ranks' partial [T, 2048] outputs (NCCL over NVLink)
+                else:
+                    y.add_(ysh)
 
-        us = _time_graph(torch, step, max(args.steps // 16, 5), inner=steps)
+        us = _max_over_ranks(torch, _time_graph(torch, step, max(args.steps // 16, 5), inner=steps), world, dev)
         distinct = sum(len(torch.unique(i)) for i in ids) / steps
-        per_expert = (gate.nbytes + up.nbytes + down.nbytes) / E
+        per_expert = (gate.nbytes + up.nbytes + down.nbytes) / n_local
         nbytes = distinct * per_expert + sh_gu.nbytes + sh_down.nbytes
-        print(json.dumps({"workload": f"MoE decode layer, {T} token(s), 256 experts top-8 + shared expert", "us_per_layer": us,
-                          "distinct_experts": distinct, "compressed_bytes": nbytes, "GBps": nbytes / us / 1e3,
-                          "frac_of_measured_hbm": nbytes / us / 1e3 / peak, "launches_per_layer": 7}), flush=True)
+        if rank == 0:
+            print(json.dumps({"workload": f"MoE decode layer, {T} token(s), 256 experts top-8 + shared expert", "n_gpus": world,
+                              "parallelism": "1 GPU" if world == 1 else f"expert-parallel over {world} GPUs + NCCL all-reduce",
+                              "us_per_layer": us, "distinct_experts": distinct, "compressed_bytes": nbytes,
+                              "GBps": nbytes / us / 1e3, "frac_of_measured_hbm": nbytes / us / 1e3 / peak / world,
+                              "launches_per_layer": 7 + (world > 1)}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def run_moe_prefill(args):
     """Config 4: the same expert weights with 2048 and 8192 tokens: routing sort, batched gate/up + SwiGLU (BF16 out),
     batched down (FP32 out), combine."""
     import torch
-    from orin_qwen_lossless_b200 import ops
-    dev = torch.device("cuda", 0)
+    import torch.distributed as dist
+    from orin_qwen_lossless_b200 import ops, sharded
+    rank, world, dev = _dist_setup(torch)
     ops.init()
     E, k = 256, 8
-    gate, up, down = _moe_weights(ops, dev, E)
+    n_local = E // world
+    gate, up, down = _moe_weights(ops, dev, n_local, rank)
     for T in (2048, 8192):
-        x = torch.randn(T, 2048, device=dev).to(torch.bfloat16)
-        wts, ids = ops.moe_topk(torch.randn(T, E, device=dev), k)
-        us = _time_graph(torch, lambda: ops.moe_experts(x, gate, up, down, wts, ids, E), max(args.steps // 100, 5))
         flops = 6.0 * 512 * 2048 * k * T
-        nbytes = gate.nbytes + up.nbytes + down.nbytes
-        print(json.dumps({"workload": f"MoE prefill layer, {T} tokens, 256 experts top-8", "us_per_layer": us,
-                          "TFLOPs": flops / us / 1e6, "weight_GBps": nbytes / us / 1e3,
-                          "frac_of_bf16_peak_1679": flops / us / 1e6 / 1679.3}), flush=True)
+        nbytes = (gate.nbytes + up.nbytes + down.nbytes) * world
+        if world == 1:
+            x = torch.randn(T, 2048, device=dev).to(torch.bfloat16)
+            wts, ids = ops.moe_topk(torch.randn(T, E, device=dev), k)
+            us = _time_graph(torch, lambda: ops.moe_experts(x, gate, up, down, wts, ids, E), max(args.steps // 100, 5))
+            par = "1 GPU"
+        else:
+            # tokens data-parallel (T / world per rank), experts sharded: all-to-all dispatch of the routed rows, batched
+            # kernels on the owner, all-to-all back, combine. The exchange sizes come back to the host, so the layer is
+            # timed as eager launches with CUDA events (max over ranks).
+            Tl = T // world
+            x = torch.randn(Tl, 2048, device=dev).to(torch.bfloat16)
+            wts, ids = ops.moe_topk(torch.randn(Tl, E, device=dev), k)
+            for _ in range(3):
+                sharded.moe_prefill_ep(x, wts, ids, gate, up, down, E)
+            reps = max(args.steps // 100, 5)
+            torch.cuda.synchronize(); dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                sharded.moe_prefill_ep(x, wts, ids, gate, up, down, E)
+            e1.record()
+            torch.cuda.synchronize()
+            us = _max_over_ranks(torch, e0.elapsed_time(e1) * 1e3 / reps, world, dev)
+            par = f"expert-parallel over {world} GPUs, NCCL all-to-all dispatch and return"
+        if rank == 0:
+            print(json.dumps({"workload": f"MoE prefill layer, {T} tokens, 256 experts top-8", "n_gpus": world, "parallelism": par,
+                              "us_per_layer": us, "TFLOPs": flops / us / 1e6, "weight_GBps": nbytes / us / 1e3,
+                              "frac_of_bf16_peak_1679": flops / us / 1e6 / 1679.3 / world}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def main():
@@ -448,7 +512,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cublas", action="store_true", help="also time a stock BF16 GEMV of the uncompressed matrix")
     ap.add_argument("--workload", default="lm_head", choices=["lm_head", "small", "moe_decode", "moe_prefill"],
-                    help="lm_head is the headline contract line; the others print extra lines for the other baseline configs (1 GPU)")
+                    help="lm_head is the headline contract line; the others print extra lines for the other baseline configs "
+                         "(small: 1 GPU; the MoE workloads run expert-parallel under torchrun)")
     args = ap.parse_args()
     if args.workload != "lm_head":
         return {"small": run_small, "moe_decode": run_moe_decode, "moe_prefill": run_moe_prefill}[args.workload](args)
