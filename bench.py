@@ -197,17 +197,39 @@ def run_ours(args):
     gathered = torch.empty((world, width), dtype=torch.float32, device=dev)
     mine = gathered[rank, : r1 - r0].view(1, r1 - r0) if world > 1 else logits
 
-    def step():
+    def step_nccl():
         ops.mmv(x, enc, out=mine)
         if world > 1:
             dist.all_gather_into_tensor(gathered.view(-1), gathered[rank])
 
-    y_host = torch.empty((1, rows if world == 1 else world * width), dtype=torch.float32).pin_memory()
-    y_dev_full = logits if world == 1 else gathered.view(1, -1)
+    # N > 1, the product: the GEMV kernel stores its logits into every GPU's gathered buffer itself (peer stores over
+    # NVLink, epoch flags; the kernel ends when the peers' logits have arrived); no collective. Two steps (the two buffers in turn) form one CUDA graph.
+    fused = graph2 = None
+    if world > 1:
+        from orin_qwen_lossless_b200 import sharded
+        fused = sharded.FusedShardedLinear(enc, rows, R, 1)
+        last = [fused(x) for _ in range(2)]
+        torch.cuda.synchronize()
+        graph2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph2):
+            last = [fused(x) for _ in range(2)]
+
+    def step():
+        if world > 1:
+            graph2.replay()     # two steps
+        else:
+            step_nccl()
+
+    per_call = 2 if world > 1 else 1   # steps per call of step()
+    y_host = torch.empty((1, rows if world == 1 else world * fused.width), dtype=torch.float32).pin_memory()
 
     def step_e2e():
         x.copy_(x_host, non_blocking=True)
-        step()
+        if world > 1:
+            y_dev_full = fused(x).view(1, -1)
+        else:
+            step_nccl()
+            y_dev_full = logits
         y_host.copy_(y_dev_full, non_blocking=True)
         torch.cuda.current_stream().synchronize()  # a decode step consumes its logits on the host
 
@@ -232,7 +254,12 @@ def run_ours(args):
     for _ in range(max(args.warmup, 3)):
         step()
     sampler = ClockSampler(local) if rank == 0 else None
-    ms_total = timed(step, args.steps)
+    ms_total = timed(step, args.steps // per_call) / (args.steps // per_call * per_call) * args.steps
+    nccl_us = None
+    if world > 1:   # for comparison: the same shards with an NCCL all-gather behind the kernel (eager launches)
+        for _ in range(3):
+            step_nccl()
+        nccl_us = timed(step_nccl, args.steps) / args.steps * 1e3
     # the GEMV launch alone (no collective), per launch, on the launching stream: the roofline figure
     kernel_ms = timed(lambda: ops.mmv(x, enc, out=mine), args.steps) / args.steps
     for _ in range(3):
@@ -258,13 +285,18 @@ def run_ours(args):
         wb = gen_rows(r0, r0 + n).view(torch.int16).numpy().view(np.uint16)
         xf = o.bf16_bits_to_f32(x_host.view(torch.int16).numpy().view(np.uint16)[0])
         y64, s = o.gemv_f64(wb, xf)
-        got = mine[0, :n].float().cpu().numpy()
+        got = (last[-1][rank, 0, :n] if world > 1 else mine[0, :n]).float().cpu().numpy()
         parity = {"rows_checked": n, "max_err_over_sum_abs": float((np.abs(got - y64) / s).max()), "roundtrip_bit_exact": bool(ok)}
 
+    expired = fused.xchg.expired() if fused else False
+    if fused:
+        fused.close()
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
+    if expired:
+        raise SystemExit("bench.py: a wait for a peer's logits expired")
     ms_step = ms_total / args.steps
     peak, peak_src = measured_peak()
     achieved = shard_algo_bytes / (kernel_ms * 1e-3) / 1e9
@@ -274,7 +306,8 @@ def run_ours(args):
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"lm_head {rows}x{K} HUFPAIR R={R}, batch-1 decode GEMV, BF16 activation, FP32 logits"
-                               + (f", rows sharded over {world} GPUs + NCCL all-gather" if world > 1 else ""),
+                               + (f", rows sharded over {world} GPUs, logits stored into every GPU's buffer by the GEMV kernel "
+                                  "(peer stores + epoch flags, no collective)" if world > 1 else ""),
                    "l2": "inputs larger than L2 (compressed matrix %.0f MB per GPU)" % (shard_bytes / 1e6),
                    "compressed_bytes": total_weight_bytes, "bf16_bytes": rows * K * 2,
                    "ratio": total_weight_bytes / (rows * K * 2)},
@@ -287,7 +320,8 @@ def run_ours(args):
                      "algorithmic_bytes_per_launch": shard_algo_bytes},
         "e2e": {"value": algo_bytes / (ms_e2e / args.steps * 1e-3) / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": K * 2, "d2h_bytes_per_step": int(y_host.numel() * 4), "us_per_step": ms_e2e / args.steps * 1e3},
-        "gpu_launches": args.steps,
+        "gpu_launches": args.steps,   # one kernel per step at every N
+        "nccl_allgather_us_per_step": nccl_us,
         "cublas_bf16_gemv_us": cublas_us,
         "clocks": clocks, "parity": parity,
         "host": {"gen_s": t_gen, "encode_s": t_enc, "encode_GBps_bf16": (r1 - r0) * K * 2 / t_enc / 1e9, "threads": os.cpu_count()},

@@ -173,6 +173,45 @@ int bf16n_moe_decode_static(const bf16n_weight * gate, const bf16n_weight * up, 
                             int64_t x_tok, const float * router_logits, int n_experts, int32_t * topk_ids, float * topk_weights,
                             int n_tok, int n_used, int expert_lo, int n_experts_local, void * y, int y_bf16, void * stream);
 
+/* ---- multi-GPU: outputs written straight into the other GPUs of the node ------------------------------------------
+ * New: the reference is single-GPU and has nothing like this. A row-sharded projection normally ends with a collective
+ * that gathers the shards; here the GEMV kernel itself stores every logit it produces into each peer's buffer as well
+ * (plain stores to peer memory over NVLink), and the last block to finish publishes an epoch number in the peers'
+ * headers. A consumer waits for the epochs of all its peers with bf16n_peer_wait (one tiny kernel) instead of running a
+ * collective. No multicast, no library collective on this path.
+ *
+ * An exchange buffer is [256-byte header | payload]. Header words (uint32): 0..7 epoch announced by rank r (written by
+ * rank r), 16 finished-block counter, 17 epochs sent, 18 epochs waited for, 19 set when a wait expired. The counters
+ * live on the device, so launches captured in a CUDA graph keep working when replayed; every rank must issue the same
+ * sequence of fan-out launches and waits. Use two payload areas in turn when a step may start before every peer has
+ * consumed the previous one. */
+#define BF16N_EXCHANGE_HEADER_BYTES 256
+#define BF16N_MAX_PEERS 7
+#define BF16N_IPC_HANDLE_BYTES 64
+typedef struct bf16n_peer_out {
+    int n_peers;                         /* 0..7 other GPUs */
+    void * y[BF16N_MAX_PEERS];           /* where the same output goes in each peer's exchange buffer (mapped here) */
+    uint32_t * flag[BF16N_MAX_PEERS];    /* header word [my rank] of each peer's exchange buffer (mapped here) */
+    uint32_t * local_header;             /* this GPU's own exchange buffer */
+    int wait_mask;                       /* 0, or the ranks (bit r) whose output of the same epoch must have arrived here
+                                          * before the kernel ends: the kernel then replaces bf16n_peer_wait as well */
+} bf16n_peer_out;
+/* Allocates a zeroed exchange buffer of header + payload_bytes on the current device and exports it for the other
+ * processes of the node (cudaIpcGetMemHandle). */
+int bf16n_exchange_create(size_t payload_bytes, void ** base, unsigned char handle[BF16N_IPC_HANDLE_BYTES]);
+/* Maps a peer's exchange buffer into this process (peer access is enabled on demand). */
+int bf16n_exchange_open(const unsigned char handle[BF16N_IPC_HANDLE_BYTES], void ** base);
+int bf16n_exchange_close(void * peer_base);
+int bf16n_exchange_destroy(void * base);
+/* bf16n_mmv whose output also goes to the peers (dense row-major HUFPAIR matrices; one kernel does the product, the
+ * peer stores and the announcement). a->y must point into this GPU's exchange payload at the offset the peers use. */
+int bf16n_mmv_peers(const bf16n_weight * w, const bf16n_mmv_args * a, const bf16n_peer_out * peers, void * stream);
+/* Waits on the stream until every peer in rank_mask (bit r = rank r) has announced its next epoch; bounded (about two
+ * seconds), after which header word 19 is set and the stream continues. */
+int bf16n_peer_wait(uint32_t * local_header, int rank_mask, void * stream);
+/* Synchronises the stream and returns header word 19 (non-zero: a wait expired since the buffer was created). */
+int bf16n_peer_expired(const uint32_t * local_header, void * stream, int * expired);
+
 #ifdef __cplusplus
 }
 #endif

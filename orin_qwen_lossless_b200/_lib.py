@@ -30,6 +30,11 @@ class MmvArgs(C.Structure):
                 ("y_slot", C.c_int64), ("rows_per_matrix", C.c_int64), ("row0", C.c_int64), ("nrows", C.c_int64)]
 
 
+class PeerOut(C.Structure):
+    """struct bf16n_peer_out"""
+    _fields_ = [("n_peers", C.c_int), ("y", C.c_void_p * 7), ("flag", C.c_void_p * 7), ("local_header", C.c_void_p), ("wait_mask", C.c_int)]
+
+
 # name -> (restype, argtypes); every symbol include/bf16n_c.h declares
 SIGNATURES = {
     "bf16n_last_error": (C.c_char_p, []),
@@ -62,6 +67,13 @@ SIGNATURES = {
                                           C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                           C.c_int, C.c_void_p]),
     "bf16n_moe_topk": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "bf16n_exchange_create": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]),
+    "bf16n_exchange_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "bf16n_exchange_close": (C.c_int, [C.c_void_p]),
+    "bf16n_exchange_destroy": (C.c_int, [C.c_void_p]),
+    "bf16n_mmv_peers": (C.c_int, [C.POINTER(Weight), C.POINTER(MmvArgs), C.POINTER(PeerOut), C.c_void_p]),
+    "bf16n_peer_wait": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "bf16n_peer_expired": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
 }
 
 _lib = None

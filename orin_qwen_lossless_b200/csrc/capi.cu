@@ -326,4 +326,74 @@ int bf16n_moe_decode_static(const bf16n_weight * gate, const bf16n_weight * up, 
     });
 }
 
+
+int bf16n_exchange_create(size_t payload_bytes, void ** base, unsigned char handle[BF16N_IPC_HANDLE_BYTES]) {
+    return guarded([&] {
+        static_assert(sizeof(cudaIpcMemHandle_t) == BF16N_IPC_HANDLE_BYTES, "IPC handle size");
+        require(base && handle, "exchange_create: null output");
+        void * p = nullptr;
+        const size_t bytes = BF16N_EXCHANGE_HEADER_BYTES + ((payload_bytes + 255) & ~(size_t) 255);
+        cuda_ok(cudaMalloc(&p, bytes), "exchange buffer");
+        cuda_ok(cudaMemset(p, 0, bytes), "exchange buffer clear");
+        cuda_ok(cudaDeviceSynchronize(), "exchange buffer clear");
+        cudaIpcMemHandle_t h;
+        cuda_ok(cudaIpcGetMemHandle(&h, p), "exchange buffer export");
+        memcpy(handle, &h, sizeof h);
+        *base = p;
+    });
+}
+
+int bf16n_exchange_open(const unsigned char handle[BF16N_IPC_HANDLE_BYTES], void ** base) {
+    return guarded([&] {
+        require(base && handle, "exchange_open: null argument");
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handle, sizeof h);
+        void * p = nullptr;
+        cuda_ok(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), "exchange buffer import");
+        *base = p;
+    });
+}
+
+int bf16n_exchange_close(void * peer_base) {
+    return guarded([&] { cuda_ok(cudaIpcCloseMemHandle(peer_base), "exchange buffer unmap"); });
+}
+
+int bf16n_exchange_destroy(void * base) {
+    return guarded([&] { cuda_ok(cudaFree(base), "exchange buffer free"); });
+}
+
+int bf16n_mmv_peers(const bf16n_weight * w, const bf16n_mmv_args * a, const bf16n_peer_out * peers, void * stream) {
+    return guarded([&] {
+        ensure_init();
+        check_weight(*w);
+        no_frag_order(*w);
+        require(a->ncols > 0 && a->ncols <= 65535, "ncols out of range");
+        whole_units(*w, *a);
+        check_x(*w, *a);
+        require(peers && peers->n_peers >= 0 && peers->n_peers <= BF16N_MAX_PEERS, "mmv_peers: 0..7 peers");
+        require(peers->n_peers == 0 || peers->local_header, "mmv_peers: the local exchange header is missing");
+        require(peers->wait_mask >= 0 && peers->wait_mask < 256, "mmv_peers: wait_mask names ranks 0..7");
+        for (int r = 0; r < peers->n_peers; r++) { require(peers->y[r] && peers->flag[r], "mmv_peers: null peer pointer"); }
+        require(a->nrows > 0, "mmv_peers: empty product (every rank must announce)");
+        gemv(*w, *a, (cudaStream_t) stream, false, peers);
+    });
+}
+
+int bf16n_peer_wait(uint32_t * local_header, int rank_mask, void * stream) {
+    return guarded([&] {
+        require(local_header && rank_mask >= 0 && rank_mask < 256, "peer_wait: header and a mask of ranks 0..7");
+        peer_wait(local_header, rank_mask, (cudaStream_t) stream);
+    });
+}
+
+int bf16n_peer_expired(const uint32_t * local_header, void * stream, int * expired) {
+    return guarded([&] {
+        require(local_header && expired, "peer_expired: null argument");
+        uint32_t v = 0;
+        cuda_ok(cudaMemcpyAsync(&v, local_header + 19, sizeof v, cudaMemcpyDeviceToHost, (cudaStream_t) stream), "exchange header read");
+        cuda_ok(cudaStreamSynchronize((cudaStream_t) stream), "exchange header read");
+        *expired = (int) v;
+    });
+}
+
 } // extern "C"

@@ -84,6 +84,18 @@ struct OutVec { // one output column, FP32 or BF16 (round to nearest even)
 
 // ---------------------------------------------------------------- columns (tokens, or (token, expert slot) pairs)
 
+// Optional fan-out of a kernel's output to other GPUs (dense columns only): every value written to y is also stored at
+// the same offset of each peer's buffer, and the last block to finish announces the launch in the peers' headers.
+constexpr int MAX_PEERS = 7;
+struct PeerOut {
+    int n;                        // number of peers (0: none)
+    char * y[MAX_PEERS];          // the peers' copies of y (peer memory mapped into this process)
+    uint32_t * flag[MAX_PEERS];   // this rank's slot in each peer's exchange header
+    uint32_t * hdr;               // this rank's own exchange header (block counter, epochs): words of bf16n_c.h's layout
+    int wait_mask;                // ranks whose announcement of the same epoch the last block awaits before the kernel ends
+};
+constexpr int XH_DONE = 16, XH_SENT = 17, XH_WAITED = 18, XH_EXPIRED = 19; // header words (0..7: the peers' flags)
+
 struct Cols {
     const char * x; char * y;
     int64_t x_tok, x_slot, y_tok, y_slot; // byte strides
@@ -91,7 +103,61 @@ struct Cols {
     int n_used, x_per_slot;
     int64_t rows_per_matrix, row0, nrows;
     bool y_bf16;
+    PeerOut peers;
 };
+
+// value i of dense column `col`, to every peer
+__device__ __forceinline__ void peers_put(const Cols & c, int col, int64_t i, float v) {
+    for (int r = 0; r < c.peers.n; r++) {
+        char * q = c.peers.y[r] + col * c.y_tok;
+        if (c.y_bf16) { ((__nv_bfloat16 *) q)[i] = __float2bfloat16_rn(v); } else { ((float *) q)[i] = v; }
+    }
+}
+// End of a kernel that fans out: call with every thread of the block that is still running. Each block makes its
+// stores visible system-wide and counts itself; the last one advances this rank's epoch and publishes it to the peers
+// (release), whose bf16n_peer_wait acquires it.
+__device__ __forceinline__ void peers_done(const Cols & c) {
+    if (c.peers.n == 0) { return; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        const unsigned blocks = gridDim.x * gridDim.y * gridDim.z;
+        if (atomicAdd(c.peers.hdr + XH_DONE, 1u) == blocks - 1u) {
+            c.peers.hdr[XH_DONE] = 0u;
+            const uint32_t epoch = c.peers.hdr[XH_SENT] + 1u;
+            c.peers.hdr[XH_SENT] = epoch;
+            __threadfence_system();
+            for (int r = 0; r < c.peers.n; r++) {
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(c.peers.flag[r]), "r"(epoch) : "memory");
+            }
+            // Optionally the kernel also stands in for the consumer's wait: it ends only when the peers' outputs of the
+            // same epoch have arrived here. A peer publishes before it waits, so no rank waits for a rank that waits
+            // for it. Bounded: after about two seconds the header's expired word is set and the kernel ends anyway.
+            if (c.peers.wait_mask) {
+                uint64_t t0 = 0;
+                bool all = false;
+                for (uint32_t i = 0; i < (1u << 26) && !all; i++) {
+                    all = true;
+                    for (int r = 0; r < 8; r++) {
+                        if (c.peers.wait_mask >> r & 1) {
+                            uint32_t seen;
+                            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(c.peers.hdr + r) : "memory");
+                            all = all && (int32_t) (seen - epoch) >= 0;
+                        }
+                    }
+                    if (!all && (i & 1023u) == 1023u) {
+                        uint64_t now;
+                        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                        if (t0 == 0) { t0 = now; } else if (now - t0 > 2000000000ull) { break; }
+                    }
+                }
+                if (!all) { c.peers.hdr[XH_EXPIRED] = 1u; }
+                c.peers.hdr[XH_WAITED] = epoch;
+                __threadfence_system();
+            }
+        }
+    }
+}
 
 // activation pointer, output column and first weight row of column `col`
 template <typename TX>
@@ -323,8 +389,17 @@ inline NibView nib_view(const bf16n_weight & w, int64_t shift_rows = 0) {
             (const uint32_t *) (w.aux + w.off_c) + shift_rows, (const uint32_t *) (w.aux + w.off_d)};
 }
 
-inline Cols make_cols(const bf16n_mmv_args & a) {
+inline Cols make_cols(const bf16n_mmv_args & a, const bf16n_peer_out * peers = nullptr) {
     Cols c = {};
+    if (peers) {
+        c.peers.n = peers->n_peers;
+        for (int r = 0; r < peers->n_peers && r < MAX_PEERS; r++) {
+            c.peers.y[r] = (char *) peers->y[r];
+            c.peers.flag[r] = peers->flag[r];
+        }
+        c.peers.hdr = peers->local_header;
+        c.peers.wait_mask = peers->wait_mask;
+    }
     c.x = (const char *) a.x; c.y = (char *) a.y;
     c.x_tok = a.x_tok; c.y_tok = a.y_tok; c.x_slot = a.x_slot; c.y_slot = a.y_slot;
     c.ids = (const char *) a.ids; c.ids_s0 = a.ids_s0; c.ids_s1 = a.ids_s1;

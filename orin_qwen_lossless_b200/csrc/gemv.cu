@@ -98,10 +98,12 @@ __global__ void __launch_bounds__(512) k_pair_gemv(const PairView w, int R, Cols
                     OutVec o = out;
                     o.p += n * p.y_tok;
                     o.put(u * R + rr, s);
+                    if (NC == 1) { peers_put(p, blockIdx.y, u * R + rr, s); }
                 }
             }
         }
     }
+    if (NC == 1) { peers_done(p); }
 }
 
 // y = silu(gate x) * (up x), separate row-major gate / up matrices with the same geometry
@@ -510,8 +512,12 @@ dim3 row_geometry(int64_t work, int ncols) { // 8 warps per block, one work item
 }
 
 template <typename TX>
-void launch_gemv(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st, bool multi_col) {
-    const Cols p = make_cols(a);
+void launch_gemv(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st, bool multi_col, const bf16n_peer_out * peers) {
+    const Cols p = make_cols(a, peers);
+    if (peers && peers->n_peers > 0) {
+        require(w.format == FMT_HUFPAIR && !w.cm && !a.ids, "peer outputs need a dense row-major HUFPAIR product");
+        multi_col = false; // one column per blockIdx.y: the kernels that fan out
+    }
     const int C = (int) (w.K / CHUNK);
     if (w.format == FMT_HUFPAIR) {
         const int64_t units = a.nrows / w.R;
@@ -542,10 +548,10 @@ void launch_gemv(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t 
 #undef MC
             }
         } else if (gemv_rings_enabled() && gemv_rings_applies(w, a)) {
-            gemv_rings(w, a, st);
+            gemv_rings(w, a, st, peers);
             return;
         } else if (gemv_staged_applies(w, a)) {
-            gemv_staged(w, a, st);
+            gemv_staged(w, a, st, peers);
             return;
         } else {
             unit_geometry(units, a.ncols, 16, grid, threads);
@@ -646,8 +652,8 @@ void gemv_init() {
     gemv_rings_init();
 }
 
-void gemv(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st, bool multi_col) {
-    if (a.x_bf16) { launch_gemv<bf16>(w, a, st, multi_col); } else { launch_gemv<float>(w, a, st, multi_col); }
+void gemv(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st, bool multi_col, const bf16n_peer_out * peers) {
+    if (a.x_bf16) { launch_gemv<bf16>(w, a, st, multi_col, peers); } else { launch_gemv<float>(w, a, st, multi_col, peers); }
 }
 
 void gemv_glu_merged(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st) {

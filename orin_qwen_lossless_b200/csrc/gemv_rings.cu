@@ -206,8 +206,12 @@ __global__ void __launch_bounds__(NT, 1) k_pair_gemv_rings(const PairView w, int
             const float s = warp_sum((a[0] + a[1]) + (a[2] + a[3]));
             if (lane == rr) { mine = s; }
         }
-        if (lane < R) { out.put(u * R + lane, mine); }
+        if (lane < R) {
+            out.put(u * R + lane, mine);
+            peers_put(p, blockIdx.y, u * R + lane, mine);
+        }
     }
+    peers_done(p);
 }
 
 constexpr int RING_SET = 32 * RING_BYTES;
@@ -235,8 +239,8 @@ bool gemv_rings_applies(const bf16n_weight & w, const bf16n_mmv_args & a) {
     return a.nrows / w.R >= (int64_t) device_info().sms * 16 * std::max(1, a.ncols);
 }
 
-void gemv_rings(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st) {
-    const Cols p = make_cols(a);
+void gemv_rings(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st, const bf16n_peer_out * peers) {
+    const Cols p = make_cols(a, peers);
     const int64_t units = a.nrows / w.R, sms = device_info().sms;
     const int max_warps = std::min(g_warps, w.K == 2048 ? 32 : 28);
     int best = max_warps;

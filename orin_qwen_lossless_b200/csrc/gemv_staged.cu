@@ -130,9 +130,13 @@ __global__ void __launch_bounds__(512, 1) k_pair_gemv_staged(const PairView w, c
             rd.rd.open(w, gu, lane);
             mine = unit_rows<C, TX>(rd, 0u, k, pl, R, x, lane);
         }
-        if (lane < R) { out.put(u * R + lane, mine); }
+        if (lane < R) {
+            out.put(u * R + lane, mine);
+            peers_put(p, blockIdx.y, u * R + lane, mine);
+        }
         cur = nxt;
     }
+    peers_done(p);
 }
 
 constexpr int FIXED_SMEM = 4 * HP_MAX_PAIRS + 128;
@@ -159,8 +163,8 @@ bool gemv_staged_applies(const bf16n_weight & w, const bf16n_mmv_args & a) {
     return room >= 8 && units >= (int64_t) device_info().sms * 8 * std::max(1, a.ncols);
 }
 
-void gemv_staged(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st) {
-    const Cols p = make_cols(a);
+void gemv_staged(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st, const bf16n_peer_out * peers) {
+    const Cols p = make_cols(a, peers);
     const uint32_t cap = buffer_bytes(w);
     const int64_t units = a.nrows / w.R, sms = device_info().sms;
     const int max_warps = (int) std::min<int64_t>(16, (device_info().smem_optin - FIXED_SMEM) / cap);

@@ -47,7 +47,7 @@ __device__ __forceinline__ void grid_dependency_wait() {
 
 // gemv.cu
 void gemv_init();
-void gemv(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st, bool multi_col);
+void gemv(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st, bool multi_col, const bf16n_peer_out * peers = nullptr);
 void gemv_glu_merged(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st);
 void gemv_glu(const bf16n_weight & g, const bf16n_weight & u, const bf16n_mmv_args & a, cudaStream_t st);
 void expand_store(const bf16n_weight & w, int64_t row0, int64_t nrows, uint16_t * out, cudaStream_t st);
@@ -59,13 +59,16 @@ void gather_rows(const bf16n_weight & w, const void * ids, int64_t ids_s0, int64
 // gemv_staged.cu
 void gemv_staged_init();
 bool gemv_staged_applies(const bf16n_weight & w, const bf16n_mmv_args & a);
-void gemv_staged(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st);
+void gemv_staged(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st, const bf16n_peer_out * peers = nullptr);
 
 // gemv_rings.cu
 void gemv_rings_init();
 bool gemv_rings_enabled();
 bool gemv_rings_applies(const bf16n_weight & w, const bf16n_mmv_args & a);
-void gemv_rings(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st);
+void gemv_rings(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st, const bf16n_peer_out * peers = nullptr);
+
+// peer.cu: exchange buffers shared between the GPUs of a node and the wait for the peers' announcements
+void peer_wait(uint32_t * local_header, int n_peers_mask, cudaStream_t st);
 
 // moe.cu
 void moe_init();

@@ -11,11 +11,14 @@ collectives (NCCL over NVLink on the GPUs, gloo in the CPU tests).
 """
 from __future__ import annotations
 
+import ctypes as C
+
 import numpy as np
 import torch
 import torch.distributed as dist
 
 from . import ops
+from ._lib import MmvArgs, PeerOut, check, lib
 from .ops import FLAG_CHUNK_MAJOR, FLAG_FRAG_ORDER, FMT_HUFFMAN, FMT_HUFPAIR, FMT_NIBBLE, HEADER, MAGIC, Meta
 
 HP_TAIL_WORDS, HUF_TAIL_WORDS = 32, 16
@@ -89,6 +92,99 @@ def shard_rows(plane: torch.Tensor, aux: torch.Tensor, r0: int, r1: int) -> tupl
     return p, new_aux, ops.parse_header(new_aux)
 
 
+# ------------------------------------------------------------------ exchange buffers between the GPUs of one node
+
+HEADER_BYTES = 256          # BF16N_EXCHANGE_HEADER_BYTES
+IPC_HANDLE_BYTES = 64
+
+
+class PeerExchange:
+    """One exchange buffer per rank ([256-byte header | payload], allocated by the library), every peer's buffer mapped
+    into this process through CUDA IPC. Kernels launched with `peer_out()` store their output into all of them and
+    announce it; `wait()` holds the stream until every peer has announced its next launch. One process per GPU, all on
+    one node; the handles travel through the process group once, at construction."""
+
+    def __init__(self, payload_bytes: int, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if not 2 <= self.world <= 8:
+            raise ValueError("bf16n PeerExchange: 2..8 ranks on one node")
+        self.payload_bytes = payload_bytes
+        base = C.c_void_p()
+        handle = C.create_string_buffer(IPC_HANDLE_BYTES)
+        check(lib().bf16n_exchange_create(payload_bytes, C.byref(base), handle))
+        self.base = base.value
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle.raw, group=group)
+        self.bases = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.bases.append(self.base)
+                continue
+            peer = C.c_void_p()
+            check(lib().bf16n_exchange_open(h, C.byref(peer)))
+            self.bases.append(peer.value)
+        self.peers = [r for r in range(self.world) if r != self.rank]
+        self.mask = sum(1 << r for r in self.peers)
+        dist.barrier(group=group)  # every rank has mapped every buffer before anyone writes
+
+    def payload(self, offset: int, shape, dtype) -> torch.Tensor:
+        """A tensor over this rank's payload at `offset` bytes (a view of library-owned memory: keep `self` alive)."""
+        n = int(np.prod(shape)) * torch.empty((), dtype=dtype).element_size()
+        if offset % 16 or offset + n > self.payload_bytes:
+            raise ValueError("bf16n PeerExchange: payload range out of bounds or unaligned")
+        buf = (C.c_char * n).from_address(self.base + HEADER_BYTES + offset)
+        iface = {"shape": tuple(int(s) for s in shape), "typestr": {torch.float32: "<f4", torch.bfloat16: "<u2"}[dtype],
+                 "data": (self.base + HEADER_BYTES + offset, False), "version": 3}
+        holder = type("_Span", (), {"__cuda_array_interface__": iface, "_keep": buf})()
+        t = torch.as_tensor(holder, device=torch.device("cuda", torch.cuda.current_device()))
+        return t.view(dtype) if dtype == torch.bfloat16 else t
+
+    def peer_out(self, offset: int, wait: bool = False) -> PeerOut:
+        """Fan-out descriptor: the peers' payloads at `offset` and this rank's flag word in each peer's header.
+        wait=True: the kernel also waits for the peers' outputs of the same epoch before it ends (no wait() call)."""
+        o = PeerOut()
+        o.wait_mask = self.mask if wait else 0
+        o.n_peers = len(self.peers)
+        for i, r in enumerate(self.peers):
+            o.y[i] = self.bases[r] + HEADER_BYTES + offset
+            o.flag[i] = self.bases[r] + 4 * self.rank
+        o.local_header = self.base
+        return o
+
+    def wait(self) -> None:
+        check(lib().bf16n_peer_wait(self.base, self.mask, ops._stream()))
+
+    def expired(self) -> bool:
+        v = C.c_int(0)
+        check(lib().bf16n_peer_expired(self.base, ops._stream(), C.byref(v)))
+        return bool(v.value)
+
+    def close(self) -> None:
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)  # nobody still writes into a buffer that is about to go away
+        for r in self.peers:
+            check(lib().bf16n_exchange_close(self.bases[r]))
+        check(lib().bf16n_exchange_destroy(self.base))
+        self.bases, self.base = [], None
+
+
+def mmv_peers(x: torch.Tensor, w: ops.Weight, y: torch.Tensor, peers: PeerOut) -> None:
+    """y = W x for dense x [T, K] like ops.mmv, the same values stored into every peer's buffer by the same kernel."""
+    cw = w.c()
+    ops._check_x(x, w.meta.K)
+    if x.dim() != 2 or y.dim() != 2 or y.shape != (x.shape[0], w.meta.rows) or y.stride(1) != 1:
+        raise RuntimeError("bf16n.mmv_peers: x [T, K], y [T, rows] with unit column stride")
+    a = MmvArgs()
+    a.x, a.x_bf16, a.y, a.y_bf16 = x.data_ptr(), int(x.dtype == torch.bfloat16), y.data_ptr(), int(y.dtype == torch.bfloat16)
+    a.ncols, a.n_used, a.x_per_slot = x.shape[0], 1, 1
+    a.x_tok, a.y_tok = x.stride(0) * x.element_size(), y.stride(0) * y.element_size()
+    a.rows_per_matrix, a.nrows = w.meta.rows, w.meta.rows
+    with torch.cuda.device(w.plane.device):
+        check(lib().bf16n_mmv_peers(C.byref(cw), C.byref(a), C.byref(peers), ops._stream()))
+
+
 # ------------------------------------------------------------------ vocabulary projection: rows sharded + all-gather
 
 class ShardedLinear:
@@ -120,6 +216,46 @@ class ShardedLinear:
     def assemble(self, gathered: torch.Tensor) -> torch.Tensor:
         """[T, rows_total] logits from the gathered shards."""
         return torch.cat([gathered[r, :, : b - a] for r, (a, b) in enumerate(self.ranges)], dim=1)
+
+
+class FusedShardedLinear:
+    """Row shard of a projection whose GEMV kernel writes its logits into every rank's gathered buffer itself (peer
+    stores over NVLink), announces them and (wait_in_kernel) ends only when the peers' logits have arrived: one kernel per
+    step, no collective. With wait_in_kernel=False a separate small wait kernel follows instead. The gathered buffers live in a PeerExchange payload,
+    two of them used in turn so that a step may start before every peer has read the previous one."""
+
+    def __init__(self, weight: ops.Weight, rows_total: int, unit_rows: int, max_tokens: int, group=None, wait_in_kernel: bool = True):
+        self.w = weight
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.ranges = [unit_range(r, self.world, rows_total, unit_rows) for r in range(self.world)]
+        self.rows_total, self.T = rows_total, max_tokens
+        # buffer b: [world][T][width] FP32, shards padded to the widest and placed at 256-byte aligned offsets
+        self.width = (max(b - a for a, b in self.ranges) + 63) // 64 * 64
+        self.area = self.world * max_tokens * self.width * 4
+        self.xchg = PeerExchange(2 * self.area, group)
+        self.step = 0
+        self._views = [self.xchg.payload(b * self.area, (self.world, max_tokens, self.width), torch.float32) for b in range(2)]
+        self.wait_in_kernel = wait_in_kernel
+        self._outs = [self.xchg.peer_out(b * self.area + self.rank * max_tokens * self.width * 4, wait_in_kernel) for b in range(2)]
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        """x [T, K] (replicated, T == max_tokens) -> gathered [world, T, width]: rank r's logits in [r, :, :rows_r],
+        complete on this stream when the call returns."""
+        if x.shape[0] != self.T:
+            raise RuntimeError("bf16n FusedShardedLinear: built for a fixed number of tokens")
+        b = self.step & 1
+        self.step += 1
+        a0, a1 = self.ranges[self.rank]
+        mmv_peers(x, self.w, self._views[b][self.rank][:, : a1 - a0], self._outs[b])  # rows of the padded [T, width] slot
+        if not self.wait_in_kernel:
+            self.xchg.wait()
+        return self._views[b]
+
+    def assemble(self, gathered: torch.Tensor) -> torch.Tensor:
+        return torch.cat([gathered[r, :, : b - a] for r, (a, b) in enumerate(self.ranges)], dim=1)
+
+    def close(self) -> None:
+        self.xchg.close()
 
 
 # ------------------------------------------------------------------ MoE decode: expert-parallel + all-reduce

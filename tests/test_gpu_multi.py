@@ -1,4 +1,5 @@
-"""Two-GPU runs of the sharded paths over NCCL (skipped with fewer than two GPUs): row-sharded projection + all-gather,
+"""Two-GPU runs of the sharded paths (skipped with fewer than two GPUs): row-sharded projection + NCCL all-gather, the same
+projection with the gather fused into the GEMV kernel (stores to peer memory, epoch flags, bounded wait kernel),
 expert-parallel MoE decode + all-reduce, expert-parallel MoE prefill + all-to-all, each against the single-GPU result."""
 import os
 import socket
@@ -40,6 +41,39 @@ def _worker(rank, world, port, ret):
         full = ops.mmv(x, ops.upload(p, a, m, dev))
         ok1 = bool(torch.equal(y, full))  # every row is computed by the same kernel code: bitwise
 
+        # 1b. the same projection with the gather fused into the GEMV kernel: peer stores + epoch flags, no collective.
+        # Several steps with changing activations, under a CUDA graph too (the epoch counters live on the device).
+        ok1b = True
+        for T1, big in ((2, 0), (1, 16), (1, 10)):  # units per SM and rank: general kernel, per-lane rings, bulk-copy staged
+            if big:
+                rows_b = 16 * 148 * big * world
+                wb_b = o.weights_like(rows_b, K, 8)
+                p_b, a_b, m_b = enc(wb_b, R, False)
+                rb0, rb1 = sharded.unit_range(rank, world, rows_b, R)
+                sh = ops.upload(*sharded.shard_rows(p_b, a_b, rb0, rb1), dev)
+                whole, nrows = ops.upload(p_b, a_b, m_b, dev), rows_b
+            else:
+                sh, whole, nrows = ops.upload(sp, sa, sm, dev), ops.upload(p, a, m, dev), rows
+            fused = sharded.FusedShardedLinear(sh, nrows, R, T1, wait_in_kernel=bool(big != 10))  # both forms of the wait
+            xs = [to_bf16_tensor(o.f32_to_bf16_bits(np.random.default_rng(40 + i).standard_normal((T1, K)).astype(np.float32))).to(dev)
+                  for i in range(4)]
+            for i in range(4):
+                got = fused.assemble(fused(xs[i]))
+                ok1b = ok1b and bool(torch.equal(got, ops.mmv(xs[i], whole)))
+            xg = xs[0].clone()
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                outs = [fused.assemble(fused(xg)) for _ in range(2)]   # both buffers in turn
+            for i in range(1, 4):
+                xg.copy_(xs[i])
+                gr.replay()
+                torch.cuda.synchronize()
+                want = ops.mmv(xs[i], whole)
+                ok1b = ok1b and all(bool(torch.equal(t, want)) for t in outs)
+            ok1b = ok1b and not fused.xchg.expired()
+            fused.close()
+
         # 2. MoE decode, experts split over the ranks
         bits = {"gate": o.weights_like(E * N, H, 11), "up": o.weights_like(E * N, H, 12), "down": o.weights_like(E * H, N, 13)}
         n_local = E // world
@@ -67,7 +101,7 @@ def _worker(rank, world, port, ret):
         y_loc = ops.moe_experts(xp, g, u, d, w_p, i_p, E)
         err = float((y_a2a.float() - y_loc.float()).abs().max())
         ok3 = err <= 2.0 ** -7 * float(y_loc.float().abs().max())
-        ret[rank] = (ok1, ok2, ok3)
+        ret[rank] = (ok1, ok1b, ok2, ok3)
     finally:
         dist.destroy_process_group()
 
@@ -86,4 +120,4 @@ def test_two_gpu_paths():
     for p in procs:
         p.join(600)
         assert p.exitcode == 0
-    assert [ret[r] for r in range(2)] == [(True, True, True)] * 2
+    assert [ret[r] for r in range(2)] == [(True, True, True, True)] * 2
