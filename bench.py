@@ -205,9 +205,19 @@ def run_ours(args):
     # N > 1, the product: the GEMV kernel stores its logits into every GPU's gathered buffer itself (peer stores over
     # NVLink, epoch flags; the kernel ends when the peers' logits have arrived); no collective. Two steps (the two buffers in turn) form one CUDA graph.
     fused = graph2 = None
+    fused_note = None
     if world > 1:
         from orin_qwen_lossless_b200 import sharded
-        fused = sharded.FusedShardedLinear(enc, rows, R, 1)
+        try:
+            fused = sharded.FusedShardedLinear(enc, rows, R, 1)
+        except (RuntimeError, ValueError) as e:   # e.g. no peer access between these GPUs: say so and gather with NCCL
+            fused_note = str(e)
+        agree = torch.tensor([0 if fused else 1], dtype=torch.int32, device=dev)
+        dist.all_reduce(agree)
+        if int(agree.item()) and fused:
+            fused.close()
+            fused, fused_note = None, "exchange buffers unavailable on another rank"
+    if fused:
         last = [fused(x) for _ in range(2)]
         torch.cuda.synchronize()
         graph2 = torch.cuda.CUDAGraph()
@@ -215,18 +225,21 @@ def run_ours(args):
             last = [fused(x) for _ in range(2)]
 
     def step():
-        if world > 1:
+        if fused:
             graph2.replay()     # two steps
         else:
             step_nccl()
 
-    per_call = 2 if world > 1 else 1   # steps per call of step()
-    y_host = torch.empty((1, rows if world == 1 else world * fused.width), dtype=torch.float32).pin_memory()
+    per_call = 2 if fused else 1   # steps per call of step()
+    y_host = torch.empty((1, rows if world == 1 else world * (fused.width if fused else width)), dtype=torch.float32).pin_memory()
 
     def step_e2e():
         x.copy_(x_host, non_blocking=True)
-        if world > 1:
+        if fused:
             y_dev_full = fused(x).view(1, -1)
+        elif world > 1:
+            step_nccl()
+            y_dev_full = gathered.view(1, -1)
         else:
             step_nccl()
             y_dev_full = logits
@@ -285,10 +298,11 @@ def run_ours(args):
         wb = gen_rows(r0, r0 + n).view(torch.int16).numpy().view(np.uint16)
         xf = o.bf16_bits_to_f32(x_host.view(torch.int16).numpy().view(np.uint16)[0])
         y64, s = o.gemv_f64(wb, xf)
-        got = (last[-1][rank, 0, :n] if world > 1 else mine[0, :n]).float().cpu().numpy()
+        got = (last[-1][rank, 0, :n] if fused else mine[0, :n]).float().cpu().numpy()
         parity = {"rows_checked": n, "max_err_over_sum_abs": float((np.abs(got - y64) / s).max()), "roundtrip_bit_exact": bool(ok)}
 
     expired = fused.xchg.expired() if fused else False
+    fused_used = fused is not None
     if fused:
         fused.close()
     if rank != 0:
@@ -307,7 +321,8 @@ def run_ours(args):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"lm_head {rows}x{K} HUFPAIR R={R}, batch-1 decode GEMV, BF16 activation, FP32 logits"
                                + (f", rows sharded over {world} GPUs, logits stored into every GPU's buffer by the GEMV kernel "
-                                  "(peer stores + epoch flags, no collective)" if world > 1 else ""),
+                                  "(peer stores + epoch flags, no collective)" if fused_used else
+                                  f", rows sharded over {world} GPUs + NCCL all-gather ({fused_note})" if world > 1 else ""),
                    "l2": "inputs larger than L2 (compressed matrix %.0f MB per GPU)" % (shard_bytes / 1e6),
                    "compressed_bytes": total_weight_bytes, "bf16_bytes": rows * K * 2,
                    "ratio": total_weight_bytes / (rows * K * 2)},
@@ -454,6 +469,10 @@ def run_moe_decode(args):
         a = torch.empty(T, 512, device=dev)
 
         side = torch.cuda.Stream()
+        fmd = None
+        if world > 1:
+            from orin_qwen_lossless_b200 import sharded
+            fmd = sharded.FusedMoeDecode(gate, up, down, E, k, T)
 
         def step():
             # the shared expert does not depend on the routed experts: it runs on a second stream (a parallel branch of
@@ -464,6 +483,13 @@ def run_moe_decode(args):
                 with torch.cuda.stream(side):
                     ops._mmv_common(xs[i], sh_gu, None, 0, False, True, True, a)   # shared expert: merged gate|up GLU
                     ops.mmv(a, sh_down, out=ysh)
+                if fmd and not args.nccl:
+                    # expert-parallel, no collective: the combine kernel stores the partial output into every rank and
+                    # waits for the peers'; one small kernel adds the partials and the shared expert
+                    fmd(xs[i], logits[i], y, None, wts[i], ids[i])
+                    main.wait_stream(side)
+                    y.add_(ysh)
+                    continue
                 ops.moe_decode(xs[i], gate, up, down, E, k, router_logits=logits[i], topk_weights=wts[i], topk_ids=ids[i],
                                scratch=scratch, out=y, expert_lo=rank * n_local, n_experts_local=n_local)
                 main.wait_stream(side)
@@ -480,10 +506,13 @@ def run_moe_decode(args):
         nbytes = distinct * per_expert + sh_gu.nbytes + sh_down.nbytes
         if rank == 0:
             print(json.dumps({"workload": f"MoE decode layer, {T} token(s), 256 experts top-8 + shared expert", "n_gpus": world,
-                              "parallelism": "1 GPU" if world == 1 else f"expert-parallel over {world} GPUs + NCCL all-reduce",
+                              "parallelism": "1 GPU" if world == 1 else f"expert-parallel over {world} GPUs + NCCL all-reduce" if args.nccl
+                              else f"expert-parallel over {world} GPUs, partial outputs stored into every GPU by the combine kernel, no collective",
                               "us_per_layer": us, "distinct_experts": distinct, "compressed_bytes": nbytes,
                               "GBps": nbytes / us / 1e3, "frac_of_measured_hbm": nbytes / us / 1e3 / peak / world,
                               "launches_per_layer": 7 + (world > 1)}), flush=True)
+        if fmd:
+            fmd.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -545,6 +574,7 @@ def main():
     ap.add_argument("--rows", type=int, default=ROWS, help="rows of the matrix (default: the vocabulary projection)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cublas", action="store_true", help="also time a stock BF16 GEMV of the uncompressed matrix")
+    ap.add_argument("--nccl", action="store_true", help="N > 1, moe_decode: all-reduce with NCCL instead of the fused peer stores")
     ap.add_argument("--workload", default="lm_head", choices=["lm_head", "small", "moe_decode", "moe_prefill"],
                     help="lm_head is the headline contract line; the others print extra lines for the other baseline configs "
                          "(small: 1 GPU; the MoE workloads run expert-parallel under torchrun)")

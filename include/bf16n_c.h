@@ -209,6 +209,16 @@ int bf16n_mmv_peers(const bf16n_weight * w, const bf16n_mmv_args * a, const bf16
 /* Waits on the stream until every peer in rank_mask (bit r = rank r) has announced its next epoch; bounded (about two
  * seconds), after which header word 19 is set and the stream continues. */
 int bf16n_peer_wait(uint32_t * local_header, int rank_mask, void * stream);
+/* bf16n_moe_decode on an expert-parallel rank whose last kernel (the slot-order combine) also stores the rank's partial
+ * [n_tok, H] output into every peer (y and peers->y[r] are this rank's slot in the exchange payloads), announces it and,
+ * with peers->wait_mask, ends only when the peers' partial outputs have arrived. */
+int bf16n_moe_decode_peers(const bf16n_weight * gate, const bf16n_weight * up, const bf16n_weight * down, const void * x, int x_bf16,
+                           int64_t x_tok, const float * router_logits, int n_experts, int32_t * topk_ids, float * topk_weights,
+                           int n_tok, int n_used, int expert_lo, int n_experts_local, float * scratch, size_t scratch_bytes,
+                           void * y, int y_bf16, const bf16n_peer_out * peers, void * stream);
+/* y[i] = parts[0][i] + ... + parts[n_parts-1][i] (+ extra[i] when extra is not null): the ranks' partial outputs added
+ * in rank order, so that every rank gets the same bits. parts: n_parts consecutive arrays of n floats. */
+int bf16n_peer_sum(const float * parts, int n_parts, int64_t n, const float * extra, void * y, int y_bf16, void * stream);
 /* Synchronises the stream and returns header word 19 (non-zero: a wait expired since the buffer was created). */
 int bf16n_peer_expired(const uint32_t * local_header, void * stream, int * expired);
 

@@ -72,6 +72,10 @@ SIGNATURES = {
     "bf16n_exchange_close": (C.c_int, [C.c_void_p]),
     "bf16n_exchange_destroy": (C.c_int, [C.c_void_p]),
     "bf16n_mmv_peers": (C.c_int, [C.POINTER(Weight), C.POINTER(MmvArgs), C.POINTER(PeerOut), C.c_void_p]),
+    "bf16n_moe_decode_peers": (C.c_int, [C.POINTER(Weight), C.POINTER(Weight), C.POINTER(Weight), C.c_void_p, C.c_int, C.c_int64, C.c_void_p,
+                                         C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t,
+                                         C.c_void_p, C.c_int, C.POINTER(PeerOut), C.c_void_p]),
+    "bf16n_peer_sum": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "bf16n_peer_wait": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "bf16n_peer_expired": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
 }

@@ -277,26 +277,60 @@ size_t bf16n_moe_decode_scratch_bytes(int n_tok, int n_used, int64_t rows_gate, 
     return (size_t) n_tok * n_used * (2 * rows_gate + rows_down) * sizeof(float);
 }
 
+static void moe_decode_checked(const bf16n_weight * gate, const bf16n_weight * up, const bf16n_weight * down, const void * x, int x_bf16,
+                               int64_t x_tok, const float * router_logits, int n_experts, int32_t * topk_ids, float * topk_weights,
+                               int n_tok, int n_used, int expert_lo, int n_experts_local, float * scratch, size_t scratch_bytes,
+                               void * y, int y_bf16, void * stream, const bf16n_peer_out * peers) {
+    ensure_init();
+    check_weight(*gate); check_weight(*up); check_weight(*down);
+    require(moe_decode_supported(*gate, *up, *down),
+            "moe_decode: gate/up must be chunk-major HUFPAIR R = 8 K = 2048 and down row-major HUFPAIR R = 16 K = 512");
+    require(n_tok >= 0 && n_tok <= 64 && n_used > 0 && n_used <= 32, "moe_decode: 0..64 tokens, 1..32 slots");
+    require(n_experts_local > 0 && expert_lo >= 0 && expert_lo + n_experts_local <= n_experts, "moe_decode: expert slice out of range");
+    require(gate->rows % n_experts_local == 0 && down->rows % n_experts_local == 0, "rows must split evenly into experts");
+    const int64_t N = gate->rows / n_experts_local, H = down->rows / n_experts_local;
+    require(N == down->K && H % down->R == 0 && N % gate->R == 0, "moe_decode: down's K must equal the gate/up rows per expert");
+    require(scratch_bytes >= bf16n_moe_decode_scratch_bytes(n_tok, n_used, N, H), "moe_decode: scratch too small");
+    require((uintptr_t) x % 16 == 0 && x_tok % 16 == 0 && (uintptr_t) scratch % 16 == 0, "moe_decode: x, its row stride and scratch must be 16-byte aligned");
+    if (peers) {
+        require(n_tok > 0, "moe_decode_peers: empty step (every rank must announce)");
+        require(peers->n_peers >= 0 && peers->n_peers <= BF16N_MAX_PEERS && peers->wait_mask >= 0 && peers->wait_mask < 256,
+                "moe_decode_peers: 0..7 peers, wait_mask over ranks 0..7");
+        require(peers->n_peers == 0 || peers->local_header, "moe_decode_peers: the local exchange header is missing");
+        for (int r = 0; r < peers->n_peers; r++) { require(peers->y[r] && peers->flag[r], "moe_decode_peers: null peer pointer"); }
+    }
+    if (n_tok == 0) { return; }
+    if (router_logits) { moe_topk(router_logits, n_tok, n_experts, n_used, topk_ids, topk_weights, (cudaStream_t) stream); }
+    moe_decode(*gate, *up, *down, x, x_bf16 != 0, x_tok, topk_ids, topk_weights, n_tok, n_used, n_experts_local, expert_lo,
+               scratch, y, y_bf16 != 0, (cudaStream_t) stream, peers);
+}
+
 int bf16n_moe_decode(const bf16n_weight * gate, const bf16n_weight * up, const bf16n_weight * down, const void * x, int x_bf16,
                      int64_t x_tok, const float * router_logits, int n_experts, int32_t * topk_ids, float * topk_weights, int n_tok,
                      int n_used, int expert_lo, int n_experts_local, float * scratch, size_t scratch_bytes, void * y, int y_bf16,
                      void * stream) {
     return guarded([&] {
-        ensure_init();
-        check_weight(*gate); check_weight(*up); check_weight(*down);
-        require(moe_decode_supported(*gate, *up, *down),
-                "moe_decode: gate/up must be chunk-major HUFPAIR R = 8 K = 2048 and down row-major HUFPAIR R = 16 K = 512");
-        require(n_tok >= 0 && n_tok <= 64 && n_used > 0 && n_used <= 32, "moe_decode: 0..64 tokens, 1..32 slots");
-        require(n_experts_local > 0 && expert_lo >= 0 && expert_lo + n_experts_local <= n_experts, "moe_decode: expert slice out of range");
-        require(gate->rows % n_experts_local == 0 && down->rows % n_experts_local == 0, "rows must split evenly into experts");
-        const int64_t N = gate->rows / n_experts_local, H = down->rows / n_experts_local;
-        require(N == down->K && H % down->R == 0 && N % gate->R == 0, "moe_decode: down's K must equal the gate/up rows per expert");
-        require(scratch_bytes >= bf16n_moe_decode_scratch_bytes(n_tok, n_used, N, H), "moe_decode: scratch too small");
-        require((uintptr_t) x % 16 == 0 && x_tok % 16 == 0 && (uintptr_t) scratch % 16 == 0, "moe_decode: x, its row stride and scratch must be 16-byte aligned");
-        if (n_tok == 0) { return; }
-        if (router_logits) { moe_topk(router_logits, n_tok, n_experts, n_used, topk_ids, topk_weights, (cudaStream_t) stream); }
-        moe_decode(*gate, *up, *down, x, x_bf16 != 0, x_tok, topk_ids, topk_weights, n_tok, n_used, n_experts_local, expert_lo,
-                   scratch, y, y_bf16 != 0, (cudaStream_t) stream);
+        moe_decode_checked(gate, up, down, x, x_bf16, x_tok, router_logits, n_experts, topk_ids, topk_weights, n_tok, n_used, expert_lo,
+                           n_experts_local, scratch, scratch_bytes, y, y_bf16, stream, nullptr);
+    });
+}
+
+int bf16n_moe_decode_peers(const bf16n_weight * gate, const bf16n_weight * up, const bf16n_weight * down, const void * x, int x_bf16,
+                           int64_t x_tok, const float * router_logits, int n_experts, int32_t * topk_ids, float * topk_weights,
+                           int n_tok, int n_used, int expert_lo, int n_experts_local, float * scratch, size_t scratch_bytes,
+                           void * y, int y_bf16, const bf16n_peer_out * peers, void * stream) {
+    return guarded([&] {
+        require(peers != nullptr, "moe_decode_peers: peers is null");
+        moe_decode_checked(gate, up, down, x, x_bf16, x_tok, router_logits, n_experts, topk_ids, topk_weights, n_tok, n_used, expert_lo,
+                           n_experts_local, scratch, scratch_bytes, y, y_bf16, stream, peers);
+    });
+}
+
+int bf16n_peer_sum(const float * parts, int n_parts, int64_t n, const float * extra, void * y, int y_bf16, void * stream) {
+    return guarded([&] {
+        require(parts && y && n_parts >= 1 && n_parts <= 8 && n >= 0, "peer_sum: 1..8 parts");
+        if (n == 0) { return; }
+        peer_sum(parts, n_parts, n, extra, y, y_bf16 != 0, (cudaStream_t) stream);
     });
 }
 

@@ -106,42 +106,46 @@ struct Cols {
     PeerOut peers;
 };
 
+// value i of the output column that starts `col_bytes` into y, to every peer
+__device__ __forceinline__ void peers_put(const PeerOut & o, int64_t col_bytes, bool bf16, int64_t i, float v) {
+    for (int r = 0; r < o.n; r++) {
+        char * q = o.y[r] + col_bytes;
+        if (bf16) { ((__nv_bfloat16 *) q)[i] = __float2bfloat16_rn(v); } else { ((float *) q)[i] = v; }
+    }
+}
 // value i of dense column `col`, to every peer
 __device__ __forceinline__ void peers_put(const Cols & c, int col, int64_t i, float v) {
-    for (int r = 0; r < c.peers.n; r++) {
-        char * q = c.peers.y[r] + col * c.y_tok;
-        if (c.y_bf16) { ((__nv_bfloat16 *) q)[i] = __float2bfloat16_rn(v); } else { ((float *) q)[i] = v; }
-    }
+    peers_put(c.peers, col * c.y_tok, c.y_bf16, i, v);
 }
 // End of a kernel that fans out: call with every thread of the block that is still running. Each block makes its
 // stores visible system-wide and counts itself; the last one advances this rank's epoch and publishes it to the peers
 // (release), whose bf16n_peer_wait acquires it.
-__device__ __forceinline__ void peers_done(const Cols & c) {
-    if (c.peers.n == 0) { return; }
+__device__ __forceinline__ void peers_done(const PeerOut & o) {
+    if (o.n == 0) { return; }
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence_system();
         const unsigned blocks = gridDim.x * gridDim.y * gridDim.z;
-        if (atomicAdd(c.peers.hdr + XH_DONE, 1u) == blocks - 1u) {
-            c.peers.hdr[XH_DONE] = 0u;
-            const uint32_t epoch = c.peers.hdr[XH_SENT] + 1u;
-            c.peers.hdr[XH_SENT] = epoch;
+        if (atomicAdd(o.hdr + XH_DONE, 1u) == blocks - 1u) {
+            o.hdr[XH_DONE] = 0u;
+            const uint32_t epoch = o.hdr[XH_SENT] + 1u;
+            o.hdr[XH_SENT] = epoch;
             __threadfence_system();
-            for (int r = 0; r < c.peers.n; r++) {
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(c.peers.flag[r]), "r"(epoch) : "memory");
+            for (int r = 0; r < o.n; r++) {
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(o.flag[r]), "r"(epoch) : "memory");
             }
             // Optionally the kernel also stands in for the consumer's wait: it ends only when the peers' outputs of the
             // same epoch have arrived here. A peer publishes before it waits, so no rank waits for a rank that waits
             // for it. Bounded: after about two seconds the header's expired word is set and the kernel ends anyway.
-            if (c.peers.wait_mask) {
+            if (o.wait_mask) {
                 uint64_t t0 = 0;
                 bool all = false;
                 for (uint32_t i = 0; i < (1u << 26) && !all; i++) {
                     all = true;
                     for (int r = 0; r < 8; r++) {
-                        if (c.peers.wait_mask >> r & 1) {
+                        if (o.wait_mask >> r & 1) {
                             uint32_t seen;
-                            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(c.peers.hdr + r) : "memory");
+                            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(o.hdr + r) : "memory");
                             all = all && (int32_t) (seen - epoch) >= 0;
                         }
                     }
@@ -151,13 +155,14 @@ __device__ __forceinline__ void peers_done(const Cols & c) {
                         if (t0 == 0) { t0 = now; } else if (now - t0 > 2000000000ull) { break; }
                     }
                 }
-                if (!all) { c.peers.hdr[XH_EXPIRED] = 1u; }
-                c.peers.hdr[XH_WAITED] = epoch;
+                if (!all) { o.hdr[XH_EXPIRED] = 1u; }
+                o.hdr[XH_WAITED] = epoch;
                 __threadfence_system();
             }
         }
     }
 }
+__device__ __forceinline__ void peers_done(const Cols & c) { peers_done(c.peers); }
 
 // activation pointer, output column and first weight row of column `col`
 template <typename TX>
@@ -389,17 +394,23 @@ inline NibView nib_view(const bf16n_weight & w, int64_t shift_rows = 0) {
             (const uint32_t *) (w.aux + w.off_c) + shift_rows, (const uint32_t *) (w.aux + w.off_d)};
 }
 
+inline PeerOut make_peer_out(const bf16n_peer_out * peers) {
+    PeerOut o = {};
+    if (peers) {
+        o.n = peers->n_peers;
+        for (int r = 0; r < peers->n_peers && r < MAX_PEERS; r++) {
+            o.y[r] = (char *) peers->y[r];
+            o.flag[r] = peers->flag[r];
+        }
+        o.hdr = peers->local_header;
+        o.wait_mask = peers->wait_mask;
+    }
+    return o;
+}
+
 inline Cols make_cols(const bf16n_mmv_args & a, const bf16n_peer_out * peers = nullptr) {
     Cols c = {};
-    if (peers) {
-        c.peers.n = peers->n_peers;
-        for (int r = 0; r < peers->n_peers && r < MAX_PEERS; r++) {
-            c.peers.y[r] = (char *) peers->y[r];
-            c.peers.flag[r] = peers->flag[r];
-        }
-        c.peers.hdr = peers->local_header;
-        c.peers.wait_mask = peers->wait_mask;
-    }
+    c.peers = make_peer_out(peers);
     c.x = (const char *) a.x; c.y = (char *) a.y;
     c.x_tok = a.x_tok; c.y_tok = a.y_tok; c.x_slot = a.x_slot; c.y_slot = a.y_slot;
     c.ids = (const char *) a.ids; c.ids_s0 = a.ids_s0; c.ids_s1 = a.ids_s1;

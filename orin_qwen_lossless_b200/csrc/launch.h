@@ -83,7 +83,8 @@ void moe_decode_init();
 bool moe_decode_supported(const bf16n_weight & gate, const bf16n_weight & up, const bf16n_weight & down);
 void moe_decode(const bf16n_weight & gate, const bf16n_weight & up, const bf16n_weight & down, const void * x, bool x_bf16,
                 int64_t x_tok, const int32_t * ids, const float * weights, int n_tok, int n_used, int n_experts_local, int e_lo,
-                float * scratch, void * y, bool y_bf16, cudaStream_t st);
+                float * scratch, void * y, bool y_bf16, cudaStream_t st, const bf16n_peer_out * peers = nullptr);
+void peer_sum(const float * parts, int n_parts, int64_t n, const float * extra, void * y, bool y_bf16, cudaStream_t st);
 
 size_t moe_decode_static_capacity_floats();
 void moe_decode_static(const bf16n_weight & gate, const bf16n_weight & up, const bf16n_weight & down, const void * x, bool x_bf16,

@@ -186,7 +186,7 @@ __global__ void __launch_bounds__(256) k_expert_units(const ExpertMat m0, const 
 
 // y[t, i] = sum over slots, in slot order, of w[t, k] * ys[t, k, i]
 __global__ void k_combine_f32(const float * __restrict__ ys, const float * __restrict__ w, char * __restrict__ y, bool y_bf16, int n_used,
-                              int64_t n) {
+                              int64_t n, const PeerOut peers) {
     grid_dependency_wait();
     const int t = blockIdx.y;
     const OutVec out = {y + (int64_t) t * n * (y_bf16 ? 2 : 4), y_bf16};
@@ -196,6 +196,21 @@ __global__ void k_combine_f32(const float * __restrict__ ys, const float * __res
             const int64_t s = (int64_t) t * n_used + kx;
             acc = fmaf(w[s], ys[s * n + i], acc);
         }
+        out.put(i, acc);
+        peers_put(peers, (int64_t) t * n * (y_bf16 ? 2 : 4), y_bf16, i, acc);
+    }
+    peers_done(peers); // expert-parallel ranks: the partial output also went to every peer; announce it and await theirs
+}
+
+// y[i] = parts[0][i] + parts[1][i] + ... (+ extra[i]): the ranks' partial outputs in rank order, the same on every rank
+__global__ void k_peer_sum(const float * __restrict__ parts, int n_parts, int64_t n, const float * __restrict__ extra,
+                           char * __restrict__ y, bool y_bf16) {
+    grid_dependency_wait();
+    const OutVec out = {y, y_bf16};
+    for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) {
+        float acc = parts[i];
+        for (int r = 1; r < n_parts; r++) { acc += parts[(int64_t) r * n + i]; }
+        if (extra) { acc += extra[i]; }
         out.put(i, acc);
     }
 }
@@ -266,7 +281,7 @@ void moe_decode_init() {
 // scratch: FP32 [2 * n_tok * n_used * N + n_tok * n_used * H] (N, H = rows per expert of gate and down).
 void moe_decode(const bf16n_weight & gate, const bf16n_weight & up, const bf16n_weight & down, const void * x, bool x_bf16,
                 int64_t x_tok, const int32_t * ids, const float * weights, int n_tok, int n_used, int n_experts_local, int e_lo,
-                float * scratch, void * y, bool y_bf16, cudaStream_t st) {
+                float * scratch, void * y, bool y_bf16, cudaStream_t st, const bf16n_peer_out * peers) {
     const int64_t N = gate.rows / n_experts_local, H = down.rows / n_experts_local;
     const int ncols = n_tok * n_used;
     float * g = scratch, * u = g + (int64_t) ncols * N, * ys = u + (int64_t) ncols * N;
@@ -285,7 +300,12 @@ void moe_decode(const bf16n_weight & gate, const bf16n_weight & up, const bf16n_
     q.rows_per_expert = H; q.cap_bytes = unit_cap(down);
     launch_units<1, 16, false, float, true>(expert_mat(down, ys), expert_mat(down, ys), 1, q, ncols, st);
     const dim3 grid((unsigned) std::min<int64_t>((H + 255) / 256, 64), (unsigned) n_tok);
-    launch_chained(k_combine_f32, grid, dim3(256), 0, st, ys, weights, (char *) y, y_bf16, n_used, H);
+    launch_chained(k_combine_f32, grid, dim3(256), 0, st, ys, weights, (char *) y, y_bf16, n_used, H, make_peer_out(peers));
+}
+
+void peer_sum(const float * parts, int n_parts, int64_t n, const float * extra, void * y, bool y_bf16, cudaStream_t st) {
+    const unsigned blocks = (unsigned) std::min<int64_t>((n + 255) / 256, 256);
+    launch_chained(k_peer_sum, dim3(blocks), dim3(256), 0, st, parts, n_parts, n, extra, (char *) y, y_bf16);
     check_launch();
 }
 

@@ -479,10 +479,11 @@ def moe_decode(x: torch.Tensor, gate: Weight, up: Weight, down: Weight, n_expert
                router_logits: torch.Tensor | None = None, topk_weights: torch.Tensor | None = None,
                topk_ids: torch.Tensor | None = None, expert_lo: int = 0, n_experts_local: int | None = None,
                scratch: torch.Tensor | None = None, out: torch.Tensor | None = None,
-               out_dtype: torch.dtype = torch.float32):
+               out_dtype: torch.dtype = torch.float32, peers=None):
     """One MoE decode step of the routed experts in four launches (router, gate+up, down with SwiGLU on load,
     combine). Either router_logits (FP32 [T, n_experts]) or topk_weights / topk_ids (FP32 / int32 [T, top_k]) is given.
     The weights hold experts [expert_lo, expert_lo + n_experts_local); other slots add zeros (expert parallelism).
+    peers (a bf16n_peer_out): the combine also stores y into the peers' exchange buffers and announces it.
     Returns (y [T, H], topk_weights, topk_ids)."""
     cg, cu, cd = gate.c(), up.c(), down.c()
     _check_x(x, gate.meta.K)
@@ -504,9 +505,12 @@ def moe_decode(x: torch.Tensor, gate: Weight, up: Weight, down: Weight, n_expert
     if scratch is None:
         scratch = moe_decode_scratch(T, top_k, gate, down, n_local, dev)
     y = torch.empty((T, H), dtype=out_dtype, device=dev) if out is None else out
+    args = (C.byref(cg), C.byref(cu), C.byref(cd), x.data_ptr(), int(x.dtype == torch.bfloat16), x.stride(0) * x.element_size(),
+            router_logits.data_ptr() if router_logits is not None else None, n_experts, topk_ids.data_ptr(), topk_weights.data_ptr(),
+            T, top_k, expert_lo, n_local, scratch.data_ptr(), scratch.numel() * 4, y.data_ptr(), int(y.dtype == torch.bfloat16))
     with torch.cuda.device(dev):
-        check(lib().bf16n_moe_decode(C.byref(cg), C.byref(cu), C.byref(cd), x.data_ptr(), int(x.dtype == torch.bfloat16),
-                                     x.stride(0) * x.element_size(), router_logits.data_ptr() if router_logits is not None else None,
-                                     n_experts, topk_ids.data_ptr(), topk_weights.data_ptr(), T, top_k, expert_lo, n_local,
-                                     scratch.data_ptr(), scratch.numel() * 4, y.data_ptr(), int(y.dtype == torch.bfloat16), _stream()))
+        if peers is None:
+            check(lib().bf16n_moe_decode(*args, _stream()))
+        else:
+            check(lib().bf16n_moe_decode_peers(*args, C.byref(peers), _stream()))
     return y, topk_weights, topk_ids

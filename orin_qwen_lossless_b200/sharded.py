@@ -274,6 +274,45 @@ def moe_decode_ep(x, gate, up, down, n_experts, top_k, router_logits, group=None
     return y, wts, ids
 
 
+class FusedMoeDecode:
+    """Expert-parallel decode step without a collective: the step's last kernel (the slot-order combine) stores this
+    rank's partial [T, H] output into every rank's exchange buffer, announces it and ends when the peers' partials have
+    arrived; one small kernel then adds the partials in rank order (the same bits on every rank) plus an optional extra
+    term (the shared expert). Two buffers alternate as in FusedShardedLinear."""
+
+    def __init__(self, gate, up, down, n_experts: int, top_k: int, max_tokens: int, group=None):
+        self.gate, self.up, self.down, self.E, self.k, self.T = gate, up, down, n_experts, top_k, max_tokens
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.n_local = n_experts // self.world
+        self.H = down.meta.rows // self.n_local
+        self.area = self.world * max_tokens * self.H * 4
+        self.xchg = PeerExchange(2 * self.area, group)
+        self.step = 0
+        slot = self.rank * max_tokens * self.H * 4
+        self._views = [self.xchg.payload(b * self.area, (self.world, max_tokens, self.H), torch.float32) for b in range(2)]
+        self._outs = [self.xchg.peer_out(b * self.area + slot, wait=True) for b in range(2)]
+        self.scratch = ops.moe_decode_scratch(max_tokens, top_k, gate, down, self.n_local, gate.plane.device)
+
+    def __call__(self, x, router_logits, out, extra=None, topk_weights=None, topk_ids=None):
+        """x [T, K], router_logits [T, E] (both replicated) -> out [T, H] = sum over ranks of the routed experts' output
+        (+ extra [T, H] FP32). T == max_tokens."""
+        if x.shape[0] != self.T:
+            raise RuntimeError("bf16n FusedMoeDecode: built for a fixed number of tokens")
+        b = self.step & 1
+        self.step += 1
+        _, wts, ids = ops.moe_decode(x, self.gate, self.up, self.down, self.E, self.k, router_logits=router_logits,
+                                     topk_weights=topk_weights, topk_ids=topk_ids, expert_lo=self.rank * self.n_local,
+                                     n_experts_local=self.n_local, scratch=self.scratch, out=self._views[b][self.rank],
+                                     peers=self._outs[b])
+        parts = self._views[b]
+        check(lib().bf16n_peer_sum(parts.data_ptr(), self.world, self.T * self.H, extra.data_ptr() if extra is not None else None,
+                                   out.data_ptr(), int(out.dtype == torch.bfloat16), ops._stream()))
+        return out, wts, ids
+
+    def close(self) -> None:
+        self.xchg.close()
+
+
 # ------------------------------------------------------------------ MoE prefill: expert-parallel + all-to-all dispatch
 
 def dispatch_plan(topk_ids: torch.Tensor, n_experts: int, world: int):

@@ -91,6 +91,29 @@ def _worker(rank, world, port, ret):
         y_ep, _, _ = sharded.moe_decode_ep(xt, gl, ul, dl, E, TOPK, logits)
         y_1, wts, ids = ops.moe_decode(xt, g, u, d, E, TOPK, router_logits=logits)
         ok2 = bool(torch.allclose(y_ep, y_1, rtol=0, atol=2.0 ** -17 * float(y_1.abs().max()) * TOPK))
+        # 2b. the same step with the all-reduce fused away: the combine kernel stores the partial output into every rank,
+        # a small kernel adds the partials in rank order (every rank gets the same bits), eager and from a CUDA graph
+        fmd = sharded.FusedMoeDecode(gl, ul, dl, E, TOPK, T)
+        extra = torch.from_numpy(np.random.default_rng(8).standard_normal((T, H)).astype(np.float32)).to(dev)
+        y_f = torch.empty((T, H), device=dev)
+        for _ in range(3):
+            fmd(xt, logits, y_f, extra)
+        tol = 2.0 ** -17 * float(y_1.abs().max()) * TOPK
+        ok2 = ok2 and bool(torch.allclose(y_f - extra, y_1, rtol=0, atol=tol))
+        both = [torch.empty_like(y_f) for _ in range(world)]
+        dist.all_gather(both, y_f)
+        ok2 = ok2 and all(bool(torch.equal(b_, y_f)) for b_ in both)
+        torch.cuda.synchronize()
+        gr2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr2):
+            for _ in range(2):
+                fmd(xt, logits, y_f, extra)
+        want_f = y_f.clone()
+        y_f.zero_()
+        gr2.replay()
+        torch.cuda.synchronize()
+        ok2 = ok2 and bool(torch.equal(y_f, want_f)) and not fmd.xchg.expired()
+        fmd.close()
 
         # 3. MoE prefill: tokens split over the ranks, all-to-all dispatch to the experts' ranks
         Tp = 40 + 8 * rank
