@@ -486,9 +486,7 @@ def run_moe_decode(args):
                 if fmd and not args.nccl:
                     # expert-parallel, no collective: the combine kernel stores the partial output into every rank and
                     # waits for the peers'; one small kernel adds the partials and the shared expert
-                    fmd(xs[i], logits[i], y, None, wts[i], ids[i])
-                    main.wait_stream(side)
-                    y.add_(ysh)
+                    fmd(xs[i], logits[i], y, ysh, wts[i], ids[i], join=side)
                     continue
                 ops.moe_decode(xs[i], gate, up, down, E, k, router_logits=logits[i], topk_weights=wts[i], topk_ids=ids[i],
                                scratch=scratch, out=y, expert_lo=rank * n_local, n_experts_local=n_local)

@@ -293,9 +293,9 @@ class FusedMoeDecode:
         self._outs = [self.xchg.peer_out(b * self.area + slot, wait=True) for b in range(2)]
         self.scratch = ops.moe_decode_scratch(max_tokens, top_k, gate, down, self.n_local, gate.plane.device)
 
-    def __call__(self, x, router_logits, out, extra=None, topk_weights=None, topk_ids=None):
+    def __call__(self, x, router_logits, out, extra=None, topk_weights=None, topk_ids=None, join=None):
         """x [T, K], router_logits [T, E] (both replicated) -> out [T, H] = sum over ranks of the routed experts' output
-        (+ extra [T, H] FP32). T == max_tokens."""
+        (+ extra [T, H] FP32). T == max_tokens. join: a stream the final sum waits for (the one that produces extra)."""
         if x.shape[0] != self.T:
             raise RuntimeError("bf16n FusedMoeDecode: built for a fixed number of tokens")
         b = self.step & 1
@@ -305,6 +305,8 @@ class FusedMoeDecode:
                                      n_experts_local=self.n_local, scratch=self.scratch, out=self._views[b][self.rank],
                                      peers=self._outs[b])
         parts = self._views[b]
+        if join is not None:
+            torch.cuda.current_stream().wait_stream(join)
         check(lib().bf16n_peer_sum(parts.data_ptr(), self.world, self.T * self.H, extra.data_ptr() if extra is not None else None,
                                    out.data_ptr(), int(out.dtype == torch.bfloat16), ops._stream()))
         return out, wts, ids
