@@ -35,7 +35,7 @@ __device__ __forceinline__ void stage_lut(uint32_t * dst, const uint32_t * src, 
 // ---------------------------------------------------------------- HUFPAIR, row-major units
 
 // NC dense columns (NC == 1: also routed columns, one per blockIdx.y). XR: the lane's activations live in registers.
-template <int C, int NC, typename TX, bool XR>
+template <int C, int NC, typename TX, bool XR, bool PEERS = false>
 __global__ void __launch_bounds__(512) k_pair_gemv(const PairView w, int R, Cols p) {
     constexpr int K = C * CHUNK;
     extern __shared__ __align__(16) unsigned char smem[];
@@ -98,12 +98,12 @@ __global__ void __launch_bounds__(512) k_pair_gemv(const PairView w, int R, Cols
                     OutVec o = out;
                     o.p += n * p.y_tok;
                     o.put(u * R + rr, s);
-                    if (NC == 1) { peers_put(p, blockIdx.y, u * R + rr, s); }
+                    if (PEERS) { peers_put(p, blockIdx.y, u * R + rr, s); }
                 }
             }
         }
     }
-    if (NC == 1) { peers_done(p); }
+    if (PEERS) { peers_done(p); }
 }
 
 // y = silu(gate x) * (up x), separate row-major gate / up matrices with the same geometry
@@ -295,6 +295,11 @@ __device__ __forceinline__ float nib_dot(const NibRow<C> & d, const NibView & w,
 // GLU: g rows are the gate, v rows the up half (separate matrices, or the same matrix shifted by nrows rows)
 template <int C, typename TX, bool GLU>
 __global__ void __launch_bounds__(256) k_nib_gemv(const NibView g, const NibView v, Cols p) {
+    // Launched as a programmatic dependent (launch_chained): a warp fetches its first row's weights while the kernel
+    // before it on the stream is still draining, and waits for that kernel only before it reads activations or writes
+    // outputs (expert ids, when there are any, belong to an earlier kernel too).
+    bool waited = p.ids != nullptr;
+    if (waited) { grid_dependency_wait(); }
     const TX * xg; OutVec out; int64_t rbase;
     column<TX>(p, blockIdx.y, xg, out, rbase);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -302,6 +307,7 @@ __global__ void __launch_bounds__(256) k_nib_gemv(const NibView g, const NibView
         NibRow<C> dg, dv;
         nib_load<C>(dg, g, rbase + r, lane);
         if (GLU) { nib_load<C>(dv, v, rbase + r, lane); }
+        if (!waited) { grid_dependency_wait(); waited = true; }
         const float gs = nib_dot<C, TX>(dg, g, xg, lane);
         if (GLU) {
             const float vs = nib_dot<C, TX>(dv, v, xg, lane);
@@ -556,22 +562,32 @@ void launch_gemv(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t 
         } else {
             unit_geometry(units, a.ncols, 16, grid, threads);
             const size_t shm = 4 * HP_MAX_PAIRS + w.K * 4;
-            switch (C) {
-                case 1: k_pair_gemv<1, 1, TX, true><<<grid, threads, shm, st>>>(pair_view(w), w.R, p); break;
-                case 2: k_pair_gemv<2, 1, TX, true><<<grid, threads, shm, st>>>(pair_view(w), w.R, p); break;
-                case 4: k_pair_gemv<4, 1, TX, true><<<grid, threads, shm, st>>>(pair_view(w), w.R, p); break;
-                case 8: k_pair_gemv<8, 1, TX, false><<<grid, threads, shm, st>>>(pair_view(w), w.R, p); break;
-                default: fail_invalid("unsupported K");
+            if (p.peers.n) {
+                switch (C) {
+                    case 1: k_pair_gemv<1, 1, TX, true, true><<<grid, threads, shm, st>>>(pair_view(w), w.R, p); break;
+                    case 2: k_pair_gemv<2, 1, TX, true, true><<<grid, threads, shm, st>>>(pair_view(w), w.R, p); break;
+                    case 4: k_pair_gemv<4, 1, TX, true, true><<<grid, threads, shm, st>>>(pair_view(w), w.R, p); break;
+                    case 8: k_pair_gemv<8, 1, TX, false, true><<<grid, threads, shm, st>>>(pair_view(w), w.R, p); break;
+                    default: fail_invalid("unsupported K");
+                }
+            } else {
+                switch (C) {
+                    case 1: k_pair_gemv<1, 1, TX, true><<<grid, threads, shm, st>>>(pair_view(w), w.R, p); break;
+                    case 2: k_pair_gemv<2, 1, TX, true><<<grid, threads, shm, st>>>(pair_view(w), w.R, p); break;
+                    case 4: k_pair_gemv<4, 1, TX, true><<<grid, threads, shm, st>>>(pair_view(w), w.R, p); break;
+                    case 8: k_pair_gemv<8, 1, TX, false><<<grid, threads, shm, st>>>(pair_view(w), w.R, p); break;
+                    default: fail_invalid("unsupported K");
+                }
             }
         }
     } else if (w.format == FMT_NIBBLE) {
         const dim3 grid = row_geometry(a.nrows, a.ncols);
         const NibView v = nib_view(w);
         switch (C) {
-            case 1: k_nib_gemv<1, TX, false><<<grid, 256, 0, st>>>(v, v, p); break;
-            case 2: k_nib_gemv<2, TX, false><<<grid, 256, 0, st>>>(v, v, p); break;
-            case 4: k_nib_gemv<4, TX, false><<<grid, 256, 0, st>>>(v, v, p); break;
-            case 8: k_nib_gemv<8, TX, false><<<grid, 256, 0, st>>>(v, v, p); break;
+            case 1: launch_chained(k_nib_gemv<1, TX, false>, grid, dim3(256), 0, st, v, v, p); break;
+            case 2: launch_chained(k_nib_gemv<2, TX, false>, grid, dim3(256), 0, st, v, v, p); break;
+            case 4: launch_chained(k_nib_gemv<4, TX, false>, grid, dim3(256), 0, st, v, v, p); break;
+            case 8: launch_chained(k_nib_gemv<8, TX, false>, grid, dim3(256), 0, st, v, v, p); break;
             default: fail_invalid("unsupported K");
         }
     } else {
@@ -590,10 +606,10 @@ void launch_glu(const bf16n_weight & g, const NibView * up_nib, const bf16n_weig
         const dim3 grid = row_geometry(a.nrows, a.ncols);
         const NibView gv = nib_view(g), uv = up_nib ? *up_nib : nib_view(*u);
         switch (C) {
-            case 1: k_nib_gemv<1, TX, true><<<grid, 256, 0, st>>>(gv, uv, p); break;
-            case 2: k_nib_gemv<2, TX, true><<<grid, 256, 0, st>>>(gv, uv, p); break;
-            case 4: k_nib_gemv<4, TX, true><<<grid, 256, 0, st>>>(gv, uv, p); break;
-            case 8: k_nib_gemv<8, TX, true><<<grid, 256, 0, st>>>(gv, uv, p); break;
+            case 1: launch_chained(k_nib_gemv<1, TX, true>, grid, dim3(256), 0, st, gv, uv, p); break;
+            case 2: launch_chained(k_nib_gemv<2, TX, true>, grid, dim3(256), 0, st, gv, uv, p); break;
+            case 4: launch_chained(k_nib_gemv<4, TX, true>, grid, dim3(256), 0, st, gv, uv, p); break;
+            case 8: launch_chained(k_nib_gemv<8, TX, true>, grid, dim3(256), 0, st, gv, uv, p); break;
             default: fail_invalid("unsupported K");
         }
     } else if (g.format == FMT_HUFPAIR) {

@@ -143,7 +143,7 @@ __device__ __forceinline__ uint2 lds64_ro(uint32_t addr) {
 // One unit per warp, as many warps as the register file allows: the activations live in shared memory (BF16, natural
 // order: lane l's four activations of column quad j of chunk c are the 8 bytes at ((c*4 + j)*32 + l)*8, so every read
 // is base + immediate and conflict-free) and the plane is prefetched one row ahead chunk by chunk.
-template <int C, int NT>
+template <int C, int NT, bool PEERS = false> // PEERS: the output also goes to the other GPUs (a separate instantiation: the plain kernel carries none of it)
 __global__ void __launch_bounds__(NT, 1) k_pair_gemv_rings(const PairView w, int R, Cols p, const Opaque k) {
     constexpr int K = C * CHUNK;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -208,10 +208,10 @@ __global__ void __launch_bounds__(NT, 1) k_pair_gemv_rings(const PairView w, int
         }
         if (lane < R) {
             out.put(u * R + lane, mine);
-            peers_put(p, blockIdx.y, u * R + lane, mine);
+            if (PEERS) { peers_put(p, blockIdx.y, u * R + lane, mine); }
         }
     }
-    peers_done(p);
+    if (PEERS) { peers_done(p); }
 }
 
 constexpr int RING_SET = 32 * RING_BYTES;
@@ -226,6 +226,8 @@ void gemv_rings_init() {
 #define ATTR(KERNEL) cuda_ok(cudaFuncSetAttribute(KERNEL, cudaFuncAttributeMaxDynamicSharedMemorySize, optin), #KERNEL)
     ATTR((k_pair_gemv_rings<1, 896>)); ATTR((k_pair_gemv_rings<2, 896>)); ATTR((k_pair_gemv_rings<4, 896>));
     ATTR((k_pair_gemv_rings<4, 768>)); ATTR((k_pair_gemv_rings<4, 1024>));
+    ATTR((k_pair_gemv_rings<1, 896, true>)); ATTR((k_pair_gemv_rings<2, 896, true>)); ATTR((k_pair_gemv_rings<4, 896, true>));
+    ATTR((k_pair_gemv_rings<4, 768, true>)); ATTR((k_pair_gemv_rings<4, 1024, true>));
 #undef ATTR
     if (const char * e = getenv("BF16N_RINGS_WARPS")) { g_warps = atoi(e); }
 }
@@ -254,7 +256,8 @@ void gemv_rings(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t s
     const size_t shm = fixed_smem(w.K) + (size_t) best * RING_SET;
     const Opaque k = {1u, 4u, ~0u, 32u, 16u};
     const PairView v = pair_view(w);
-#define GO(CC, NT) k_pair_gemv_rings<CC, NT><<<grid, best * 32, shm, st>>>(v, w.R, p, k)
+#define GO(CC, NT) if (p.peers.n) { k_pair_gemv_rings<CC, NT, true><<<grid, best * 32, shm, st>>>(v, w.R, p, k); } \
+                   else { k_pair_gemv_rings<CC, NT, false><<<grid, best * 32, shm, st>>>(v, w.R, p, k); }
     if (w.K == 2048 && best > 28) { GO(4, 1024); }
     else if (w.K == 2048 && best <= 24) { GO(4, 768); }
     else { switch (w.K / CHUNK) { case 1: GO(1, 896); break; case 2: GO(2, 896); break; default: GO(4, 896); break; } }

@@ -56,7 +56,7 @@ __device__ __forceinline__ float unit_rows(Reader & rd, uint32_t lut, const Opaq
     return mine;
 }
 
-template <int C, typename TX>
+template <int C, typename TX, bool PEERS = false> // PEERS: the output also goes to the other GPUs (separate instantiation)
 __global__ void __launch_bounds__(512, 1) k_pair_gemv_staged(const PairView w, const AuxHeader * hdr, int R, Cols p, uint32_t cap_bytes,
                                                              const Opaque k) {
     extern __shared__ __align__(128) unsigned char smem[];
@@ -132,11 +132,11 @@ __global__ void __launch_bounds__(512, 1) k_pair_gemv_staged(const PairView w, c
         }
         if (lane < R) {
             out.put(u * R + lane, mine);
-            peers_put(p, blockIdx.y, u * R + lane, mine);
+            if (PEERS) { peers_put(p, blockIdx.y, u * R + lane, mine); }
         }
         cur = nxt;
     }
-    peers_done(p);
+    if (PEERS) { peers_done(p); }
 }
 
 constexpr int FIXED_SMEM = 4 * HP_MAX_PAIRS + 128;
@@ -151,6 +151,8 @@ void gemv_staged_init() {
 #define ATTR(KERNEL) cuda_ok(cudaFuncSetAttribute(KERNEL, cudaFuncAttributeMaxDynamicSharedMemorySize, optin), #KERNEL)
     ATTR((k_pair_gemv_staged<1, float>)); ATTR((k_pair_gemv_staged<2, float>)); ATTR((k_pair_gemv_staged<4, float>));
     ATTR((k_pair_gemv_staged<1, bf16>)); ATTR((k_pair_gemv_staged<2, bf16>)); ATTR((k_pair_gemv_staged<4, bf16>));
+    ATTR((k_pair_gemv_staged<1, float, true>)); ATTR((k_pair_gemv_staged<2, float, true>)); ATTR((k_pair_gemv_staged<4, float, true>));
+    ATTR((k_pair_gemv_staged<1, bf16, true>)); ATTR((k_pair_gemv_staged<2, bf16, true>)); ATTR((k_pair_gemv_staged<4, bf16, true>));
 #undef ATTR
 }
 
@@ -181,7 +183,8 @@ void gemv_staged(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t 
     const AuxHeader * hdr = (const AuxHeader *) w.aux;
     const PairView v = pair_view(w);
     const Opaque k = {1u, 4u, ~0u, 32u};
-#define GO(CC, TX) k_pair_gemv_staged<CC, TX><<<grid, best * 32, shm, st>>>(v, hdr, w.R, p, cap, k)
+#define GO(CC, TX) if (p.peers.n) { k_pair_gemv_staged<CC, TX, true><<<grid, best * 32, shm, st>>>(v, hdr, w.R, p, cap, k); } \
+                   else { k_pair_gemv_staged<CC, TX, false><<<grid, best * 32, shm, st>>>(v, hdr, w.R, p, cap, k); }
     if (a.x_bf16) {
         switch (w.K / CHUNK) { case 1: GO(1, bf16); break; case 2: GO(2, bf16); break; default: GO(4, bf16); break; }
     } else {
