@@ -44,6 +44,7 @@ void ensure_init() {
             moe_init();
             moe_decode_init();
             prefill_init();
+            fo_init();
         } catch (const std::exception & e) {
             g_init_status = BF16N_ECUDA;
             g_init_error = e.what();
@@ -62,7 +63,13 @@ void check_weight(const bf16n_weight & w) {
     require(((uintptr_t) w.plane | (uintptr_t) w.aux) % 16 == 0, "plane and aux must be 16-byte aligned");
 }
 void no_frag_order(const bf16n_weight & w) {
-    require(!w.fo, "fragment-order matrices have no kernels in this build");
+    require(!w.fo, "this operation has no kernel for fragment-order matrices");
+}
+// fragment-order matrices go to their own kernels (fo.cu): true when w is one (and checks that they can take it)
+bool frag_order(const bf16n_weight & w) {
+    if (!w.fo) { return false; }
+    require(fo_supported(w), "fragment order: HUFPAIR bands of 16 rows with K up to 4096");
+    return true;
 }
 void whole_units(const bf16n_weight & w, const bf16n_mmv_args & a) {
     require(w.format == FMT_NIBBLE || (a.nrows % w.R == 0 && a.row0 % w.R == 0 && a.rows_per_matrix % w.R == 0),
@@ -144,11 +151,11 @@ int bf16n_mmv(const bf16n_weight * w, const bf16n_mmv_args * a, void * stream, i
     return guarded([&] {
         ensure_init();
         check_weight(*w);
-        no_frag_order(*w);
         require(a->ncols > 0 && a->ncols <= 65535, "ncols out of range");
         whole_units(*w, *a);
         check_x(*w, *a);
         if (a->nrows == 0) { return; }
+        if (frag_order(*w)) { fo_gemv(*w, *a, (cudaStream_t) stream); return; }
         gemv(*w, *a, (cudaStream_t) stream, multi_col != 0);
     });
 }
@@ -189,10 +196,10 @@ int bf16n_dequant(const bf16n_weight * w, int64_t row0, int64_t nrows, uint16_t 
     return guarded([&] {
         ensure_init();
         check_weight(*w);
-        no_frag_order(*w);
         if (nrows == 0) { return; }
         require(row0 >= 0 && nrows > 0 && row0 + nrows <= w->rows, "dequant rows out of range");
         require(w->format == FMT_NIBBLE || (nrows % w->R == 0 && row0 % w->R == 0), "dequant rows must be whole units");
+        if (frag_order(*w)) { fo_expand_store(*w, row0, nrows, out, (cudaStream_t) stream); return; }
         expand_store(*w, row0, nrows, out, (cudaStream_t) stream);
     });
 }
@@ -202,11 +209,11 @@ int bf16n_verify(const bf16n_weight * w, int64_t row0, int64_t nrows, const uint
     return guarded([&] {
         ensure_init();
         check_weight(*w);
-        no_frag_order(*w);
         if (nrows == 0) { return; }
         require(row0 >= 0 && nrows > 0 && row0 + nrows <= w->rows, "verify rows out of range");
         require(w->format == FMT_NIBBLE || (nrows % w->R == 0 && row0 % w->R == 0), "verify rows must be whole units");
         require((uintptr_t) src % 8 == 0, "verify source must be 8-byte aligned");
+        if (frag_order(*w)) { fo_expand_compare(*w, row0, nrows, src, mismatches, (cudaStream_t) stream); return; }
         expand_compare(*w, row0, nrows, src, mismatches, (cudaStream_t) stream);
     });
 }
@@ -216,12 +223,12 @@ int bf16n_get_rows(const bf16n_weight * w, const void * ids, int64_t ids_s0, int
     return guarded([&] {
         ensure_init();
         check_weight(*w);
-        no_frag_order(*w);
         require(n >= 0, "get_rows: n must be nonnegative");
         require(row0 >= 0 && (n == 0 ? row0 <= w->rows : row0 < w->rows), "get_rows: row0 out of range");
         require(!w->cm, "get_rows of a chunk-major (expert) matrix");
         require(w->format != FMT_HUFFMAN, "get_rows is not implemented for the single-symbol Huffman format");
         if (n == 0) { return; }
+        if (frag_order(*w)) { fo_gather_rows(*w, ids, ids_s0, n, dst, dst_bf16 != 0, dst_s1, row0, (cudaStream_t) stream); return; }
         gather_rows(*w, ids, ids_s0, n, dst, dst_bf16 != 0, dst_s1, row0, (cudaStream_t) stream);
     });
 }

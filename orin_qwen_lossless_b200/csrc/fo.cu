@@ -1,0 +1,264 @@
+// Fragment-order HUFPAIR tensors (header flag 2, R = 16): exact reconstruction, row gather and the decode GEMV.
+//
+// Layout (core/src/encode.cpp:64-92, 387-394; docs/FORMAT.md "Fragment-order units"): rows come in bands of 16, a unit is
+// one 512-column slab of a band (unit = band * K/512 + slab). Inside a slab the 16 x 16 tiles kt = 0..31 are walked in
+// order; lane l owns, of every tile, the four column pairs q = 0..3 at row (l >> 2) + 8 * (q & 1), columns
+// 2 * (l & 3) + 8 * (q >> 1) + {0, 1} (the A-operand registers of mma.m16n8k16). Its stream holds the pair symbols in the
+// order tiles -> q; its plane bytes for the tile pair p = kt / 2 are the 16 bytes at band * 16 * K + p * 512 + l * 16
+// (byte 8 * (kt & 1) + 2 * q + {0, 1}). Code tables and stream offsets are those of row-major units.
+//
+// The reference multiplies these fragments with mma.sync (core/include/bf16n/kernels.cuh:1507-2391). Here a lane keeps two
+// FP32 accumulators per activation column (its two rows), multiplies with FMAs and the four lanes of a row quad are
+// added at the end; up to 8 columns are served by one decode. Sums differ from the reference's tensor-core order within
+// FP32 rounding (tested against FP64).
+#include "decode.cuh"
+#include "launch.h"
+
+namespace b16 {
+namespace {
+
+using namespace dev;
+using bf16 = __nv_bfloat16;
+
+constexpr int BAND = 16;
+
+__device__ __forceinline__ void stage_lut(uint32_t * dst, const uint32_t * src) {
+    for (int i = threadIdx.x; i < HP_MAX_PAIRS / 4; i += blockDim.x) { ((uint4 *) dst)[i] = __ldg((const uint4 *) src + i); }
+}
+// row (inside the band) and first column (inside the tile) of symbol q of lane l
+__device__ __forceinline__ int frag_row(int l, int q) { return (l >> 2) + 8 * (q & 1); }
+__device__ __forceinline__ int frag_col(int l, int q) { return 2 * (l & 3) + 8 * (q >> 1); }
+
+// ---------------------------------------------------------------- exact reconstruction
+
+struct FoStore { // row-major BF16 output, row 0 = row0
+    uint16_t * out; int64_t K;
+    __device__ __forceinline__ void pair(int64_t r, int64_t col, uint32_t w) { *(uint32_t *) (out + r * K + col) = w; }
+    __device__ __forceinline__ void finish(int) {}
+};
+struct FoCompare { // count BF16 words that differ from src
+    const uint16_t * src; int64_t K; unsigned long long * total; unsigned int bad;
+    __device__ __forceinline__ void pair(int64_t r, int64_t col, uint32_t w) {
+        const uint32_t d = __ldg((const uint32_t *) (src + r * K + col)) ^ w;
+        bad += ((d & 0xFFFFu) != 0) + ((d >> 16) != 0);
+    }
+    __device__ __forceinline__ void finish(int lane) {
+        unsigned int b = bad;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) { b += __shfl_xor_sync(FULL, b, o); }
+        if (lane == 0 && b) { atomicAdd(total, (unsigned long long) b); }
+    }
+};
+
+// one warp per unit (band, slab) of rows [row0, row0 + nrows)
+template <typename Sink>
+__global__ void __launch_bounds__(256) k_fo_expand(const PairView w, int C, int64_t row0, int64_t nrows, const Sink sink_in) {
+    Sink sink = sink_in;
+    __shared__ uint32_t lut[HP_MAX_PAIRS];
+    stage_lut(lut, w.lut);
+    __syncthreads();
+    const int64_t K = (int64_t) C * CHUNK;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t units = nrows / BAND * C;
+    for (int64_t u = (int64_t) blockIdx.x * 8 + warp; u < units; u += (int64_t) gridDim.x * 8) {
+        const int64_t band = u / C, slab = u - band * C, gband = row0 / BAND + band;
+        PairReader rd;
+        rd.open(w, gband * C + slab, lane);
+        const uint8_t * pl = w.plane + gband * BAND * K + slab * (16 * 512) + 16 * lane;
+        for (int p = 0; p < 16; p++) {
+            uint32_t e[8], wv[8];
+            rd.take8(lut, e);
+            assemble8(ld_stream16(pl + p * 512), e, wv);
+#pragma unroll
+            for (int s = 0; s < 8; s++) {
+                const int q = s & 3, kt = (int) slab * 32 + 2 * p + (s >> 2);
+                sink.pair(band * BAND + frag_row(lane, q), (int64_t) kt * 16 + frag_col(lane, q), wv[s]);
+            }
+        }
+    }
+    sink.finish(lane);
+}
+
+// one warp per requested row: the four lanes of the row's quad decode their streams and keep the row's half
+template <bool BF>
+__global__ void __launch_bounds__(256) k_fo_rows(const PairView w, int C, const char * ids, int64_t ids_s0, int64_t n, int64_t row0,
+                                                 char * dst, int64_t dst_s1) {
+    __shared__ uint32_t lut[HP_MAX_PAIRS];
+    stage_lut(lut, w.lut);
+    __syncthreads();
+    const int64_t K = (int64_t) C * CHUNK;
+    const int j = threadIdx.x & 31;
+    const int64_t i = (int64_t) blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (i >= n || j >= 4) { return; }
+    const int64_t gr = row0 + *(const int32_t *) (ids + i * ids_s0);
+    const int64_t band = gr / BAND;
+    const int r = (int) (gr - band * BAND), l = 4 * (r & 7) + j, half = r >> 3;
+    for (int slab = 0; slab < C; slab++) {
+        PairReader rd;
+        rd.open(w, band * C + slab, l);
+        const uint8_t * pl = w.plane + band * BAND * K + (int64_t) slab * (16 * 512) + 16 * l;
+        for (int p = 0; p < 16; p++) {
+            uint32_t e[8], wv[8];
+            rd.take8(lut, e);
+            assemble8(ld_stream16(pl + p * 512), e, wv);
+#pragma unroll
+            for (int s = 0; s < 8; s++) {
+                const int q = s & 3;
+                if ((q & 1) != half) { continue; }
+                const int64_t col = (int64_t) (slab * 32 + 2 * p + (s >> 2)) * 16 + frag_col(l, q);
+                if (BF) { *(uint32_t *) (dst + i * dst_s1 + col * 2) = wv[s]; }
+                else { *(float2 *) (dst + i * dst_s1 + col * 4) = make_float2(bf16lo_f32(wv[s]), bf16hi_f32(wv[s])); }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------- decode GEMV
+
+// NC dense columns (NC == 1: also routed columns, one per blockIdx.y); one warp per band, slabs in order
+template <int NC, typename TX>
+__global__ void __launch_bounds__(256) k_fo_gemv(const PairView w, int C, Cols p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    uint32_t * lut = (uint32_t *) smem;
+    float * xs = (float *) (smem + 4 * HP_MAX_PAIRS);   // NC columns of K activations
+    const int64_t K = (int64_t) C * CHUNK;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    stage_lut(lut, w.lut);
+    grid_dependency_wait(); // activations (and expert ids) may come from the kernel before this one
+    const TX * xg; OutVec out; int64_t rbase;
+    column<TX>(p, NC == 1 ? blockIdx.y : 0, xg, out, rbase);
+#pragma unroll
+    for (int n = 0; n < NC; n++) {
+        const TX * xn = (const TX *) ((const char *) xg + n * p.x_tok);
+        for (int i = threadIdx.x; i < K; i += blockDim.x) { xs[n * K + i] = to_f32(xn[i]); }
+    }
+    __syncthreads();
+    const int64_t bands = p.nrows / BAND;
+    const int cq = 2 * (lane & 3); // this lane's columns inside a tile: cq + {0, 1} and cq + 8 + {0, 1}
+    for (int64_t b = (int64_t) blockIdx.x * nwarp + warp; b < bands; b += (int64_t) gridDim.x * nwarp) {
+        const int64_t gband = rbase / BAND + b;
+        float acc[NC][2];
+#pragma unroll
+        for (int n = 0; n < NC; n++) { acc[n][0] = acc[n][1] = 0.f; }
+        for (int slab = 0; slab < C; slab++) {
+            PairReader rd;
+            rd.open(w, gband * C + slab, lane);
+            const uint8_t * pl = w.plane + gband * BAND * K + (int64_t) slab * (16 * 512) + 16 * lane;
+            uint4 nxt = ld_stream16(pl);
+            for (int pp = 0; pp < 16; pp++) {
+                const uint4 cur = nxt;
+                if (pp + 1 < 16) { nxt = ld_stream16(pl + (pp + 1) * 512); }
+                uint32_t e[8], wv[8];
+                rd.take8(lut, e);
+                assemble8(cur, e, wv);
+#pragma unroll
+                for (int s = 0; s < 8; s++) {
+                    const int q = s & 3;
+                    const int col = (slab * 32 + 2 * pp + (s >> 2)) * 16 + cq + 8 * (q >> 1);
+                    const float w0 = bf16lo_f32(wv[s]), w1 = bf16hi_f32(wv[s]);
+#pragma unroll
+                    for (int n = 0; n < NC; n++) {
+                        const float2 xv = *(const float2 *) (xs + n * K + col);
+                        acc[n][q & 1] = fmaf(w1, xv.y, fmaf(w0, xv.x, acc[n][q & 1]));
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int n = 0; n < NC; n++) {
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                float v = acc[n][h];
+                v += __shfl_xor_sync(FULL, v, 1);
+                v += __shfl_xor_sync(FULL, v, 2);
+                if ((lane & 3) == 0) {
+                    OutVec o = out;
+                    o.p += n * p.y_tok;
+                    o.put(b * BAND + (lane >> 2) + 8 * h, v);
+                }
+            }
+        }
+    }
+}
+
+template <int NC, typename TX>
+void launch_fo(const bf16n_weight & w, const Cols & p, int ncols_grid, cudaStream_t st) {
+    const int C = (int) (w.K / CHUNK);
+    const int64_t bands = p.nrows / BAND;
+    const int64_t sms = device_info().sms;
+    // small blocks while there are few bands, so that they spread over the SMs
+    const int warps = bands * ncols_grid >= sms * 32 ? 8 : bands * ncols_grid >= sms * 8 ? 4 : 2;
+    const dim3 grid((unsigned) std::min<int64_t>((bands + warps - 1) / warps, sms * 8), (unsigned) ncols_grid);
+    const size_t shm = 4 * HP_MAX_PAIRS + (size_t) NC * w.K * 4;
+    launch_chained(k_fo_gemv<NC, TX>, grid, dim3(warps * 32), shm, st, pair_view(w), C, p);
+}
+
+template <typename TX>
+void fo_gemv_t(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st) {
+    Cols p = make_cols(a);
+    if (a.ids) {
+        launch_fo<1, TX>(w, p, a.ncols, st);
+        return;
+    }
+    for (int c0 = 0; c0 < a.ncols;) { // groups of 8, 4, 2, 1 columns, each decoding the matrix once
+        const int left = a.ncols - c0, nc = left >= 8 ? 8 : left >= 4 ? 4 : left >= 2 ? 2 : 1;
+        Cols q = p;
+        q.x += c0 * p.x_tok;
+        q.y += c0 * p.y_tok;
+        switch (nc) {
+            case 8: launch_fo<8, TX>(w, q, 1, st); break;
+            case 4: launch_fo<4, TX>(w, q, 1, st); break;
+            case 2: launch_fo<2, TX>(w, q, 1, st); break;
+            default: launch_fo<1, TX>(w, q, 1, st); break;
+        }
+        c0 += nc;
+    }
+}
+
+} // namespace
+
+void fo_init() {
+    const int optin = device_info().smem_optin;
+#define ATTR(KERNEL) cuda_ok(cudaFuncSetAttribute(KERNEL, cudaFuncAttributeMaxDynamicSharedMemorySize, optin), #KERNEL)
+    ATTR((k_fo_gemv<1, float>)); ATTR((k_fo_gemv<2, float>)); ATTR((k_fo_gemv<4, float>)); ATTR((k_fo_gemv<8, float>));
+    ATTR((k_fo_gemv<1, bf16>)); ATTR((k_fo_gemv<2, bf16>)); ATTR((k_fo_gemv<4, bf16>)); ATTR((k_fo_gemv<8, bf16>));
+#undef ATTR
+}
+
+// K up to 4096 columns with 8 activation columns staged as FP32 beside the table
+bool fo_supported(const bf16n_weight & w) {
+    return w.fo && w.format == FMT_HUFPAIR && w.R == BAND && !w.cm && w.K % CHUNK == 0 && w.rows % BAND == 0 &&
+           4 * HP_MAX_PAIRS + 8 * w.K * 4 <= device_info().smem_optin;
+}
+
+void fo_gemv(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st) {
+    if (a.x_bf16) { fo_gemv_t<bf16>(w, a, st); } else { fo_gemv_t<float>(w, a, st); }
+}
+
+void fo_expand_store(const bf16n_weight & w, int64_t row0, int64_t nrows, uint16_t * out, cudaStream_t st) {
+    const int C = (int) (w.K / CHUNK);
+    const int64_t units = nrows / BAND * C;
+    const unsigned gx = (unsigned) std::max<int64_t>(1, std::min<int64_t>((units + 7) / 8, (int64_t) device_info().sms * 16));
+    k_fo_expand<FoStore><<<gx, 256, 0, st>>>(pair_view(w), C, row0, nrows, FoStore{out, w.K});
+    check_launch();
+}
+
+void fo_expand_compare(const bf16n_weight & w, int64_t row0, int64_t nrows, const uint16_t * src, unsigned long long * total,
+                       cudaStream_t st) {
+    const int C = (int) (w.K / CHUNK);
+    const int64_t units = nrows / BAND * C;
+    const unsigned gx = (unsigned) std::max<int64_t>(1, std::min<int64_t>((units + 7) / 8, (int64_t) device_info().sms * 16));
+    k_fo_expand<FoCompare><<<gx, 256, 0, st>>>(pair_view(w), C, row0, nrows, FoCompare{src, w.K, total, 0u});
+    check_launch();
+}
+
+void fo_gather_rows(const bf16n_weight & w, const void * ids, int64_t ids_s0, int64_t n, void * dst, bool dst_bf16, int64_t dst_s1,
+                    int64_t row0, cudaStream_t st) {
+    const int C = (int) (w.K / CHUNK);
+    const unsigned gx = (unsigned) ((n + 7) / 8);
+    if (dst_bf16) { k_fo_rows<true><<<gx, 256, 0, st>>>(pair_view(w), C, (const char *) ids, ids_s0, n, row0, (char *) dst, dst_s1); }
+    else { k_fo_rows<false><<<gx, 256, 0, st>>>(pair_view(w), C, (const char *) ids, ids_s0, n, row0, (char *) dst, dst_s1); }
+    check_launch();
+}
+
+} // namespace b16

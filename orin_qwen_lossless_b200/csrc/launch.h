@@ -67,6 +67,16 @@ bool gemv_rings_enabled();
 bool gemv_rings_applies(const bf16n_weight & w, const bf16n_mmv_args & a);
 void gemv_rings(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st, const bf16n_peer_out * peers = nullptr);
 
+// fo.cu: fragment-order HUFPAIR tensors
+void fo_init();
+bool fo_supported(const bf16n_weight & w);
+void fo_gemv(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st);
+void fo_expand_store(const bf16n_weight & w, int64_t row0, int64_t nrows, uint16_t * out, cudaStream_t st);
+void fo_expand_compare(const bf16n_weight & w, int64_t row0, int64_t nrows, const uint16_t * src, unsigned long long * total,
+                       cudaStream_t st);
+void fo_gather_rows(const bf16n_weight & w, const void * ids, int64_t ids_s0, int64_t n, void * dst, bool dst_bf16, int64_t dst_s1,
+                    int64_t row0, cudaStream_t st);
+
 // peer.cu: exchange buffers shared between the GPUs of a node and the wait for the peers' announcements
 void peer_wait(uint32_t * local_header, int n_peers_mask, cudaStream_t st);
 

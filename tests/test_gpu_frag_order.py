@@ -1,0 +1,111 @@
+"""Fragment-order HUFPAIR tensors (16-row bands in mma A-fragment order, the layout the reference's vLLM policy picks for
+experts, linear layers and lm_head): bit-exact device reconstruction and verify, row gather, and the decode GEMV against
+FP64 over the exact weights for 1..8 dense tokens and for routed (token, slot) columns. Shapes and seeds follow the
+fragment-order cases of the reference's tests/core/test_roundtrip.py and test_kernels.py."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import GEMV_REL, bits_of, to_bf16_tensor
+from oracle import cpu_oracle as o
+
+pytestmark = pytest.mark.gpu
+HP = 3
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from orin_qwen_lossless_b200 import ops as m
+    assert torch.cuda.is_available()
+    m.init()
+    return m
+
+
+def fo(ops, bits):
+    plane, aux, meta = ops.encode(to_bf16_tensor(bits), HP, 16, False, True)
+    assert meta.frag_order and meta.R == 16
+    return ops.upload(plane, aux, meta, "cuda")
+
+
+def act(shape, seed):
+    xb = o.f32_to_bf16_bits(np.random.default_rng(500 + seed).standard_normal(shape).astype(np.float32))
+    return to_bf16_tensor(xb).cuda(), o.bf16_bits_to_f32(xb).astype(np.float64)
+
+
+@pytest.mark.parametrize("rows,K", [(16, 512), (64, 512), (2048, 512), (512, 2048), (48, 1024), (32, 4096)])
+def test_roundtrip_and_verify(ops, rows, K):
+    bits = o.with_specials(o.weights_like(rows, K, rows + K), rows + K).reshape(rows, K)  # NaN, infinities, denormals, zeros too
+    w = fo(ops, bits)
+    src = to_bf16_tensor(bits).cuda()
+    assert torch.equal(ops.dequant(w).view(torch.int16), src.view(torch.int16))
+    assert ops.mismatches(w, src) == 0
+    if rows >= 48:  # a band range in the middle
+        assert torch.equal(ops.dequant(w, 16, 32).view(torch.int16), src[16:48].view(torch.int16))
+    bad = src.clone()
+    bad.view(torch.int16)[rows - 1, K - 3] ^= 0x0100
+    bad.view(torch.int16)[0, 17] ^= 0x0001
+    assert ops.mismatches(w, bad) == 2
+
+
+def test_matches_the_oracle_decoder_bytes(ops):
+    bits = o.weights_like(64, 1024, 9)
+    plane, aux, meta = ops.encode(to_bf16_tensor(bits), HP, 16, False, True)
+    op, oa, _ = o.encode(bits, HP, 16, False, True)
+    assert np.array_equal(plane.numpy().ravel(), op.ravel()) and np.array_equal(aux.numpy(), oa)
+    assert np.array_equal(o.decode(op, oa), bits)
+
+
+@pytest.mark.parametrize("T", [1, 2, 3, 5, 8])
+@pytest.mark.parametrize("rows,K", [(2048, 512), (512, 2048), (160, 1024)])
+def test_dense_gemv_against_fp64(ops, rows, K, T):
+    bits = o.weights_like(rows, K, 3 * rows + K)
+    w = fo(ops, bits)
+    x, x64 = act((T, K), T)
+    w64 = o.bf16_bits_to_f32(bits).astype(np.float64)
+    ref, s = x64 @ w64.T, np.abs(x64) @ np.abs(w64).T
+    y = ops.mmv(x, w)
+    assert y.shape == (T, rows) and y.dtype == torch.float32
+    assert (np.abs(y.cpu().numpy() - ref) <= GEMV_REL * s).all()
+    # a column's result does not depend on what it is batched with; FP32 activations give the same bits as BF16 ones
+    y1 = ops.mmv(x[:1].contiguous(), w)
+    assert torch.equal(y1[0], y[0])
+    assert torch.equal(ops.mmv(x.float(), w), y)
+    yb = ops.mmv(x, w, out_dtype=torch.bfloat16)
+    assert torch.equal(yb.view(torch.int16), y.to(torch.bfloat16).view(torch.int16))
+
+
+def test_routed_columns(ops):
+    E, rows_e, K, T, k = 4, 512, 512, 3, 2
+    bits = o.weights_like(E * rows_e, K, 77)
+    w = fo(ops, bits)
+    ids = torch.tensor([[0, 3], [2, 2], [1, 0]], dtype=torch.int32, device="cuda")
+    x, x64 = act((T, k, K), 4)
+    y = ops.mmv(x, w, ids, rows_e)
+    w64 = o.bf16_bits_to_f32(bits).astype(np.float64).reshape(E, rows_e, K)
+    for t in range(T):
+        for s_ in range(k):
+            e = int(ids[t, s_])
+            ref, s = w64[e] @ x64[t, s_], np.abs(w64[e]) @ np.abs(x64[t, s_])
+            assert (np.abs(y[t, s_].cpu().numpy() - ref) <= GEMV_REL * s).all()
+
+
+def test_get_rows_and_linear(ops):
+    rows, K = 256, 2048
+    bits = o.weights_like(rows, K, 5)
+    w = fo(ops, bits)
+    src = to_bf16_tensor(bits).cuda()
+    ids = torch.tensor([0, 255, 17, 8, 129, 17], dtype=torch.int64, device="cuda")
+    assert torch.equal(ops.get_rows(ids, w).view(torch.int16), src[ids].view(torch.int16))
+    assert torch.equal(ops.get_rows(ids.int(), w, torch.float32), src[ids].float())
+    x, _ = act((12, K), 6)  # more than 8 tokens: exact dequantisation + GEMM
+    assert torch.equal(ops.linear(x, w).view(torch.int16), (x @ src.t()).view(torch.int16))
+
+
+def test_what_has_no_fragment_order_kernel_says_so(ops):
+    bits = o.weights_like(4 * 512, 2048, 6)
+    w = fo(ops, bits)
+    assert not ops.mm_ids_supported(w)
+    x, _ = act((9, 2048), 7)
+    ids = torch.zeros((9, 2), dtype=torch.int32, device="cuda")
+    with pytest.raises(ValueError, match="no batched kernel"):
+        ops.moe_mm_ids(x, ids, w, 4)
