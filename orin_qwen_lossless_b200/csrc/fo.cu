@@ -7,10 +7,11 @@
 // order tiles -> q; its plane bytes for the tile pair p = kt / 2 are the 16 bytes at band * 16 * K + p * 512 + l * 16
 // (byte 8 * (kt & 1) + 2 * q + {0, 1}). Code tables and stream offsets are those of row-major units.
 //
-// The reference multiplies these fragments with mma.sync (core/include/bf16n/kernels.cuh:1507-2391). Here a lane keeps two
-// FP32 accumulators per activation column (its two rows), multiplies with FMAs and the four lanes of a row quad are
-// added at the end; up to 8 columns are served by one decode. Sums differ from the reference's tensor-core order within
-// FP32 rounding (tested against FP64).
+// The reference multiplies these fragments with mma.sync (core/include/bf16n/kernels.cuh:1507-2391). Here 2..8 dense BF16
+// columns do the same (k_fo_gemv_mma: one decode and one mma.m16n8k16 per tile serve eight tokens; the tcgen05 path has
+// no operand form for register fragments, so this small-N product stays on the warp-level instruction), while single
+// columns, FP32 activations and routed columns use FMAs: a lane keeps two FP32 accumulators per column (its two rows)
+// and the four lanes of a row quad are added at the end. Results are within FP32 rounding of FP64 either way (tested).
 #include "decode.cuh"
 #include "launch.h"
 
@@ -181,6 +182,65 @@ __global__ void __launch_bounds__(256) k_fo_gemv(const PairView w, int C, Cols p
     }
 }
 
+// Up to 8 dense BF16 columns on the tensor cores: a lane's four symbols of a tile are exactly its A registers of
+// mma.m16n8k16 (that is what the layout is for), the activations are the B operand (k x 8 tokens) and a band's
+// D[16 rows, 8 tokens] accumulates in four registers per lane, so eight tokens cost one decode and one MMA per tile.
+// Shared memory holds the 8 activation rows as BF16, each padded by 8 elements so that the B-fragment reads of a warp
+// fall into 32 different banks; columns beyond ncols are zero.
+constexpr int XPAD = 8;
+__global__ void __launch_bounds__(256) k_fo_gemv_mma(const PairView w, int C, Cols p, int ncols) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    uint32_t * lut = (uint32_t *) smem;
+    bf16 * xs = (bf16 *) (smem + 4 * HP_MAX_PAIRS);
+    const int K = C * CHUNK, XS = K + XPAD;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    stage_lut(lut, w.lut);
+    grid_dependency_wait();
+    for (int i = threadIdx.x; i < 8 * K; i += blockDim.x) {
+        const int n = i / K, c = i - n * K;
+        xs[n * XS + c] = n < ncols ? ((const bf16 *) (p.x + n * p.x_tok))[c] : __float2bfloat16(0.f);
+    }
+    __syncthreads();
+    const int g = lane >> 2, t = lane & 3;
+    const bf16 * xl = xs + g * XS + 2 * t; // B fragment: token g, k = 2t, 2t+1 (and + 8) of every tile
+    const int64_t bands = p.nrows / BAND;
+    for (int64_t b = (int64_t) blockIdx.x * nwarp + warp; b < bands; b += (int64_t) gridDim.x * nwarp) {
+        const int64_t gband = p.row0 / BAND + b;
+        float d[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int slab = 0; slab < C; slab++) {
+            PairReader rd;
+            rd.open(w, gband * C + slab, lane);
+            const uint8_t * pl = w.plane + gband * BAND * (int64_t) K + (int64_t) slab * (16 * 512) + 16 * lane;
+            uint4 nxt = ld_stream16(pl);
+            for (int pp = 0; pp < 16; pp++) {
+                const uint4 cur = nxt;
+                if (pp + 1 < 16) { nxt = ld_stream16(pl + (pp + 1) * 512); }
+                uint32_t e[8], a[8];
+                rd.take8(lut, e);
+                assemble8(cur, e, a);
+#pragma unroll
+                for (int kk = 0; kk < 2; kk++) {
+                    const int col = (slab * 32 + 2 * pp + kk) * 16;
+                    const uint32_t b0 = *(const uint32_t *) (xl + col), b1 = *(const uint32_t *) (xl + col + 8);
+                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+                                 "{%0, %1, %2, %3};"
+                                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                                 : "r"(a[4 * kk]), "r"(a[4 * kk + 1]), "r"(a[4 * kk + 2]), "r"(a[4 * kk + 3]), "r"(b0), "r"(b1));
+                }
+            }
+        }
+        // d[0], d[1]: row g, tokens 2t, 2t+1; d[2], d[3]: row g + 8
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int n = 2 * t + (i & 1);
+            if (n < ncols) {
+                const OutVec o = {p.y + n * p.y_tok, p.y_bf16};
+                o.put(b * BAND + g + 8 * (i >> 1), d[i]);
+            }
+        }
+    }
+}
+
 template <int NC, typename TX>
 void launch_fo(const bf16n_weight & w, const Cols & p, int ncols_grid, cudaStream_t st) {
     const int C = (int) (w.K / CHUNK);
@@ -198,6 +258,20 @@ void fo_gemv_t(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st
     Cols p = make_cols(a);
     if (a.ids) {
         launch_fo<1, TX>(w, p, a.ncols, st);
+        return;
+    }
+    if (a.x_bf16 && a.ncols >= 2) { // BF16 activations, several tokens: the tensor-core kernel, 8 columns per decode
+        const int C = (int) (w.K / CHUNK);
+        const int64_t bands = p.nrows / BAND, sms = device_info().sms;
+        const int warps = bands >= sms * 32 ? 8 : bands >= sms * 8 ? 4 : 2;
+        const dim3 grid((unsigned) std::min<int64_t>((bands + warps - 1) / warps, sms * 8));
+        const size_t shm = 4 * HP_MAX_PAIRS + (size_t) 8 * (w.K + XPAD) * 2;
+        for (int c0 = 0; c0 < a.ncols; c0 += 8) {
+            Cols q = p;
+            q.x += c0 * p.x_tok;
+            q.y += c0 * p.y_tok;
+            launch_chained(k_fo_gemv_mma, grid, dim3(warps * 32), shm, st, pair_view(w), C, q, std::min(8, a.ncols - c0));
+        }
         return;
     }
     for (int c0 = 0; c0 < a.ncols;) { // groups of 8, 4, 2, 1 columns, each decoding the matrix once
@@ -222,6 +296,7 @@ void fo_init() {
 #define ATTR(KERNEL) cuda_ok(cudaFuncSetAttribute(KERNEL, cudaFuncAttributeMaxDynamicSharedMemorySize, optin), #KERNEL)
     ATTR((k_fo_gemv<1, float>)); ATTR((k_fo_gemv<2, float>)); ATTR((k_fo_gemv<4, float>)); ATTR((k_fo_gemv<8, float>));
     ATTR((k_fo_gemv<1, bf16>)); ATTR((k_fo_gemv<2, bf16>)); ATTR((k_fo_gemv<4, bf16>)); ATTR((k_fo_gemv<8, bf16>));
+    ATTR(k_fo_gemv_mma);
 #undef ATTR
 }
 

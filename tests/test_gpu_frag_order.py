@@ -66,10 +66,12 @@ def test_dense_gemv_against_fp64(ops, rows, K, T):
     y = ops.mmv(x, w)
     assert y.shape == (T, rows) and y.dtype == torch.float32
     assert (np.abs(y.cpu().numpy() - ref) <= GEMV_REL * s).all()
-    # a column's result does not depend on what it is batched with; FP32 activations give the same bits as BF16 ones
-    y1 = ops.mmv(x[:1].contiguous(), w)
-    assert torch.equal(y1[0], y[0])
-    assert torch.equal(ops.mmv(x.float(), w), y)
+    # several BF16 tokens run on the tensor cores, one token and FP32 activations on FMAs: all within the bound, and a
+    # column's result does not depend on what it is batched with (first column of a 2-token batch vs of the full batch)
+    yf = ops.mmv(x.float(), w)
+    assert (np.abs(yf.cpu().numpy() - ref) <= GEMV_REL * s).all()
+    if T >= 2:
+        assert torch.equal(ops.mmv(x[:2].contiguous(), w)[0], y[0])
     yb = ops.mmv(x, w, out_dtype=torch.bfloat16)
     assert torch.equal(yb.view(torch.int16), y.to(torch.bfloat16).view(torch.int16))
 
