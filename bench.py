@@ -357,7 +357,7 @@ def run_ours(args):
 
 # ------------------------------------------------------------------ secondary workloads (configs 2, 3, 4 of the baseline)
 
-def _enc(ops, rows, K, fmt, R, cm, seed, dev):
+def _enc(ops, rows, K, fmt, R, cm, seed, dev, fo=False):
     import torch
     g = torch.Generator().manual_seed(seed)
     w = torch.empty((rows, K), dtype=torch.bfloat16)
@@ -365,7 +365,7 @@ def _enc(ops, rows, K, fmt, R, cm, seed, dev):
     for r0 in range(0, rows, step):
         n = min(step, rows - r0)
         w[r0:r0 + n] = (torch.randn((n, K), generator=g) * 0.02).to(torch.bfloat16)
-    plane, aux, meta = ops.encode(w, fmt, R, cm)
+    plane, aux, meta = ops.encode(w, fmt, R, cm, fo)
     return ops.upload(plane, aux, meta, dev)
 
 
@@ -417,11 +417,12 @@ def run_small(args):
                       "frac_of_measured_hbm": nbytes / us / 1e3 / peak, "l2": "191 MB of weights per replay > L2"}), flush=True)
 
 
-def _moe_weights(ops, dev, n_experts, rank=0):
-    """Routed expert weights of one rank (every rank draws its own experts: seeds differ per rank)."""
-    gate = _enc(ops, n_experts * 512, 2048, 3, 8, True, 101 + 10 * rank, dev)
-    up = _enc(ops, n_experts * 512, 2048, 3, 8, True, 102 + 10 * rank, dev)
-    down = _enc(ops, n_experts * 2048, 512, 3, 16, False, 103 + 10 * rank, dev)
+def _moe_weights(ops, dev, n_experts, rank=0, fo=False):
+    """Routed expert weights of one rank (every rank draws its own experts: seeds differ per rank). fo: 16-row
+    fragment-order bands (the vLLM layout) instead of chunk-major R = 8 gate / up and row-major R = 16 down."""
+    gate = _enc(ops, n_experts * 512, 2048, 3, 16 if fo else 8, not fo, 101 + 10 * rank, dev, fo)
+    up = _enc(ops, n_experts * 512, 2048, 3, 16 if fo else 8, not fo, 102 + 10 * rank, dev, fo)
+    down = _enc(ops, n_experts * 2048, 512, 3, 16, False, 103 + 10 * rank, dev, fo)
     return gate, up, down
 
 
@@ -532,7 +533,7 @@ def run_moe_prefill(args):
     ops.init()
     E, k = 256, 8
     n_local = E // world
-    gate, up, down = _moe_weights(ops, dev, n_local, rank)
+    gate, up, down = _moe_weights(ops, dev, n_local, rank, args.fo)
     for T in (2048, 8192):
         flops = 6.0 * 512 * 2048 * k * T
         nbytes = (gate.nbytes + up.nbytes + down.nbytes) * world
@@ -561,7 +562,8 @@ def run_moe_prefill(args):
             us = _max_over_ranks(torch, e0.elapsed_time(e1) * 1e3 / reps, world, dev)
             par = f"expert-parallel over {world} GPUs, NCCL all-to-all dispatch and return"
         if rank == 0:
-            print(json.dumps({"workload": f"MoE prefill layer, {T} tokens, 256 experts top-8", "n_gpus": world, "parallelism": par,
+            print(json.dumps({"workload": f"MoE prefill layer, {T} tokens, 256 experts top-8" + (", fragment-order experts" if args.fo else ""),
+                              "n_gpus": world, "parallelism": par,
                               "us_per_layer": us, "TFLOPs": flops / us / 1e6, "weight_GBps": nbytes / us / 1e3,
                               "frac_of_bf16_peak_1679": flops / us / 1e6 / 1679.3 / world}), flush=True)
     if world > 1:
@@ -578,6 +580,7 @@ def main():
     ap.add_argument("--rows", type=int, default=ROWS, help="rows of the matrix (default: the vocabulary projection)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cublas", action="store_true", help="also time a stock BF16 GEMV of the uncompressed matrix")
+    ap.add_argument("--fo", action="store_true", help="moe_prefill: experts in the fragment-order layout (mma.sync batched kernel)")
     ap.add_argument("--nccl", action="store_true", help="N > 1, moe_decode: all-reduce with NCCL instead of the fused peer stores")
     ap.add_argument("--workload", default="lm_head", choices=["lm_head", "small", "moe_decode", "moe_prefill"],
                     help="lm_head is the headline contract line; the others print extra lines for the other baseline configs "

@@ -233,7 +233,10 @@ int bf16n_get_rows(const bf16n_weight * w, const void * ids, int64_t ids_s0, int
     });
 }
 
-int bf16n_mm_ids_supported(const bf16n_weight * w, const bf16n_weight * up) { return prefill_supported(*w, up) ? 1 : 0; }
+int bf16n_mm_ids_supported(const bf16n_weight * w, const bf16n_weight * up) {
+    if (w->fo || (up && up->fo)) { return device_info().sms > 0 && fo_mm_ids_supported(*w, up) ? 1 : 0; }
+    return prefill_supported(*w, up) ? 1 : 0;
+}
 
 int bf16n_mm_ids_route(const void * ids, int ids_i64, int64_t ids_row_stride, int32_t * ids_src1, int32_t * ids_dst,
                        int32_t * bounds, int n_experts, int n_tok, int n_used, int nchannels_y, int sis1, void * stream) {
@@ -251,8 +254,13 @@ int bf16n_mm_ids(const bf16n_weight * w, const bf16n_weight * up, const void * x
         ensure_init();
         check_weight(*w);
         if (up) { check_weight(*up); }
-        require(prefill_supported(*w, up), "no batched kernel for this matrix");
         require(n_experts > 0 && w->rows % n_experts == 0, "rows must split evenly into experts");
+        if (w->fo || (up && up->fo)) {
+            require(fo_mm_ids_supported(*w, up), "no batched kernel for this matrix");
+            fo_mm_ids(*w, up, x_bf16, x_row, ids_src1, ids_dst, bounds, dst, dst_bf16 != 0, dst_col, n_experts, (cudaStream_t) stream);
+            return;
+        }
+        require(prefill_supported(*w, up), "no batched kernel for this matrix");
         prefill_mm_ids(*w, up, x_bf16, x_row, ids_src1, ids_dst, bounds, dst, dst_bf16 != 0, dst_col, n_experts, n_tok, n_used,
                        (cudaStream_t) stream);
     });

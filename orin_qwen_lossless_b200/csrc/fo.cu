@@ -241,6 +241,118 @@ __global__ void __launch_bounds__(256) k_fo_gemv_mma(const PairView w, int C, Co
     }
 }
 
+// ---------------------------------------------------------------- batched routed product (prefill)
+
+// dst[t, slot, :] = W_e x_t for every routed (token, slot) pair, optionally fused gate/up + SwiGLU, for fragment-order
+// experts (replaces the reference's k_fo_mm_ids / k_fo_mm_glu, kernels.cuh:2070-2391). A block of 8 warps takes 8
+// consecutive bands of one expert (GLU: the same bands of gate and up, one after the other in the same warp, so that a
+// lane ends with gate and up of the same (row, token)). The expert's tokens come in passes of up to 64; per 512-column
+// slab their activation rows are gathered into shared memory once for the block, and every decoded tile is multiplied
+// with the pass's tokens eight at a time (mma.m16n8k16), accumulating D[16 rows, 64 tokens] in registers across slabs.
+constexpr int FO_TOK = 64;                      // tokens per pass
+constexpr int FO_XS = CHUNK + XPAD;             // padded activation row of one slab (BF16 elements)
+
+struct FoBatch {
+    PairView w0, w1;
+    const bf16 * x; int64_t x_row;
+    const int32_t * ids_src1; const int32_t * ids_dst; const int32_t * bounds;
+    char * dst; int64_t dst_col; bool dst_bf16;
+    int n_experts, C;
+    int64_t rows_per_expert;
+};
+
+template <bool GLU>
+__global__ void __launch_bounds__(256) k_fo_mm_ids(const FoBatch p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    uint32_t * lut0 = (uint32_t *) smem;
+    uint32_t * lut1 = lut0 + (GLU ? HP_MAX_PAIRS : 0);
+    bf16 * xs = (bf16 *) (lut1 + HP_MAX_PAIRS);                 // FO_TOK rows of FO_XS
+    __shared__ int32_t tok_src[FO_TOK], tok_dst[FO_TOK];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    stage_lut(lut0, p.w0.lut);
+    if (GLU) { stage_lut(lut1, p.w1.lut); }
+    const int64_t bands_e = p.rows_per_expert / BAND, K = (int64_t) p.C * CHUNK;
+    const int groups_e = (int) ((bands_e + 7) / 8);
+    const int g = lane >> 2, t = lane & 3;
+    for (int item = blockIdx.x; item < p.n_experts * groups_e; item += gridDim.x) {
+        const int e = item / groups_e;
+        const int64_t band = (int64_t) (item - e * groups_e) * 8 + warp;   // inside the expert
+        const bool active = band < bands_e;
+        const int64_t gband = (int64_t) e * bands_e + band;
+        const int j0 = p.bounds[e], j1 = p.bounds[e + 1];
+        for (int jp = j0; jp < j1; jp += FO_TOK) {
+            const int ntok = min(FO_TOK, j1 - jp), ng = (ntok + 7) / 8;
+            __syncthreads(); // the previous pass is done with tok_* and xs
+            if (threadIdx.x < FO_TOK) {
+                tok_src[threadIdx.x] = threadIdx.x < ntok ? p.ids_src1[jp + threadIdx.x] : -1;
+                tok_dst[threadIdx.x] = threadIdx.x < ntok ? p.ids_dst[jp + threadIdx.x] : -1;
+            }
+            float d0[FO_TOK / 8][4], d1[GLU ? FO_TOK / 8 : 1][4];
+#pragma unroll
+            for (int i = 0; i < FO_TOK / 8; i++) {
+#pragma unroll
+                for (int c = 0; c < 4; c++) { d0[i][c] = 0.f; if (GLU) { d1[i][c] = 0.f; } }
+            }
+            for (int slab = 0; slab < p.C; slab++) {
+                __syncthreads(); // tok_* visible; every warp is done with the previous slab's activations
+                for (int i = threadIdx.x; i < ng * 8 * (CHUNK / 8); i += blockDim.x) { // 16-byte pieces; missing tokens: zeros
+                    const int row = i / (CHUNK / 8), piece = i - row * (CHUNK / 8);
+                    uint4 v = make_uint4(0, 0, 0, 0);
+                    if (tok_src[row] >= 0) { v = __ldg((const uint4 *) (p.x + (int64_t) tok_src[row] * p.x_row + slab * CHUNK) + piece); }
+                    *(uint4 *) (xs + row * FO_XS + piece * 8) = v;
+                }
+                __syncthreads();
+                if (!active) { continue; }
+#pragma unroll
+                for (int m = 0; m < (GLU ? 2 : 1); m++) {
+                    const PairView & w = m ? p.w1 : p.w0;
+                    const uint32_t * lut = m ? lut1 : lut0;
+                    PairReader rd;
+                    rd.open(w, gband * p.C + slab, lane);
+                    const uint8_t * pl = w.plane + gband * BAND * K + (int64_t) slab * (16 * 512) + 16 * lane;
+                    uint4 nxt = ld_stream16(pl);
+                    for (int pp = 0; pp < 16; pp++) {
+                        const uint4 cur = nxt;
+                        if (pp + 1 < 16) { nxt = ld_stream16(pl + (pp + 1) * 512); }
+                        uint32_t en[8], a[8];
+                        rd.take8(lut, en);
+                        assemble8(cur, en, a);
+#pragma unroll
+                        for (int kk = 0; kk < 2; kk++) {
+                            const bf16 * xl = xs + g * FO_XS + (2 * pp + kk) * 16 + 2 * t;
+#pragma unroll
+                            for (int i = 0; i < FO_TOK / 8; i++) {
+                                if (i < ng) {
+                                    const uint32_t b0 = *(const uint32_t *) (xl + i * 8 * FO_XS), b1 = *(const uint32_t *) (xl + i * 8 * FO_XS + 8);
+                                    float * d = m ? d1[GLU ? i : 0] : d0[i];
+                                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+                                                 "{%8, %9}, {%0, %1, %2, %3};"
+                                                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                                                 : "r"(a[4 * kk]), "r"(a[4 * kk + 1]), "r"(a[4 * kk + 2]), "r"(a[4 * kk + 3]), "r"(b0), "r"(b1));
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            if (!active) { continue; }
+            // d[i][0..1]: row g, tokens 8i + 2t, + 1; d[i][2..3]: row g + 8
+#pragma unroll
+            for (int i = 0; i < FO_TOK / 8; i++) {
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const int tok = 8 * i + 2 * t + (c & 1);
+                    if (i < ng && tok < ntok) {
+                        const float v = GLU ? silu_f(d0[i][c]) * d1[GLU ? i : 0][c] : d0[i][c];
+                        const int64_t at = (int64_t) tok_dst[tok] * p.dst_col + band * BAND + g + 8 * (c >> 1);
+                        if (p.dst_bf16) { ((bf16 *) p.dst)[at] = __float2bfloat16_rn(v); } else { ((float *) p.dst)[at] = v; }
+                    }
+                }
+            }
+        }
+    }
+}
+
 template <int NC, typename TX>
 void launch_fo(const bf16n_weight & w, const Cols & p, int ncols_grid, cudaStream_t st) {
     const int C = (int) (w.K / CHUNK);
@@ -297,6 +409,9 @@ void fo_init() {
     ATTR((k_fo_gemv<1, float>)); ATTR((k_fo_gemv<2, float>)); ATTR((k_fo_gemv<4, float>)); ATTR((k_fo_gemv<8, float>));
     ATTR((k_fo_gemv<1, bf16>)); ATTR((k_fo_gemv<2, bf16>)); ATTR((k_fo_gemv<4, bf16>)); ATTR((k_fo_gemv<8, bf16>));
     ATTR(k_fo_gemv_mma);
+    // these two also have a little static shared memory: ask for what they use, not for the whole opt-in limit
+    cuda_ok(cudaFuncSetAttribute(k_fo_mm_ids<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * HP_MAX_PAIRS + FO_TOK * FO_XS * 2), "k_fo_mm_ids");
+    cuda_ok(cudaFuncSetAttribute(k_fo_mm_ids<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * HP_MAX_PAIRS + FO_TOK * FO_XS * 2), "k_fo_mm_ids glu");
 #undef ATTR
 }
 
@@ -304,6 +419,31 @@ void fo_init() {
 bool fo_supported(const bf16n_weight & w) {
     return w.fo && w.format == FMT_HUFPAIR && w.R == BAND && !w.cm && w.K % CHUNK == 0 && w.rows % BAND == 0 &&
            4 * HP_MAX_PAIRS + 8 * w.K * 4 <= device_info().smem_optin;
+}
+
+bool fo_mm_ids_supported(const bf16n_weight & w, const bf16n_weight * up) {
+    if (!fo_supported(w)) { return false; }
+    return !up || (fo_supported(*up) && up->K == w.K && up->rows == w.rows);
+}
+
+void fo_mm_ids(const bf16n_weight & w, const bf16n_weight * up, const void * x_bf16, int64_t x_row, const int32_t * ids_src1,
+               const int32_t * ids_dst, const int32_t * bounds, void * dst, bool dst_bf16, int64_t dst_col, int n_experts,
+               cudaStream_t st) {
+    FoBatch a = {};
+    a.w0 = pair_view(w);
+    a.w1 = up ? pair_view(*up) : a.w0;
+    a.x = (const bf16 *) x_bf16; a.x_row = x_row;
+    a.ids_src1 = ids_src1; a.ids_dst = ids_dst; a.bounds = bounds;
+    a.dst = (char *) dst; a.dst_col = dst_col; a.dst_bf16 = dst_bf16;
+    a.n_experts = n_experts; a.C = (int) (w.K / CHUNK);
+    a.rows_per_expert = w.rows / n_experts;
+    require(((uintptr_t) x_bf16 % 16) == 0 && (x_row * 2) % 16 == 0, "batched activations must be 16-byte aligned rows");
+    require(a.rows_per_expert % BAND == 0, "rows per expert must be whole 16-row bands");
+    const int64_t items = (int64_t) n_experts * ((a.rows_per_expert / BAND + 7) / 8);
+    const unsigned grid = (unsigned) std::min<int64_t>(items, (int64_t) device_info().sms * 2);
+    const size_t shm = (up ? 2 : 1) * 4 * HP_MAX_PAIRS + (size_t) FO_TOK * FO_XS * 2;
+    if (up) { k_fo_mm_ids<true><<<grid, 256, shm, st>>>(a); } else { k_fo_mm_ids<false><<<grid, 256, shm, st>>>(a); }
+    check_launch();
 }
 
 void fo_gemv(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st) {

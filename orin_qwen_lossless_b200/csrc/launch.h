@@ -71,6 +71,10 @@ void gemv_rings(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t s
 void fo_init();
 bool fo_supported(const bf16n_weight & w);
 void fo_gemv(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st);
+bool fo_mm_ids_supported(const bf16n_weight & w, const bf16n_weight * up);
+void fo_mm_ids(const bf16n_weight & w, const bf16n_weight * up, const void * x_bf16, int64_t x_row, const int32_t * ids_src1,
+               const int32_t * ids_dst, const int32_t * bounds, void * dst, bool dst_bf16, int64_t dst_col, int n_experts,
+               cudaStream_t st);
 void fo_expand_store(const bf16n_weight & w, int64_t row0, int64_t nrows, uint16_t * out, cudaStream_t st);
 void fo_expand_compare(const bf16n_weight & w, int64_t row0, int64_t nrows, const uint16_t * src, unsigned long long * total,
                        cudaStream_t st);

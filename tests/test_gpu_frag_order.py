@@ -103,11 +103,7 @@ def test_get_rows_and_linear(ops):
     assert torch.equal(ops.linear(x, w).view(torch.int16), (x @ src.t()).view(torch.int16))
 
 
-def test_what_has_no_fragment_order_kernel_says_so(ops):
+def test_batched_kernel_is_offered(ops):
     bits = o.weights_like(4 * 512, 2048, 6)
     w = fo(ops, bits)
-    assert not ops.mm_ids_supported(w)
-    x, _ = act((9, 2048), 7)
-    ids = torch.zeros((9, 2), dtype=torch.int32, device="cuda")
-    with pytest.raises(ValueError, match="no batched kernel"):
-        ops.moe_mm_ids(x, ids, w, 4)
+    assert ops.mm_ids_supported(w) and ops.mm_ids_supported(w, w)  # the batched cases themselves: test_gpu_prefill.py

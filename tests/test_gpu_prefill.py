@@ -22,12 +22,15 @@ def ops():
     return m
 
 
-@pytest.fixture(scope="module")
-def layer(ops):
+@pytest.fixture(scope="module", params=["lane_major", "fragment_order"])
+def layer(ops, request):
+    """The expert weights in the llama.cpp layout (chunk-major R = 8 gate / up, row-major R = 16 down: tcgen05 kernels) and
+    in the vLLM layout (16-row fragment-order bands everywhere: the mma.m16n8k16 batched kernel)."""
     bits = {"gate": o.weights_like(E * N, H, 21), "up": o.weights_like(E * N, H, 22), "down": o.weights_like(E * H, N, 23)}
+    fo = request.param == "fragment_order"
 
     def enc(w, R, cm):
-        plane, aux, meta = ops.encode(to_bf16_tensor(w), 3, R, cm)
+        plane, aux, meta = ops.encode(to_bf16_tensor(w), 3, 16 if fo else R, False if fo else cm, fo)
         return ops.upload(plane, aux, meta, "cuda")
 
     enc_w = {"gate": enc(bits["gate"], 8, True), "up": enc(bits["up"], 8, True), "down": enc(bits["down"], 16, False)}
