@@ -187,8 +187,8 @@ def roundtrip_equal(w: Weight, src: torch.Tensor, chunk_bytes: int = 64 << 20) -
 # ------------------------------------------------------------------ device: GEMV family
 
 def _check_x(x: torch.Tensor, K: int, what: str = "x") -> None:
-    if not x.is_cuda:
-        raise RuntimeError(f"bf16n: {what} must be a CUDA tensor")
+    if not (x.is_cuda or x.is_pinned()):  # pinned host memory is mapped into the device's address space
+        raise RuntimeError(f"bf16n: {what} must be a CUDA tensor (or pinned host memory)")
     if x.dtype not in (torch.bfloat16, torch.float32):
         raise RuntimeError(f"bf16n: {what} must be bf16 or f32")
     if x.shape[-1] != K or x.stride(-1) != 1:
@@ -228,7 +228,11 @@ def _mmv_common(x, w: Weight, ids, rows_per_matrix: int, out_bf16: bool, glu: bo
             raise RuntimeError("bf16n.mmv_glu: odd row count")
         n_out = rpm // 2 if glu else rpm
         T = x.shape[0]
-        y = torch.empty((T, n_out), dtype=odt, device=x.device) if out is None else out
+        y = torch.empty((T, n_out), dtype=odt, device=w.plane.device) if out is None else out
+        if out is not None and out.device.type == "cpu":
+            # pinned host memory is mapped into the device's address space: the kernel stores its results there itself
+            if not (out.is_pinned() and out.is_contiguous() and out.dtype == odt and tuple(out.shape) == (T, n_out)):
+                raise RuntimeError("bf16n.mmv: a host output must be pinned, contiguous and of the result's shape and dtype")
         if T == 0:
             return y
         a.y, a.ncols = y.data_ptr(), T
@@ -331,13 +335,20 @@ def linear(x: torch.Tensor, w: Weight, bias: torch.Tensor | None = None) -> torc
     return y.view(oshape)
 
 
-def linear_host(x_host: torch.Tensor, w: Weight, y_host: torch.Tensor, x_dev: torch.Tensor, y_dev: torch.Tensor) -> None:
+def linear_host(x_host: torch.Tensor, w: Weight, y_host: torch.Tensor, x_dev: torch.Tensor, y_dev: torch.Tensor | None = None) -> None:
     """One decode step of a projection with HOST activations and logits: x_host (pinned, [T, K]) is copied to x_dev,
     multiplied on the GPU (FP32 out), and the result lands in y_host (pinned, [T, rows]). All on the current stream;
-    the caller synchronises. The buffers are caller-owned so the call itself allocates nothing."""
+    the caller synchronises. The buffers are caller-owned so the call itself allocates nothing.
+    With y_dev=None the kernel writes the logits straight into the pinned host buffer (the stores cross PCIe while the
+    rest of the matrix is still being multiplied, so no copy follows the kernel); otherwise they go to y_dev and are
+    copied. The activation is always copied first: every block reads all of it, which is slow across PCIe (measured:
+    279 µs per step reading x from host memory against 225 µs with the 4 KB copy)."""
     x_dev.copy_(x_host, non_blocking=True)
-    mmv(x_dev, w, out=y_dev)
-    y_host.copy_(y_dev, non_blocking=True)
+    if y_dev is None:
+        mmv(x_dev, w, out=y_host)
+    else:
+        mmv(x_dev, w, out=y_dev)
+        y_host.copy_(y_dev, non_blocking=True)
 
 
 def get_rows(ids: torch.Tensor, w: Weight, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:

@@ -274,7 +274,14 @@ def test_linear_host_round_trip(ops):
     xd, yd = torch.empty_like(xh, device="cuda"), torch.empty(1, 1024, dtype=torch.float32, device="cuda")
     ops.linear_host(xh, enc, yh, xd, yd)
     torch.cuda.synchronize()
-    assert torch.equal(yh, ops.mmv(xh.cuda(), enc).cpu())
+    want = ops.mmv(xh.cuda(), enc).cpu()
+    assert torch.equal(yh, want)
+    yh.zero_()
+    ops.linear_host(xh, enc, yh, xd)  # no device buffer: the kernel stores into the pinned host buffer itself
+    torch.cuda.synchronize()
+    assert torch.equal(yh, want)
+    with pytest.raises(RuntimeError, match="pinned"):
+        ops.mmv(xh.cuda(), enc, out=torch.empty(1, 1024))
 
 
 # ---------------------------------------------------------------- MoE pieces
