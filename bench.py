@@ -140,6 +140,21 @@ def cpu_arm(rows_sample: int, reps: int):
             "ms_per_step": dt * 1e3, "encode_s": t_enc, "passes": reps}, nbytes
 
 
+def reference_kernels():
+    """The reference's own CUDA kernels, recompiled for sm_100a (baseline/Makefile `ref`: its sources compiled where they
+    lie, binary in baseline/_ref/), timed on this GPU on the same shape through the same C++ interface. None when the
+    binary was not built."""
+    exe = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref", "api_bench_ref")
+    if not os.path.exists(exe):
+        return None
+    try:
+        out = subprocess.run([exe, "lm_head", "30"], capture_output=True, text=True, timeout=300).stdout
+        rec = json.loads([l for l in out.splitlines() if l.startswith("{")][-1])
+        return {"us_per_step": rec["us"], "compressed_GBps": rec["compressed_GBps"], "what": rec["impl"] + ", " + rec["workload"]}
+    except Exception as e:  # a missing CUDA runtime for the binary, a timeout: report, do not fail the bench
+        return {"unavailable": str(e)[:200]}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -356,6 +371,7 @@ def run_ours(args):
     if world == 1 and not args.no_cpu:
         base, _ = cpu_arm(CPU_SAMPLE_ROWS, 100)
         line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        line["reference_kernels_same_gpu"] = reference_kernels()
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -156,6 +156,7 @@ int bf16n_mmv(const bf16n_weight * w, const bf16n_mmv_args * a, void * stream, i
         check_x(*w, *a);
         if (a->nrows == 0) { return; }
         if (frag_order(*w)) { fo_gemv(*w, *a, (cudaStream_t) stream); return; }
+        if (expert_units_applies(*w, *a)) { expert_units_mmv(*w, *a, (cudaStream_t) stream); return; }
         gemv(*w, *a, (cudaStream_t) stream, multi_col != 0);
     });
 }
@@ -234,7 +235,11 @@ int bf16n_get_rows(const bf16n_weight * w, const void * ids, int64_t ids_s0, int
 }
 
 int bf16n_mm_ids_supported(const bf16n_weight * w, const bf16n_weight * up) {
-    if (w->fo || (up && up->fo)) { return device_info().sms > 0 && fo_mm_ids_supported(*w, up) ? 1 : 0; }
+    if (w->fo || (up && up->fo)) {
+        // the fragment-order kernel's shared-memory need is checked against the device: that needs bf16n_init
+        try { ensure_init(); } catch (...) { return 0; }
+        return fo_mm_ids_supported(*w, up) ? 1 : 0;
+    }
     return prefill_supported(*w, up) ? 1 : 0;
 }
 

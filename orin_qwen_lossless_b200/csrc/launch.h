@@ -94,6 +94,8 @@ void moe_route(const void * ids, bool ids_i64, int64_t ids_row_stride, int32_t *
 
 // moe_decode.cu
 void moe_decode_init();
+bool expert_units_applies(const bf16n_weight & w, const bf16n_mmv_args & a);
+void expert_units_mmv(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st);
 bool moe_decode_supported(const bf16n_weight & gate, const bf16n_weight & up, const bf16n_weight & down);
 void moe_decode(const bf16n_weight & gate, const bf16n_weight & up, const bf16n_weight & down, const void * x, bool x_bf16,
                 int64_t x_tok, const int32_t * ids, const float * weights, int n_tok, int n_used, int n_experts_local, int e_lo,

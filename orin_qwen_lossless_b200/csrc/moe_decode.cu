@@ -275,6 +275,35 @@ void moe_decode_init() {
     launch_units<4, 8, true, bf16, false>(none, none, 2, p, 0, nullptr);
     launch_units<4, 8, true, float, false>(none, none, 2, p, 0, nullptr);
     launch_units<1, 16, false, float, true>(none, none, 1, p, 0, nullptr);
+    launch_units<1, 16, false, float, false>(none, none, 1, p, 0, nullptr);
+    launch_units<1, 16, false, bf16, false>(none, none, 1, p, 0, nullptr);
+}
+
+// bf16n_mmv with expert ids on the expert shapes of the decode step takes the unit kernel too (one warp per unit, bulk-copy
+// staged), so the reference's own operator chain (mmv gate, mmv up, swiglu, mmv down) gets it without calling the fused
+// entry point. Results are bit-identical to the general routed kernels.
+bool expert_units_applies(const bf16n_weight & w, const bf16n_mmv_args & a) {
+    if (!a.ids || a.y_bf16 || !(gate_shape_ok(w) || down_shape_ok(w)) || a.n_used <= 0 || a.ncols % a.n_used) { return false; }
+    const bool whole = a.row0 == 0 && a.nrows == a.rows_per_matrix && a.nrows > 0 && w.rows % a.rows_per_matrix == 0;
+    const bool dense_y = a.y_slot == a.nrows * 4 && a.y_tok == (int64_t) a.n_used * a.nrows * 4;
+    const bool x_ok = a.x_per_slot == 1 || a.x_per_slot == a.n_used;
+    return whole && dense_y && x_ok && a.ncols <= 65535;
+}
+
+void expert_units_mmv(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st) {
+    ExpertCols p = {};
+    p.x = (const char *) a.x; p.x_tok = a.x_tok; p.x_slot = a.x_per_slot == 1 ? 0 : a.x_slot;
+    p.ids = (const char *) a.ids; p.ids_s0 = a.ids_s0; p.ids_s1 = a.ids_s1;
+    p.n_used = a.n_used; p.rows_per_expert = a.rows_per_matrix; p.e_lo = 0; p.e_n = (int) (w.rows / a.rows_per_matrix);
+    p.cap_bytes = unit_cap(w);
+    const ExpertMat m = expert_mat(w, (float *) a.y);
+    if (w.cm) {
+        if (a.x_bf16) { launch_units<4, 8, true, bf16, false>(m, m, 1, p, a.ncols, st); }
+        else { launch_units<4, 8, true, float, false>(m, m, 1, p, a.ncols, st); }
+    } else {
+        if (a.x_bf16) { launch_units<1, 16, false, bf16, false>(m, m, 1, p, a.ncols, st); }
+        else { launch_units<1, 16, false, float, false>(m, m, 1, p, a.ncols, st); }
+    }
 }
 
 // gate/up (chunk-major R = 8, K = 2048) -> silu(g) * u -> down (row-major R = 16, K = 512) -> weighted sum over slots.
