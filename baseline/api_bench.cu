@@ -4,7 +4,7 @@
 // include/bf16n/*.h + libbf16n_b200.so, which shows that the interface is a drop-in and gives both numbers on identical
 // inputs. Test and measurement infrastructure only; the build recipe is baseline/Makefile.
 //
-//   api_bench [lm_head|moe_decode|moe_prefill|all] [reps]
+//   api_bench [lm_head|moe_decode|moe_prefill|small|all|frag_order] [reps]
 //
 // Synthetic inputs as in bench.py: weights N(0, 0.02) rounded to BF16 (mt19937_64, seed per tensor), activations N(0, 1)
 // rounded to BF16. Every timing is the median of `reps` CUDA-event measurements after warm-up; working sets larger than
@@ -63,9 +63,9 @@ static Dev upload(const bf16n::encoded & e, int64_t rows, int64_t K) {
     d.bytes = e.plane.size() + e.aux.size();
     return d;
 }
-static Dev make(int64_t rows, int64_t K, int format, int R, bool cm, uint64_t seed) {
+static Dev make(int64_t rows, int64_t K, int format, int R, bool cm, uint64_t seed, bool fo = false) {
     const std::vector<uint16_t> w = normal_bf16((size_t) rows * K, 0.02f, seed);
-    return upload(bf16n::encode(w.data(), rows, K, format, R, cm), rows, K);
+    return upload(bf16n::encode(w.data(), rows, K, format, R, cm, fo), rows, K);
 }
 template <typename T> static T * dev_copy(const std::vector<T> & v) {
     T * p;
@@ -116,6 +116,107 @@ static void lm_head(int reps) {
     const double us = median_us(reps, [&](int) { bf16n::mmv(d.w, a, 0); });
     printf("{\"impl\": \"%s\", \"workload\": \"lm_head 248320x2048 HUFPAIR R=16, batch-1 GEMV\", \"us\": %.2f, \"compressed_GBps\": %.1f, "
            "\"sum_abs_y\": %.6e}\n", IMPL_NAME, us, (double) d.bytes / us / 1e3, checksum(y, rows, "lm_head"));
+}
+
+// ---- config 2: 48 layers x {2048x512, 512x2048, 256x2048} NIBBLE, batch-1 GEMVs, captured into one CUDA graph
+static void small(int reps) {
+    struct L { Dev a, b, c; float * ya, * yb, * yc; };
+    std::vector<L> layers(48);
+    size_t bytes = 0;
+    for (int l = 0; l < 48; l++) {
+        L & s = layers[l];
+        s.a = make(2048, 512, bf16n::FMT_NIBBLE, 0, false, 300 + 3 * l);
+        s.b = make(512, 2048, bf16n::FMT_NIBBLE, 0, false, 301 + 3 * l);
+        s.c = make(256, 2048, bf16n::FMT_NIBBLE, 0, false, 302 + 3 * l);
+        CK(cudaMalloc(&s.ya, 2048 * 4)); CK(cudaMalloc(&s.yb, 512 * 4)); CK(cudaMalloc(&s.yc, 256 * 4));
+        bytes += s.a.bytes + s.b.bytes + s.c.bytes;
+    }
+    const uint16_t * x512 = dev_copy(normal_bf16(512, 1.f, 3)), * x2048 = dev_copy(normal_bf16(2048, 1.f, 4));
+    cudaStream_t st;
+    CK(cudaStreamCreate(&st));
+    auto one = [&](const Dev & d, const uint16_t * x, float * y, int64_t rows, int64_t K) {
+        bf16n::mmv_args a;
+        a.x = x; a.x_bf16 = true; a.y = y; a.y_bf16 = false; a.ncols = 1; a.x_tok = K * 2; a.y_tok = rows * 4;
+        a.rows_per_matrix = rows; a.row0 = 0; a.nrows = rows;
+        bf16n::mmv(d.w, a, st);
+    };
+    auto all = [&] { for (L & s : layers) { one(s.a, x512, s.ya, 2048, 512); one(s.b, x2048, s.yb, 512, 2048); one(s.c, x2048, s.yc, 256, 2048); } };
+    all();
+    CK(cudaStreamSynchronize(st));
+    cudaGraph_t graph; cudaGraphExec_t exec;
+    CK(cudaStreamBeginCapture(st, cudaStreamCaptureModeGlobal));
+    all();
+    CK(cudaStreamEndCapture(st, &graph));
+    CK(cudaGraphInstantiate(&exec, graph, 0));
+    cudaEvent_t e0, e1;
+    CK(cudaEventCreate(&e0)); CK(cudaEventCreate(&e1));
+    for (int i = 0; i < 5; i++) { CK(cudaGraphLaunch(exec, st)); }
+    CK(cudaStreamSynchronize(st));
+    std::vector<float> t(reps);
+    for (int i = 0; i < reps; i++) {
+        CK(cudaEventRecord(e0, st)); CK(cudaGraphLaunch(exec, st)); CK(cudaEventRecord(e1, st));
+        CK(cudaEventSynchronize(e1)); CK(cudaEventElapsedTime(&t[i], e0, e1));
+    }
+    std::sort(t.begin(), t.end());
+    const double us = t[reps / 2] * 1e3;
+    printf("{\"impl\": \"%s\", \"workload\": \"small matrices: 48 layers x 3 NIBBLE GEMVs in one CUDA graph\", \"us\": %.1f, \"us_per_gemv\": %.2f, "
+           "\"compressed_GBps\": %.1f, \"sum_abs_y\": %.6e}\n", IMPL_NAME, us, us / 144, (double) bytes / us / 1e3,
+           checksum(layers[47].ya, 2048, "small"));
+}
+
+// ---- the fragment-order layout (what the reference's vLLM policy picks): projection at 1 and 8 tokens, prefill layer
+static void frag_order(int reps) {
+    {
+        const int64_t rows = 248320, K = 2048;
+        const Dev d = make(rows, K, bf16n::FMT_HUFPAIR, 16, false, 1, true);
+        for (int T : {1, 8}) {
+            const uint16_t * x = dev_copy(normal_bf16((size_t) T * K, 1.f, 2));
+            float * y;
+            CK(cudaMalloc(&y, (size_t) T * rows * 4));
+            bf16n::mmv_args a;
+            a.x = x; a.x_bf16 = true; a.y = y; a.y_bf16 = false; a.ncols = T; a.x_tok = K * 2; a.y_tok = rows * 4;
+            a.rows_per_matrix = rows; a.row0 = 0; a.nrows = rows;
+            const double us = median_us(reps, [&](int) { bf16n::mmv(d.w, a, 0); });
+            printf("{\"impl\": \"%s\", \"workload\": \"lm_head 248320x2048 fragment order, %d token(s)\", \"us\": %.2f, \"sum_abs_y\": %.6e}\n",
+                   IMPL_NAME, T, us, checksum(y, (size_t) T * rows, "fo_lm_head_" + std::to_string(T)));
+            CK(cudaFree(y));
+        }
+        CK(cudaFree((void *) d.w.plane)); CK(cudaFree((void *) d.w.aux));
+    }
+    const int E = 256, k = 8, H = 2048, N = 512, T = 2048;
+    const Dev gate = make((int64_t) E * N, H, bf16n::FMT_HUFPAIR, 16, false, 11, true);
+    const Dev up = make((int64_t) E * N, H, bf16n::FMT_HUFPAIR, 16, false, 12, true);
+    const Dev down = make((int64_t) E * H, N, bf16n::FMT_HUFPAIR, 16, false, 13, true);
+    if (!bf16n::mm_ids_supported(gate.w, &up.w) || !bf16n::mm_ids_supported(down.w, nullptr)) {
+        printf("{\"impl\": \"%s\", \"workload\": \"MoE prefill, fragment order\", \"unavailable\": \"no batched kernel\"}\n", IMPL_NAME);
+        return;
+    }
+    std::mt19937_64 g(200 + T);
+    std::vector<int32_t> ids((size_t) T * k);
+    for (int t = 0; t < T; t++) {
+        std::vector<int> perm(E);
+        for (int i = 0; i < E; i++) { perm[i] = i; }
+        std::shuffle(perm.begin(), perm.end(), g);
+        for (int s = 0; s < k; s++) { ids[(size_t) t * k + s] = perm[s]; }
+    }
+    const int32_t * d_ids = dev_copy(ids);
+    const std::vector<float> wts((size_t) T * k, 1.f / k);
+    const float * d_w = dev_copy(wts);
+    const uint16_t * x = dev_copy(normal_bf16((size_t) T * H, 1.f, 30));
+    int32_t * src1, * dst, * bounds;
+    CK(cudaMalloc(&src1, (size_t) T * k * 4)); CK(cudaMalloc(&dst, (size_t) T * k * 4)); CK(cudaMalloc(&bounds, (E + 1) * 4));
+    uint16_t * act; float * ys, * y;
+    CK(cudaMalloc(&act, (size_t) T * k * N * 2)); CK(cudaMalloc(&ys, (size_t) T * k * H * 4)); CK(cudaMalloc(&y, (size_t) T * H * 4));
+    auto step = [&](int) {
+        bf16n::mm_ids_route(d_ids, false, k, src1, dst, bounds, E, T, k, 1, 1, 0);
+        bf16n::mm_ids(gate.w, &up.w, x, H, src1, dst, bounds, act, true, N, E, T, k, 0);
+        bf16n::mm_ids_route(d_ids, false, k, src1, dst, bounds, E, T, k, k, k, 0);
+        bf16n::mm_ids(down.w, nullptr, act, N, src1, dst, bounds, ys, false, H, E, T, k, 0);
+        bf16n::moe_combine(ys, d_w, false, y, false, T, k, H, 0);
+    };
+    const double us = median_us(std::max(5, reps / 4), step);
+    printf("{\"impl\": \"%s\", \"workload\": \"MoE prefill layer, %d tokens, fragment-order experts\", \"us\": %.1f, \"TFLOPs\": %.1f, "
+           "\"sum_abs_y\": %.6e}\n", IMPL_NAME, T, us, 6.0 * N * H * k * T / us / 1e6, checksum(y, (size_t) T * H, "fo_moe_prefill_2048"));
 }
 
 // ---- config 3: MoE decode layer through the operator chain of the reference's Python layer
@@ -216,5 +317,7 @@ int main(int argc, char ** argv) {
     if (what == "lm_head" || what == "all") { lm_head(reps); }
     if (what == "moe_decode" || what == "all") { moe_decode(reps); }
     if (what == "moe_prefill" || what == "all") { moe_prefill(reps); }
+    if (what == "small" || what == "all") { small(reps); }
+    if (what == "frag_order" || what == "more") { frag_order(reps); }
     return 0;
 }

@@ -97,10 +97,20 @@ __global__ void __launch_bounds__(256) k_route(const TI * __restrict__ ids, int6
     __shared__ int warp_tot[8];
     __shared__ int s_base;
 
+    // int32 ids in contiguous rows of a multiple of four: four ids per load (the common case: 8 slots per token)
+    const bool vec = sizeof(TI) == 4 && n_used % 4 == 0 && row_stride == n_used && ((uintptr_t) ids & 15) == 0;
     int lower = 0;
-    for (int64_t i = tid; i < (int64_t) n_tok * n_used; i += 256) {
-        const int t = (int) (i / n_used), s = (int) (i - (int64_t) t * n_used);
-        lower += (int) ids[t * row_stride + s] < e;
+    if (vec) {
+        const int4 * v = (const int4 *) ids;
+        for (int64_t i = tid; i < (int64_t) n_tok * n_used / 4; i += 256) {
+            const int4 q = __ldg(v + i);
+            lower += (q.x < e) + (q.y < e) + (q.z < e) + (q.w < e);
+        }
+    } else {
+        for (int64_t i = tid; i < (int64_t) n_tok * n_used; i += 256) {
+            const int t = (int) (i / n_used), s = (int) (i - (int64_t) t * n_used);
+            lower += (int) ids[t * row_stride + s] < e;
+        }
     }
 #pragma unroll
     for (int o = 16; o; o >>= 1) { lower += __shfl_xor_sync(FULL, lower, o); }
@@ -118,8 +128,19 @@ __global__ void __launch_bounds__(256) k_route(const TI * __restrict__ ids, int6
         const int t = t0 + tid;
         int slot = -1;
         if (t < n_tok) {
-            for (int s = 0; s < n_used; s++) {
-                if ((int) ids[t * row_stride + s] == e) { slot = s; break; }
+            if (vec) {
+                const int4 * v = (const int4 *) ids + (int64_t) t * (n_used / 4);
+                for (int s4 = n_used / 4 - 1; s4 >= 0; s4--) { // downwards, so that the lowest matching slot wins
+                    const int4 q = __ldg(v + s4);
+                    slot = q.w == e ? 4 * s4 + 3 : slot;
+                    slot = q.z == e ? 4 * s4 + 2 : slot;
+                    slot = q.y == e ? 4 * s4 + 1 : slot;
+                    slot = q.x == e ? 4 * s4 : slot;
+                }
+            } else {
+                for (int s = 0; s < n_used; s++) {
+                    if ((int) ids[t * row_stride + s] == e) { slot = s; break; }
+                }
             }
         }
         const unsigned hit = __ballot_sync(FULL, slot >= 0);

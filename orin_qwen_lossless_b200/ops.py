@@ -394,7 +394,9 @@ def moe_route(topk_ids: torch.Tensor, n_experts: int, per_slot: bool):
 
 
 def moe_mm_ids(x: torch.Tensor, topk_ids: torch.Tensor, w: Weight, n_experts: int, up: Weight | None = None,
-               out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+               out_dtype: torch.dtype = torch.float32, route=None) -> torch.Tensor:
+    """Batched routed product (more than 8 tokens). route: the (ids_src1, ids_dst, bounds) of moe_route for these ids and
+    this activation layout, when the caller already has them (moe_experts sorts once for both of its products)."""
     cw = w.c()
     cu = up.c() if up is not None else None
     _check_ids(topk_ids)
@@ -413,7 +415,7 @@ def moe_mm_ids(x: torch.Tensor, topk_ids: torch.Tensor, w: Weight, n_experts: in
         return y
     if not lib().bf16n_mm_ids_supported(C.byref(cw), C.byref(cu) if cu is not None else None):
         raise ValueError("bf16n.moe_mm_ids: no batched kernel for this matrix (format/K/R/layout)")
-    src1, dst, bounds = moe_route(topk_ids, n_experts, per_slot)
+    src1, dst, bounds = moe_route(topk_ids, n_experts, per_slot) if route is None else route
     with torch.cuda.device(x.device):
         check(lib().bf16n_mm_ids(C.byref(cw), C.byref(cu) if cu is not None else None, x.data_ptr(), w.meta.K,
                                  src1.data_ptr(), dst.data_ptr(), bounds.data_ptr(), y.data_ptr(),
@@ -471,8 +473,11 @@ def moe_experts(x: torch.Tensor, gate: Weight, up: Weight, down: Weight, topk_we
     H = down.meta.rows // n_experts
     x = x.contiguous()
     if T > GEMV_MAX_TOKENS and mm_ids_supported(gate, up) and mm_ids_supported(down):
-        a = moe_mm_ids(x, topk_ids, gate, n_experts, up=up, out_dtype=torch.bfloat16)
-        ys = moe_mm_ids(a, topk_ids, down, n_experts, out_dtype=torch.float32)
+        # one routing sort serves both products: with one activation row per (token, slot) a pair's source row is its
+        # destination row, so the down product reads ids_dst in both roles
+        src1, dst, bounds = moe_route(topk_ids, n_experts, False)
+        a = moe_mm_ids(x, topk_ids, gate, n_experts, up=up, out_dtype=torch.bfloat16, route=(src1, dst, bounds))
+        ys = moe_mm_ids(a, topk_ids, down, n_experts, out_dtype=torch.float32, route=(dst, dst, bounds))
     else:
         g = mmv(x, gate, topk_ids, N)
         u = mmv(x, up, topk_ids, N)

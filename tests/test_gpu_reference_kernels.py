@@ -1,6 +1,6 @@
 """This library against the reference's own CUDA kernels on the same GPU, same inputs, through the same C++ interface:
 baseline/api_bench.cu is built once against include/bf16n/*.h + libbf16n_b200.so and once against the reference's headers
-and sources recompiled for sm_100a (baseline/Makefile). The vocabulary projection and the routed-expert decode chain must
+and sources recompiled for sm_100a (baseline/Makefile). The vocabulary projection, the small NIBBLE GEMVs and the routed-expert decode chain must
 give the reference's FP32 results bit for bit (same summation order); the batched prefill layer, whose tensor-core
 accumulation order differs and whose intermediate is BF16 in both, must agree to 2^-9 of the largest output.
 Skipped when the reference build of the driver is not present (it is not part of the repository)."""
@@ -23,7 +23,7 @@ def test_outputs_match_the_reference_kernels(tmp_path):
         subprocess.run([exe, "all", "3"], check=True, env=env, stdout=subprocess.DEVNULL, timeout=600)
     names = sorted(f[len("ref_"):] for f in os.listdir(tmp_path) if f.startswith("ref_"))
     assert names == ["lm_head.f32", "moe_decode_1.f32", "moe_decode_2.f32", "moe_decode_4.f32", "moe_prefill_2048.f32",
-                     "moe_prefill_8192.f32"]
+                     "moe_prefill_8192.f32", "small.f32"]
     for n in names:
         a = np.fromfile(tmp_path / ("ours_" + n), np.float32)
         b = np.fromfile(tmp_path / ("ref_" + n), np.float32)
