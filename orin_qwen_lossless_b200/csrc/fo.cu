@@ -12,7 +12,7 @@
 // no operand form for register fragments, so this small-N product stays on the warp-level instruction), while single
 // columns, FP32 activations and routed columns use FMAs: a lane keeps two FP32 accumulators per column (its two rows)
 // and the four lanes of a row quad are added at the end. Results are within FP32 rounding of FP64 either way (tested).
-#include "decode.cuh"
+#include "staged.cuh"
 #include "launch.h"
 
 namespace b16 {
@@ -353,6 +353,116 @@ __global__ void __launch_bounds__(256) k_fo_mm_ids(const FoBatch p) {
     }
 }
 
+// The same product with the streams staged: persistent blocks of 8 warps, a warp walks bands and copies each slab's
+// stream block into its own shared-memory buffer with one bulk async copy (two buffers in turn, so the next slab's copy
+// runs under the current slab's decoding; bounded wait, as in gemv_staged.cu), reads it with the staged reader and
+// prefetches the plane bytes one tile pair ahead. Serves 1..8 dense BF16 columns. A slab whose streams do not fit the
+// buffer (more than 3 bits per weight) is read straight from global memory.
+constexpr uint32_t FO_CAP = (BAND * CHUNK * 3 / 8 + 64 + 15) & ~15u;
+
+__global__ void __launch_bounds__(256) k_fo_gemv_staged(const PairView w, const AuxHeader * hdr, int C, Cols p, int ncols, const Opaque k) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    uint32_t * lut = (uint32_t *) smem;
+    uint64_t * bars = (uint64_t *) (smem + 4 * HP_MAX_PAIRS);            // two per warp
+    const int K = C * CHUNK, XS = K + XPAD;
+    bf16 * xs = (bf16 *) (smem + 4 * HP_MAX_PAIRS + 128);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    unsigned char * buf = smem + 4 * HP_MAX_PAIRS + 128 + (size_t) 8 * XS * 2 + (size_t) warp * 2 * FO_CAP;
+    stage_lut(lut, w.lut);
+    if (lane == 0) { mbar_init(smem_u32(bars + 2 * warp), 1); mbar_init(smem_u32(bars + 2 * warp + 1), 1); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    grid_dependency_wait();
+    for (int i = threadIdx.x; i < 8 * (K / 8); i += blockDim.x) { // 16-byte pieces; columns beyond ncols are zero
+        const int n = i / (K / 8), c = i - n * (K / 8);
+        const uint4 v = n < ncols ? __ldg((const uint4 *) (p.x + n * p.x_tok) + c) : make_uint4(0, 0, 0, 0);
+        *(uint4 *) (xs + n * XS + c * 8) = v;
+    }
+    const uint32_t n_units = (uint32_t) hdr->n_a, n_words = (uint32_t) hdr->n_b;
+    __syncthreads();
+    struct Geo { uint32_t start, bytes, my; };
+    auto geometry = [&](int64_t gu) {
+        const uint32_t w0 = __ldg(w.ubase + gu);
+        const uint32_t w1 = gu + 1 < (int64_t) n_units ? __ldg(w.ubase + gu + 1) : n_words;
+        Geo g;
+        g.start = w0 & ~3u;
+        g.bytes = ((w1 - g.start + 4u + 3u) & ~3u) * 4u;
+        g.my = w0 - g.start + __ldg(w.lrel + gu * 32 + lane);
+        return g;
+    };
+    auto stage = [&](const Geo & g, int b) { // one lane starts the copy of a slab's streams into buffer b
+        if (g.bytes <= FO_CAP && lane == 0) {
+            const uint32_t bar = smem_u32(bars + 2 * warp + b);
+            mbar_expect_tx(bar, g.bytes);
+            bulk_g2s(smem_u32(buf + b * FO_CAP), w.stream + g.start, g.bytes, bar);
+        }
+    };
+    const int g8 = lane >> 2, t4 = lane & 3;
+    const bf16 * xl = xs + g8 * XS + 2 * t4;
+    uint32_t parity = 0u; // bit b: phase of buffer b's barrier
+    const int64_t bands = p.nrows / BAND;
+    for (int64_t b = (int64_t) blockIdx.x * nwarp + warp; b < bands; b += (int64_t) gridDim.x * nwarp) {
+        const int64_t gband = p.row0 / BAND + b;
+        float d[4] = {0.f, 0.f, 0.f, 0.f};
+        Geo cur = geometry(gband * C);
+        __syncwarp(); // every lane is done with both buffers (previous band)
+        stage(cur, 0);
+        for (int slab = 0; slab < C; slab++) {
+            Geo nxt = {0, 0, 0};
+            if (slab + 1 < C) {
+                nxt = geometry(gband * C + slab + 1);
+                __syncwarp(); // the buffer about to be refilled was read two slabs ago by every lane
+                stage(nxt, (slab + 1) & 1);
+            }
+            const uint8_t * pl = w.plane + gband * BAND * (int64_t) K + (int64_t) slab * (16 * 512) + 16 * lane;
+            auto body = [&](auto & rd, uint32_t lut_arg) {
+                uint4 nx = ld_stream16(pl);
+                for (int pp = 0; pp < 16; pp++) {
+                    const uint4 cu = nx;
+                    if (pp + 1 < 16) { nx = ld_stream16(pl + (pp + 1) * 512); }
+                    uint32_t e[8], a[8];
+                    rd.take8(lut_arg, k, e);
+                    assemble8(cu, e, a);
+#pragma unroll
+                    for (int kk = 0; kk < 2; kk++) {
+                        const int col = (slab * 32 + 2 * pp + kk) * 16;
+                        const uint32_t b0 = *(const uint32_t *) (xl + col), b1 = *(const uint32_t *) (xl + col + 8);
+                        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+                                     "{%0, %1, %2, %3};"
+                                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                                     : "r"(a[4 * kk]), "r"(a[4 * kk + 1]), "r"(a[4 * kk + 2]), "r"(a[4 * kk + 3]), "r"(b0), "r"(b1));
+                    }
+                }
+            };
+            if (cur.bytes <= FO_CAP) {
+                const int bi = slab & 1;
+                const uint32_t landed = mbar_wait(smem_u32(bars + 2 * warp + bi), (parity >> bi) & 1u);
+                if (!landed) {
+                    if (lane == 0) { atomicOr(&g_wait_expired, 1u); }
+                    return;
+                }
+                parity ^= 1u << bi;
+                StagedReader rd;
+                rd.open(smem_u32(buf + bi * FO_CAP) + 4 * cur.my, landed);
+                body(rd, smem_u32(lut));
+            } else {
+                GlobalReader rd;
+                rd.lut = lut;
+                rd.rd.open(w, gband * C + slab, lane);
+                body(rd, 0u);
+            }
+            cur = nxt;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int n = 2 * t4 + (i & 1);
+            if (n < ncols) {
+                const OutVec o = {p.y + n * p.y_tok, p.y_bf16};
+                o.put(b * BAND + g8 + 8 * (i >> 1), d[i]);
+            }
+        }
+    }
+}
+
 template <int NC, typename TX>
 void launch_fo(const bf16n_weight & w, const Cols & p, int ncols_grid, cudaStream_t st) {
     const int C = (int) (w.K / CHUNK);
@@ -372,17 +482,29 @@ void fo_gemv_t(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st
         launch_fo<1, TX>(w, p, a.ncols, st);
         return;
     }
-    if (a.x_bf16 && a.ncols >= 2) { // BF16 activations, several tokens: the tensor-core kernel, 8 columns per decode
+    if (a.x_bf16 && (a.ncols >= 2 || p.nrows / BAND >= (int64_t) device_info().sms * 16)) {
+        // BF16 activations: the tensor-core kernels, 8 columns per decode. Large matrices (at least 16 bands per SM) take
+        // the persistent kernel with staged streams, also for a single column.
         const int C = (int) (w.K / CHUNK);
         const int64_t bands = p.nrows / BAND, sms = device_info().sms;
-        const int warps = bands >= sms * 32 ? 8 : bands >= sms * 8 ? 4 : 2;
-        const dim3 grid((unsigned) std::min<int64_t>((bands + warps - 1) / warps, sms * 8));
-        const size_t shm = 4 * HP_MAX_PAIRS + (size_t) 8 * (w.K + XPAD) * 2;
+        const size_t x_bytes = (size_t) 8 * (w.K + XPAD) * 2;
+        const size_t shm_staged = 4 * HP_MAX_PAIRS + 128 + x_bytes + (size_t) 8 * 2 * FO_CAP;
+        const bool big = bands >= sms * 16 && (uintptr_t) p.x % 16 == 0 && p.x_tok % 16 == 0;
         for (int c0 = 0; c0 < a.ncols; c0 += 8) {
             Cols q = p;
             q.x += c0 * p.x_tok;
             q.y += c0 * p.y_tok;
-            launch_chained(k_fo_gemv_mma, grid, dim3(warps * 32), shm, st, pair_view(w), C, q, std::min(8, a.ncols - c0));
+            const int nc = std::min(8, a.ncols - c0);
+            if (big) {
+                const int per_sm = std::max(1, (int) (device_info().smem_optin / (shm_staged + 1024)));
+                const Opaque k = {1u, 4u, ~0u, 32u};
+                launch_chained(k_fo_gemv_staged, dim3((unsigned) (sms * per_sm)), dim3(256), shm_staged, st, pair_view(w),
+                               (const AuxHeader *) w.aux, C, q, nc, k);
+            } else {
+                const int warps = bands >= sms * 32 ? 8 : bands >= sms * 8 ? 4 : 2;
+                const dim3 grid((unsigned) std::min<int64_t>((bands + warps - 1) / warps, sms * 8));
+                launch_chained(k_fo_gemv_mma, grid, dim3(warps * 32), 4 * HP_MAX_PAIRS + x_bytes, st, pair_view(w), C, q, nc);
+            }
         }
         return;
     }
@@ -409,6 +531,7 @@ void fo_init() {
     ATTR((k_fo_gemv<1, float>)); ATTR((k_fo_gemv<2, float>)); ATTR((k_fo_gemv<4, float>)); ATTR((k_fo_gemv<8, float>));
     ATTR((k_fo_gemv<1, bf16>)); ATTR((k_fo_gemv<2, bf16>)); ATTR((k_fo_gemv<4, bf16>)); ATTR((k_fo_gemv<8, bf16>));
     ATTR(k_fo_gemv_mma);
+    ATTR(k_fo_gemv_staged);
     // these two also have a little static shared memory: ask for what they use, not for the whole opt-in limit
     cuda_ok(cudaFuncSetAttribute(k_fo_mm_ids<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * HP_MAX_PAIRS + FO_TOK * FO_XS * 2), "k_fo_mm_ids");
     cuda_ok(cudaFuncSetAttribute(k_fo_mm_ids<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * HP_MAX_PAIRS + FO_TOK * FO_XS * 2), "k_fo_mm_ids glu");

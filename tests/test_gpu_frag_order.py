@@ -76,6 +76,20 @@ def test_dense_gemv_against_fp64(ops, rows, K, T):
     assert torch.equal(yb.view(torch.int16), y.to(torch.bfloat16).view(torch.int16))
 
 
+@pytest.mark.parametrize("K,T", [(512, 1), (512, 8), (2048, 1), (2048, 5)])
+def test_large_matrix_kernel(ops, K, T):
+    """At least 16 bands per SM: the persistent kernel with bulk-copy staged streams (also for one token)."""
+    rows = 16 * 16 * 160
+    bits = o.weights_like(rows, K, K + T)
+    w = fo(ops, bits)
+    x, x64 = act((T, K), 30 + T)
+    w64 = o.bf16_bits_to_f32(bits).astype(np.float64)
+    ref, s = x64 @ w64.T, np.abs(x64) @ np.abs(w64).T
+    y = ops.mmv(x, w)
+    assert (np.abs(y.cpu().numpy() - ref) <= GEMV_REL * s).all()
+    assert torch.equal(ops.mmv(x[:1].contiguous(), w)[0], y[0])  # a column does not depend on its batch
+
+
 def test_routed_columns(ops):
     E, rows_e, K, T, k = 4, 512, 512, 3, 2
     bits = o.weights_like(E * rows_e, K, 77)
