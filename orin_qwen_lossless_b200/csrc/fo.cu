@@ -274,6 +274,7 @@ __global__ void __launch_bounds__(256) k_fo_mm_ids(const FoBatch p) {
     const int64_t bands_e = p.rows_per_expert / BAND, K = (int64_t) p.C * CHUNK;
     const int groups_e = (int) ((bands_e + 7) / 8);
     const int g = lane >> 2, t = lane & 3;
+    const uint32_t xs_s = smem_u32(xs);
     for (int item = blockIdx.x; item < p.n_experts * groups_e; item += gridDim.x) {
         const int e = item / groups_e;
         const int64_t band = (int64_t) (item - e * groups_e) * 8 + warp;   // inside the expert
@@ -293,21 +294,25 @@ __global__ void __launch_bounds__(256) k_fo_mm_ids(const FoBatch p) {
 #pragma unroll
                 for (int c = 0; c < 4; c++) { d0[i][c] = 0.f; if (GLU) { d1[i][c] = 0.f; } }
             }
+            const int ng2 = (ng + 1) & ~1; // groups are multiplied in pairs: an odd last group gets a zero partner
             for (int slab = 0; slab < p.C; slab++) {
                 __syncthreads(); // tok_* visible; every warp is done with the previous slab's activations
-                for (int i = threadIdx.x; i < ng * 8 * (CHUNK / 8); i += blockDim.x) { // 16-byte pieces; missing tokens: zeros
+                // 16-byte asynchronous copies, all in flight at once (missing tokens: zero fill), one wait for the lot
+                for (int i = threadIdx.x; i < ng2 * 8 * (CHUNK / 8); i += blockDim.x) {
                     const int row = i / (CHUNK / 8), piece = i - row * (CHUNK / 8);
-                    uint4 v = make_uint4(0, 0, 0, 0);
-                    if (tok_src[row] >= 0) { v = __ldg((const uint4 *) (p.x + (int64_t) tok_src[row] * p.x_row + slab * CHUNK) + piece); }
-                    *(uint4 *) (xs + row * FO_XS + piece * 8) = v;
+                    const bool have = tok_src[row] >= 0;
+                    const bf16 * src = p.x + (have ? (int64_t) tok_src[row] * p.x_row + slab * CHUNK + piece * 8 : 0);
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(xs_s + (uint32_t) ((row * FO_XS + piece * 8) * 2)),
+                                 "l"(src), "r"(have ? 16u : 0u) : "memory");
                 }
+                asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
                 __syncthreads();
                 if (!active) { continue; }
 #pragma unroll
                 for (int m = 0; m < (GLU ? 2 : 1); m++) {
                     const PairView & w = m ? p.w1 : p.w0;
                     const uint32_t * lut = m ? lut1 : lut0;
-                    PairReader rd;
+                    DeepPairReader rd;
                     rd.open(w, gband * p.C + slab, lane);
                     const uint8_t * pl = w.plane + gband * BAND * K + (int64_t) slab * (16 * 512) + 16 * lane;
                     uint4 nxt = ld_stream16(pl);
@@ -319,16 +324,25 @@ __global__ void __launch_bounds__(256) k_fo_mm_ids(const FoBatch p) {
                         assemble8(cur, en, a);
 #pragma unroll
                         for (int kk = 0; kk < 2; kk++) {
-                            const bf16 * xl = xs + g * FO_XS + (2 * pp + kk) * 16 + 2 * t;
+                            // B fragments of two token groups per ldmatrix.x4: lane 8j + r addresses row r of 8x8 matrix j =
+                            // (token group i + (j >> 1), k half j & 1); rows are tokens, 16 bytes of k each
+                            const uint32_t xaddr = xs_s + (uint32_t) ((((lane >> 4) * 8 + (lane & 7)) * FO_XS + (2 * pp + kk) * 16 + ((lane >> 3) & 1) * 8) * 2);
 #pragma unroll
-                            for (int i = 0; i < FO_TOK / 8; i++) {
+                            for (int i = 0; i < FO_TOK / 8; i += 2) {
                                 if (i < ng) {
-                                    const uint32_t b0 = *(const uint32_t *) (xl + i * 8 * FO_XS), b1 = *(const uint32_t *) (xl + i * 8 * FO_XS + 8);
+                                    uint32_t b0, b1, b2, b3;
+                                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                                                 : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(xaddr + (uint32_t) (i * 8 * FO_XS * 2)));
                                     float * d = m ? d1[GLU ? i : 0] : d0[i];
                                     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
                                                  "{%8, %9}, {%0, %1, %2, %3};"
                                                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                                                  : "r"(a[4 * kk]), "r"(a[4 * kk + 1]), "r"(a[4 * kk + 2]), "r"(a[4 * kk + 3]), "r"(b0), "r"(b1));
+                                    float * e2 = m ? d1[GLU ? i + 1 : 0] : d0[i + 1];
+                                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+                                                 "{%8, %9}, {%0, %1, %2, %3};"
+                                                 : "+f"(e2[0]), "+f"(e2[1]), "+f"(e2[2]), "+f"(e2[3])
+                                                 : "r"(a[4 * kk]), "r"(a[4 * kk + 1]), "r"(a[4 * kk + 2]), "r"(a[4 * kk + 3]), "r"(b2), "r"(b3));
                                 }
                             }
                         }
