@@ -199,12 +199,16 @@ struct PairReader {
     uint32_t ahead; // the word after the buffered ones, already loaded
     int have;
 
-    __device__ __forceinline__ void open(const PairView & w, int64_t unit, int lane) {
-        next = w.stream + (__ldg(w.ubase + unit) + __ldg(w.lrel + unit * 32 + lane));
-        buf = (uint64_t) __ldg(next) << 32 | __ldg(next + 1);
-        ahead = __ldg(next + 2);
-        next += 3;
+    // start at `first` with its three first words already loaded by the caller
+    __device__ __forceinline__ void open_loaded(const uint32_t * first, uint32_t w0, uint32_t w1, uint32_t w2) {
+        next = first + 3;
+        buf = (uint64_t) w0 << 32 | w1;
+        ahead = w2;
         have = 64;
+    }
+    __device__ __forceinline__ void open(const PairView & w, int64_t unit, int lane) {
+        const uint32_t * first = w.stream + (__ldg(w.ubase + unit) + __ldg(w.lrel + unit * 32 + lane));
+        open_loaded(first, __ldg(first), __ldg(first + 1), __ldg(first + 2));
     }
     __device__ __forceinline__ void top_up() {
         if (have <= 32) {
@@ -251,13 +255,15 @@ struct WidePairReader {
         }
         return w;
     }
-    __device__ __forceinline__ void open(const PairView & w, int64_t unit, int lane) {
-        const uint32_t * first = w.stream + (__ldg(w.ubase + unit) + __ldg(w.lrel + unit * 32 + lane));
+    // the aligned group that holds the stream's first word
+    static __device__ __forceinline__ const uint4 * group_of(const uint32_t * first) {
+        return (const uint4 *) (first - (((uintptr_t) first >> 2) & 3));
+    }
+    // start at `first` with its two first groups (group_of(first)[0], [1]) already loaded by the caller
+    __device__ __forceinline__ void open_loaded(const uint32_t * first, const uint4 & a, const uint4 & b) {
         const int skip = (int) (((uintptr_t) first >> 2) & 3); // words of the first aligned group before the stream
-        next = (const uint4 *) (first - skip);
-        const uint4 a = __ldg(next);
-        pre = __ldg(next + 1);
-        next += 2;
+        next = group_of(first) + 2;
+        pre = b;
         q0 = a.x; q1 = a.y; q2 = a.z; q3 = a.w;
         if (skip & 1) { q0 = q1; q1 = q2; q2 = q3; }
         if (skip & 2) { q0 = q2; q1 = q3; }
@@ -265,6 +271,11 @@ struct WidePairReader {
         const uint32_t hi = pop();
         buf = (uint64_t) hi << 32 | pop();
         have = 64;
+    }
+    __device__ __forceinline__ void open(const PairView & w, int64_t unit, int lane) {
+        const uint32_t * first = w.stream + (__ldg(w.ubase + unit) + __ldg(w.lrel + unit * 32 + lane));
+        const uint4 * g = group_of(first);
+        open_loaded(first, __ldg(g), __ldg(g + 1));
     }
     __device__ __forceinline__ void top_up() {
         if (have <= 32) {

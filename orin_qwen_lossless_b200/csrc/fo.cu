@@ -244,13 +244,22 @@ __global__ void __launch_bounds__(256) k_fo_gemv_mma(const PairView w, int C, Co
 // ---------------------------------------------------------------- batched routed product (prefill)
 
 // dst[t, slot, :] = W_e x_t for every routed (token, slot) pair, optionally fused gate/up + SwiGLU, for fragment-order
-// experts (replaces the reference's k_fo_mm_ids / k_fo_mm_glu, kernels.cuh:2070-2391). A block of 8 warps takes 8
-// consecutive bands of one expert (GLU: the same bands of gate and up, one after the other in the same warp, so that a
-// lane ends with gate and up of the same (row, token)). The expert's tokens come in passes of up to 64; per 512-column
-// slab their activation rows are gathered into shared memory once for the block, and every decoded tile is multiplied
-// with the pass's tokens eight at a time (mma.m16n8k16), accumulating D[16 rows, 64 tokens] in registers across slabs.
-constexpr int FO_TOK = 64;                      // tokens per pass
-constexpr int FO_XS = CHUNK + XPAD;             // padded activation row of one slab (BF16 elements)
+// experts (replaces the reference's k_fo_mm_ids / k_fo_mm_glu, kernels.cuh:2070-2391). One persistent block of 16 warps
+// per SM. An item is (expert, tile of up to 96 of its routed tokens, group of bands); a warp owns one band of the group
+// (GLU: warps 0-7 the gate bands, warps 8-15 the same bands of up) and keeps D[16 rows, 96 tokens] in registers over the
+// K / 512 slabs, so every weight is decoded once per (expert, token tile). The work is a sequence of steps (item, slab):
+// while a step is multiplied, the next step's activation rows are gathered into the other of two shared-memory buffers
+// with 16-byte asynchronous copies (one block barrier per step), the next unit's stream position and first three stream
+// words are loaded, and its plane and stream bytes are pulled into L2. Activation rows are 1024 bytes, their 16-byte
+// pieces XOR-swizzled by the row's low three bits so that ldmatrix reads eight rows without a bank conflict and no
+// padding is spent. SwiGLU: gate and up warps swap halves of their sums through the buffer just consumed, each then
+// finishes and stores half of the tile's tokens.
+constexpr int FO_TOK = 96;                      // tokens per tile
+constexpr int FO_NG = FO_TOK / 8;               // 8-token groups of a tile (multiplied in pairs)
+constexpr int FO_WARPS = 16;
+constexpr int FO_ROWB = CHUNK * 2;              // bytes of one staged activation row
+constexpr int FO_BUF = FO_TOK * FO_ROWB;
+static_assert(FO_NG % 2 == 0 && FO_WARPS * (FO_NG / 2) * 4 * 32 * 4 <= FO_BUF, "the swapped sums must fit one buffer");
 
 struct FoBatch {
     PairView w0, w1;
@@ -258,113 +267,205 @@ struct FoBatch {
     const int32_t * ids_src1; const int32_t * ids_dst; const int32_t * bounds;
     char * dst; int64_t dst_col; bool dst_bf16;
     int n_experts, C;
-    int64_t rows_per_expert;
+    int64_t rows_per_expert, n_units;
 };
 
+struct FoItem { int it, e, jb, ntok; int64_t band; bool valid, live; };
+
 template <bool GLU>
-__global__ void __launch_bounds__(256) k_fo_mm_ids(const FoBatch p) {
+__global__ void __launch_bounds__(FO_WARPS * 32, 1) k_fo_mm_ids(const FoBatch p) {
+    constexpr int NB = GLU ? FO_WARPS / 2 : FO_WARPS; // bands of a group
     extern __shared__ __align__(16) unsigned char smem[];
     uint32_t * lut0 = (uint32_t *) smem;
     uint32_t * lut1 = lut0 + (GLU ? HP_MAX_PAIRS : 0);
-    bf16 * xs = (bf16 *) (lut1 + HP_MAX_PAIRS);                 // FO_TOK rows of FO_XS
-    __shared__ int32_t tok_src[FO_TOK], tok_dst[FO_TOK];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned char * xb = (unsigned char *) (lut1 + HP_MAX_PAIRS);  // two buffers of FO_BUF
+    int32_t * toff = (int32_t *) (xb + 2 * FO_BUF);                // first tile of each expert, E + 1
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, E = p.n_experts, C = p.C;
+    const bool upw = GLU && warp >= NB;
+    const PairView & w = upw ? p.w1 : p.w0;
+    const uint32_t * lut = upw ? lut1 : lut0;
     stage_lut(lut0, p.w0.lut);
     if (GLU) { stage_lut(lut1, p.w1.lut); }
-    const int64_t bands_e = p.rows_per_expert / BAND, K = (int64_t) p.C * CHUNK;
-    const int groups_e = (int) ((bands_e + 7) / 8);
+    {   // tiles per expert (parked in the first buffer), then their exclusive prefix
+        int32_t * cnt = (int32_t *) xb;
+        for (int e = threadIdx.x; e < E; e += blockDim.x) { cnt[e] = (p.bounds[e + 1] - p.bounds[e] + FO_TOK - 1) / FO_TOK; }
+        __syncthreads();
+        for (int e = threadIdx.x; e <= E; e += blockDim.x) {
+            int run = 0;
+            for (int i = 0; i < e; i++) { run += cnt[i]; }
+            toff[e] = run;
+        }
+        __syncthreads();
+    }
+    const int64_t bands_e = p.rows_per_expert / BAND;
+    const int nbg = (int) ((bands_e + NB - 1) / NB);
+    const int n_items = toff[E] * nbg;
     const int g = lane >> 2, t = lane & 3;
-    const uint32_t xs_s = smem_u32(xs);
-    for (int item = blockIdx.x; item < p.n_experts * groups_e; item += gridDim.x) {
-        const int e = item / groups_e;
-        const int64_t band = (int64_t) (item - e * groups_e) * 8 + warp;   // inside the expert
-        const bool active = band < bands_e;
-        const int64_t gband = (int64_t) e * bands_e + band;
-        const int j0 = p.bounds[e], j1 = p.bounds[e + 1];
-        for (int jp = j0; jp < j1; jp += FO_TOK) {
-            const int ntok = min(FO_TOK, j1 - jp), ng = (ntok + 7) / 8;
-            __syncthreads(); // the previous pass is done with tok_* and xs
-            if (threadIdx.x < FO_TOK) {
-                tok_src[threadIdx.x] = threadIdx.x < ntok ? p.ids_src1[jp + threadIdx.x] : -1;
-                tok_dst[threadIdx.x] = threadIdx.x < ntok ? p.ids_dst[jp + threadIdx.x] : -1;
-            }
-            float d0[FO_TOK / 8][4], d1[GLU ? FO_TOK / 8 : 1][4];
+    const uint32_t xs_s = smem_u32(xb);
+    const uint32_t xrow = xs_s + (uint32_t) (((lane >> 4) * 8 + (lane & 7)) * FO_ROWB);
+    const uint32_t khalf = (lane >> 3) & 1, l7 = lane & 7;
+
+    auto item_at = [&](int it) {
+        FoItem r = {};
+        r.it = it;
+        r.valid = it < n_items;
+        if (!r.valid) { return r; }
+        const int tile = it / nbg;
+        int lo = 0, hi = E; // the largest e with toff[e] <= tile: its tiles are toff[e] .. toff[e + 1] - 1
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (toff[mid] <= tile) { lo = mid; } else { hi = mid; }
+        }
+        r.e = lo;
+        r.jb = __ldg(p.bounds + lo) + (tile - toff[lo]) * FO_TOK;
+        r.ntok = min(FO_TOK, __ldg(p.bounds + lo + 1) - r.jb);
+        r.band = (int64_t) (it - tile * nbg) * NB + (warp & (NB - 1));
+        r.live = r.band < bands_e;
+        return r;
+    };
+    // a thread copies one 16-byte piece of every 8th row: the row ids are all loaded before the first copy is issued
+    auto stage = [&](const FoItem & im, int slab, int b) { // missing tokens of the last pair of groups: zero fill
+        const int rows = ((im.ntok + 15) >> 4) << 4, row0 = threadIdx.x >> 6, piece = threadIdx.x & 63;
+        int32_t tok[FO_TOK / 8];
 #pragma unroll
-            for (int i = 0; i < FO_TOK / 8; i++) {
+        for (int i = 0; i < FO_TOK / 8; i++) {
+            const int row = row0 + 8 * i;
+            tok[i] = row < im.ntok ? __ldg(p.ids_src1 + im.jb + row) : -1;
+        }
+        const uint32_t to = xs_s + (uint32_t) (b * FO_BUF + row0 * FO_ROWB + ((piece ^ row0) << 4));
+        const bf16 * from = p.x + slab * CHUNK + piece * 8;
 #pragma unroll
-                for (int c = 0; c < 4; c++) { d0[i][c] = 0.f; if (GLU) { d1[i][c] = 0.f; } }
+        for (int i = 0; i < FO_TOK / 8; i++) {
+            if (row0 + 8 * i < rows) {
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(to + (uint32_t) (8 * i * FO_ROWB)),
+                             "l"(from + (tok[i] >= 0 ? (int64_t) tok[i] * p.x_row : 0)), "r"(tok[i] >= 0 ? 16u : 0u) : "memory");
             }
-            const int ng2 = (ng + 1) & ~1; // groups are multiplied in pairs: an odd last group gets a zero partner
-            for (int slab = 0; slab < p.C; slab++) {
-                __syncthreads(); // tok_* visible; every warp is done with the previous slab's activations
-                // 16-byte asynchronous copies, all in flight at once (missing tokens: zero fill), one wait for the lot
-                for (int i = threadIdx.x; i < ng2 * 8 * (CHUNK / 8); i += blockDim.x) {
-                    const int row = i / (CHUNK / 8), piece = i - row * (CHUNK / 8);
-                    const bool have = tok_src[row] >= 0;
-                    const bf16 * src = p.x + (have ? (int64_t) tok_src[row] * p.x_row + slab * CHUNK + piece * 8 : 0);
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(xs_s + (uint32_t) ((row * FO_XS + piece * 8) * 2)),
-                                 "l"(src), "r"(have ? 16u : 0u) : "memory");
+        }
+    };
+
+    FoItem cur = item_at(blockIdx.x);
+    if (cur.valid) { stage(cur, 0, 0); }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    int step = 0;
+    bool preloaded = false; // the next unit's stream start and first three words are in registers
+    const uint32_t * pfirst = nullptr;
+    uint32_t p0 = 0, p1 = 0, p2 = 0;
+    while (cur.valid) {
+        const FoItem nxt = item_at(cur.it + gridDim.x);
+        const int ng = (cur.ntok + 7) >> 3;
+        const int64_t unit0 = ((int64_t) cur.e * bands_e + cur.band) * C;
+        float acc[FO_NG][4];
+#pragma unroll
+        for (int i = 0; i < FO_NG; i++) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+        int b = 0;
+        for (int slab = 0; slab < C; slab++, step++) {
+            b = step & 1;
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncthreads(); // this step's rows have landed; every warp is done with the other buffer
+            if (slab + 1 < C) { stage(cur, slab + 1, b ^ 1); } else if (nxt.valid) { stage(nxt, 0, b ^ 1); }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            if (!cur.live) { continue; }
+            int64_t nu = -1; // this warp's next unit
+            if (slab + 1 < C) { nu = unit0 + slab + 1; } else if (nxt.valid && nxt.live) { nu = ((int64_t) nxt.e * bands_e + nxt.band) * C; }
+            uint32_t ub_n = 0, ub_n1 = 0, lr_n = 0;
+            if (nu >= 0) {
+                ub_n = __ldg(w.ubase + nu);
+                ub_n1 = nu + 1 < p.n_units ? __ldg(w.ubase + nu + 1) : ub_n;
+                lr_n = __ldg(w.lrel + nu * 32 + lane);
+                if (lane == 0) { bulk_prefetch_l2(w.plane + nu * (BAND * CHUNK), BAND * CHUNK); }
+            }
+            PairReader rd;
+            if (preloaded) { rd.open_loaded(pfirst, p0, p1, p2); } else { rd.open(w, unit0 + slab, lane); }
+            preloaded = false;
+            const uint8_t * pl = w.plane + (unit0 + slab) * (BAND * CHUNK) + 16 * lane;
+            const uint32_t xbuf = xrow + (uint32_t) (b * FO_BUF);
+            uint4 nx = ld_stream16(pl);
+#pragma unroll 1
+            for (int pp = 0; pp < 16; pp++) {
+                if (nu >= 0) {
+                    if (pp == 3 && lane == 0 && ub_n1 > ub_n) {
+                        const uint32_t first = ub_n & ~3u;
+                        bulk_prefetch_l2(w.stream + first, ((ub_n1 - first + 3u) & ~3u) * 4u);
+                    }
+                    if (pp == 9) {
+                        pfirst = w.stream + (ub_n + lr_n);
+                        p0 = __ldg(pfirst);
+                        p1 = __ldg(pfirst + 1);
+                        p2 = __ldg(pfirst + 2);
+                        preloaded = true;
+                    }
                 }
-                asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
-                __syncthreads();
-                if (!active) { continue; }
+                const uint4 cu = nx;
+                if (pp + 1 < 16) { nx = ld_stream16(pl + (pp + 1) * 512); }
+                uint32_t en[8], a[8];
+                rd.take8(lut, en);
+                assemble8(cu, en, a);
 #pragma unroll
-                for (int m = 0; m < (GLU ? 2 : 1); m++) {
-                    const PairView & w = m ? p.w1 : p.w0;
-                    const uint32_t * lut = m ? lut1 : lut0;
-                    DeepPairReader rd;
-                    rd.open(w, gband * p.C + slab, lane);
-                    const uint8_t * pl = w.plane + gband * BAND * K + (int64_t) slab * (16 * 512) + 16 * lane;
-                    uint4 nxt = ld_stream16(pl);
-                    for (int pp = 0; pp < 16; pp++) {
-                        const uint4 cur = nxt;
-                        if (pp + 1 < 16) { nxt = ld_stream16(pl + (pp + 1) * 512); }
-                        uint32_t en[8], a[8];
-                        rd.take8(lut, en);
-                        assemble8(cur, en, a);
+                for (int kk = 0; kk < 2; kk++) {
+                    // B fragments of two token groups per ldmatrix.x4: lane 8j + r addresses row r of 8x8 matrix j =
+                    // (token group i + (j >> 1), k half j & 1); rows are tokens, 16 bytes of k each
+                    const uint32_t xaddr = xbuf + ((((uint32_t) (4 * pp + 2 * kk) + khalf) ^ l7) << 4);
 #pragma unroll
-                        for (int kk = 0; kk < 2; kk++) {
-                            // B fragments of two token groups per ldmatrix.x4: lane 8j + r addresses row r of 8x8 matrix j =
-                            // (token group i + (j >> 1), k half j & 1); rows are tokens, 16 bytes of k each
-                            const uint32_t xaddr = xs_s + (uint32_t) ((((lane >> 4) * 8 + (lane & 7)) * FO_XS + (2 * pp + kk) * 16 + ((lane >> 3) & 1) * 8) * 2);
-#pragma unroll
-                            for (int i = 0; i < FO_TOK / 8; i += 2) {
-                                if (i < ng) {
-                                    uint32_t b0, b1, b2, b3;
-                                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-                                                 : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(xaddr + (uint32_t) (i * 8 * FO_XS * 2)));
-                                    float * d = m ? d1[GLU ? i : 0] : d0[i];
-                                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
-                                                 "{%8, %9}, {%0, %1, %2, %3};"
-                                                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                                                 : "r"(a[4 * kk]), "r"(a[4 * kk + 1]), "r"(a[4 * kk + 2]), "r"(a[4 * kk + 3]), "r"(b0), "r"(b1));
-                                    float * e2 = m ? d1[GLU ? i + 1 : 0] : d0[i + 1];
-                                    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
-                                                 "{%8, %9}, {%0, %1, %2, %3};"
-                                                 : "+f"(e2[0]), "+f"(e2[1]), "+f"(e2[2]), "+f"(e2[3])
-                                                 : "r"(a[4 * kk]), "r"(a[4 * kk + 1]), "r"(a[4 * kk + 2]), "r"(a[4 * kk + 3]), "r"(b2), "r"(b3));
-                                }
-                            }
+                    for (int i = 0; i < FO_NG; i += 2) {
+                        if (i < ng) {
+                            uint32_t b0, b1, b2, b3;
+                            asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                                         : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(xaddr + (uint32_t) (i * 8 * FO_ROWB)));
+                            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+                                         "{%8, %9}, {%0, %1, %2, %3};"
+                                         : "+f"(acc[i][0]), "+f"(acc[i][1]), "+f"(acc[i][2]), "+f"(acc[i][3])
+                                         : "r"(a[4 * kk]), "r"(a[4 * kk + 1]), "r"(a[4 * kk + 2]), "r"(a[4 * kk + 3]), "r"(b0), "r"(b1));
+                            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+                                         "{%8, %9}, {%0, %1, %2, %3};"
+                                         : "+f"(acc[i + 1][0]), "+f"(acc[i + 1][1]), "+f"(acc[i + 1][2]), "+f"(acc[i + 1][3])
+                                         : "r"(a[4 * kk]), "r"(a[4 * kk + 1]), "r"(a[4 * kk + 2]), "r"(a[4 * kk + 3]), "r"(b2), "r"(b3));
                         }
                     }
                 }
             }
-            if (!active) { continue; }
-            // d[i][0..1]: row g, tokens 8i + 2t, + 1; d[i][2..3]: row g + 8
+        }
+        // acc[i][0..1]: row g, tokens 8i + 2t, + 1; acc[i][2..3]: row g + 8
+        auto put = [&](int i, int c, float v) {
+            const int tok = 8 * i + 2 * t + (c & 1);
+            if (cur.live && tok < cur.ntok) {
+                const int64_t at = (int64_t) __ldg(p.ids_dst + cur.jb + tok) * p.dst_col + cur.band * BAND + g + 8 * (c >> 1);
+                if (p.dst_bf16) { ((bf16 *) p.dst)[at] = __float2bfloat16_rn(v); } else { ((float *) p.dst)[at] = v; }
+            }
+        };
+        if (GLU) {
+            constexpr int H = FO_NG / 2; // the gate warp finishes groups 0 .. H - 1, the up warp the rest
+            __syncthreads(); // every warp is done with this step's activations: the buffer now carries the swapped sums
+            float * red = (float *) (xb + b * FO_BUF);
 #pragma unroll
-            for (int i = 0; i < FO_TOK / 8; i++) {
+            for (int n = 0; n < H; n++) { // constant register indices on both sides of the branch
 #pragma unroll
                 for (int c = 0; c < 4; c++) {
-                    const int tok = 8 * i + 2 * t + (c & 1);
-                    if (i < ng && tok < ntok) {
-                        const float v = GLU ? silu_f(d0[i][c]) * d1[GLU ? i : 0][c] : d0[i][c];
-                        const int64_t at = (int64_t) tok_dst[tok] * p.dst_col + band * BAND + g + 8 * (c >> 1);
-                        if (p.dst_bf16) { ((bf16 *) p.dst)[at] = __float2bfloat16_rn(v); } else { ((float *) p.dst)[at] = v; }
-                    }
+                    float * at = red + ((warp * H + n) * 4 + c) * 32 + lane;
+                    if (upw) { *at = acc[n][c]; } else { *at = acc[H + n][c]; }
+                }
+            }
+            __syncthreads();
+            const float * theirs = red + (warp ^ NB) * H * 4 * 32 + lane;
+#pragma unroll
+            for (int n = 0; n < H; n++) {
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const float other = theirs[(n * 4 + c) * 32];
+                    if (upw) { put(H + n, c, silu_f(other) * acc[H + n][c]); } else { put(n, c, silu_f(acc[n][c]) * other); }
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < FO_NG; i++) {
+                if (i < ng) {
+#pragma unroll
+                    for (int c = 0; c < 4; c++) { put(i, c, acc[i][c]); }
                 }
             }
         }
+        cur = nxt;
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
 // The same product with the streams staged: persistent blocks of 8 warps, a warp walks bands and copies each slab's
@@ -546,9 +647,7 @@ void fo_init() {
     ATTR((k_fo_gemv<1, bf16>)); ATTR((k_fo_gemv<2, bf16>)); ATTR((k_fo_gemv<4, bf16>)); ATTR((k_fo_gemv<8, bf16>));
     ATTR(k_fo_gemv_mma);
     ATTR(k_fo_gemv_staged);
-    // these two also have a little static shared memory: ask for what they use, not for the whole opt-in limit
-    cuda_ok(cudaFuncSetAttribute(k_fo_mm_ids<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * HP_MAX_PAIRS + FO_TOK * FO_XS * 2), "k_fo_mm_ids");
-    cuda_ok(cudaFuncSetAttribute(k_fo_mm_ids<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * HP_MAX_PAIRS + FO_TOK * FO_XS * 2), "k_fo_mm_ids glu");
+    ATTR(k_fo_mm_ids<false>); ATTR(k_fo_mm_ids<true>);
 #undef ATTR
 }
 
@@ -556,6 +655,10 @@ void fo_init() {
 bool fo_supported(const bf16n_weight & w) {
     return w.fo && w.format == FMT_HUFPAIR && w.R == BAND && !w.cm && w.K % CHUNK == 0 && w.rows % BAND == 0 &&
            4 * HP_MAX_PAIRS + 8 * w.K * 4 <= device_info().smem_optin;
+}
+
+static size_t fo_mm_shm(bool glu, int n_experts) {
+    return (size_t) (glu ? 2 : 1) * 4 * HP_MAX_PAIRS + 2 * (size_t) FO_BUF + ((size_t) n_experts + 1) * 4;
 }
 
 bool fo_mm_ids_supported(const bf16n_weight & w, const bf16n_weight * up) {
@@ -576,10 +679,11 @@ void fo_mm_ids(const bf16n_weight & w, const bf16n_weight * up, const void * x_b
     a.rows_per_expert = w.rows / n_experts;
     require(((uintptr_t) x_bf16 % 16) == 0 && (x_row * 2) % 16 == 0, "batched activations must be 16-byte aligned rows");
     require(a.rows_per_expert % BAND == 0, "rows per expert must be whole 16-row bands");
-    const int64_t items = (int64_t) n_experts * ((a.rows_per_expert / BAND + 7) / 8);
-    const unsigned grid = (unsigned) std::min<int64_t>(items, (int64_t) device_info().sms * 2);
-    const size_t shm = (up ? 2 : 1) * 4 * HP_MAX_PAIRS + (size_t) FO_TOK * FO_XS * 2;
-    if (up) { k_fo_mm_ids<true><<<grid, 256, shm, st>>>(a); } else { k_fo_mm_ids<false><<<grid, 256, shm, st>>>(a); }
+    a.n_units = w.rows / BAND * a.C;
+    const size_t shm = fo_mm_shm(up != nullptr, n_experts);
+    require(shm <= (size_t) device_info().smem_optin, "too many experts for the fragment-order batched kernel's shared memory");
+    const unsigned grid = (unsigned) device_info().sms; // persistent: the items are counted on the device from the bounds
+    if (up) { k_fo_mm_ids<true><<<grid, FO_WARPS * 32, shm, st>>>(a); } else { k_fo_mm_ids<false><<<grid, FO_WARPS * 32, shm, st>>>(a); }
     check_launch();
 }
 
