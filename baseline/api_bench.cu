@@ -183,7 +183,7 @@ static void frag_order(int reps) {
         }
         CK(cudaFree((void *) d.w.plane)); CK(cudaFree((void *) d.w.aux));
     }
-    const int E = 256, k = 8, H = 2048, N = 512, T = 2048;
+    const int E = 256, k = 8, H = 2048, N = 512;
     const Dev gate = make((int64_t) E * N, H, bf16n::FMT_HUFPAIR, 16, false, 11, true);
     const Dev up = make((int64_t) E * N, H, bf16n::FMT_HUFPAIR, 16, false, 12, true);
     const Dev down = make((int64_t) E * H, N, bf16n::FMT_HUFPAIR, 16, false, 13, true);
@@ -191,32 +191,38 @@ static void frag_order(int reps) {
         printf("{\"impl\": \"%s\", \"workload\": \"MoE prefill, fragment order\", \"unavailable\": \"no batched kernel\"}\n", IMPL_NAME);
         return;
     }
-    std::mt19937_64 g(200 + T);
-    std::vector<int32_t> ids((size_t) T * k);
-    for (int t = 0; t < T; t++) {
-        std::vector<int> perm(E);
-        for (int i = 0; i < E; i++) { perm[i] = i; }
-        std::shuffle(perm.begin(), perm.end(), g);
-        for (int s = 0; s < k; s++) { ids[(size_t) t * k + s] = perm[s]; }
+    for (int T : {2048, 8192}) {
+        std::mt19937_64 g(200 + T);
+        std::vector<int32_t> ids((size_t) T * k);
+        for (int t = 0; t < T; t++) {
+            std::vector<int> perm(E);
+            for (int i = 0; i < E; i++) { perm[i] = i; }
+            std::shuffle(perm.begin(), perm.end(), g);
+            for (int s = 0; s < k; s++) { ids[(size_t) t * k + s] = perm[s]; }
+        }
+        const int32_t * d_ids = dev_copy(ids);
+        const std::vector<float> wts((size_t) T * k, 1.f / k);
+        const float * d_w = dev_copy(wts);
+        const uint16_t * x = dev_copy(normal_bf16((size_t) T * H, 1.f, 30));
+        int32_t * src1, * dst, * bounds;
+        CK(cudaMalloc(&src1, (size_t) T * k * 4)); CK(cudaMalloc(&dst, (size_t) T * k * 4)); CK(cudaMalloc(&bounds, (E + 1) * 4));
+        uint16_t * act; float * ys, * y;
+        CK(cudaMalloc(&act, (size_t) T * k * N * 2)); CK(cudaMalloc(&ys, (size_t) T * k * H * 4)); CK(cudaMalloc(&y, (size_t) T * H * 4));
+        auto step = [&](int) {
+            bf16n::mm_ids_route(d_ids, false, k, src1, dst, bounds, E, T, k, 1, 1, 0);
+            bf16n::mm_ids(gate.w, &up.w, x, H, src1, dst, bounds, act, true, N, E, T, k, 0);
+            bf16n::mm_ids_route(d_ids, false, k, src1, dst, bounds, E, T, k, k, k, 0);
+            bf16n::mm_ids(down.w, nullptr, act, N, src1, dst, bounds, ys, false, H, E, T, k, 0);
+            bf16n::moe_combine(ys, d_w, false, y, false, T, k, H, 0);
+        };
+        const double us = median_us(std::max(5, reps / 4), step);
+        printf("{\"impl\": \"%s\", \"workload\": \"MoE prefill layer, %d tokens, fragment-order experts\", \"us\": %.1f, \"TFLOPs\": %.1f, "
+               "\"sum_abs_y\": %.6e}\n", IMPL_NAME, T, us, 6.0 * N * H * k * T / us / 1e6, checksum(y, (size_t) T * H, "fo_moe_prefill_" + std::to_string(T)));
+        for (const void * q : {(const void *) d_ids, (const void *) d_w, (const void *) x, (const void *) src1, (const void *) dst, (const void *) bounds,
+                               (const void *) act, (const void *) ys, (const void *) y}) {
+            CK(cudaFree((void *) q));
+        }
     }
-    const int32_t * d_ids = dev_copy(ids);
-    const std::vector<float> wts((size_t) T * k, 1.f / k);
-    const float * d_w = dev_copy(wts);
-    const uint16_t * x = dev_copy(normal_bf16((size_t) T * H, 1.f, 30));
-    int32_t * src1, * dst, * bounds;
-    CK(cudaMalloc(&src1, (size_t) T * k * 4)); CK(cudaMalloc(&dst, (size_t) T * k * 4)); CK(cudaMalloc(&bounds, (E + 1) * 4));
-    uint16_t * act; float * ys, * y;
-    CK(cudaMalloc(&act, (size_t) T * k * N * 2)); CK(cudaMalloc(&ys, (size_t) T * k * H * 4)); CK(cudaMalloc(&y, (size_t) T * H * 4));
-    auto step = [&](int) {
-        bf16n::mm_ids_route(d_ids, false, k, src1, dst, bounds, E, T, k, 1, 1, 0);
-        bf16n::mm_ids(gate.w, &up.w, x, H, src1, dst, bounds, act, true, N, E, T, k, 0);
-        bf16n::mm_ids_route(d_ids, false, k, src1, dst, bounds, E, T, k, k, k, 0);
-        bf16n::mm_ids(down.w, nullptr, act, N, src1, dst, bounds, ys, false, H, E, T, k, 0);
-        bf16n::moe_combine(ys, d_w, false, y, false, T, k, H, 0);
-    };
-    const double us = median_us(std::max(5, reps / 4), step);
-    printf("{\"impl\": \"%s\", \"workload\": \"MoE prefill layer, %d tokens, fragment-order experts\", \"us\": %.1f, \"TFLOPs\": %.1f, "
-           "\"sum_abs_y\": %.6e}\n", IMPL_NAME, T, us, 6.0 * N * H * k * T / us / 1e6, checksum(y, (size_t) T * H, "fo_moe_prefill_2048"));
 }
 
 // ---- config 3: MoE decode layer through the operator chain of the reference's Python layer

@@ -2,7 +2,9 @@
 baseline/api_bench.cu is built once against include/bf16n/*.h + libbf16n_b200.so and once against the reference's headers
 and sources recompiled for sm_100a (baseline/Makefile). The vocabulary projection, the small NIBBLE GEMVs and the routed-expert decode chain must
 give the reference's FP32 results bit for bit (same summation order); the batched prefill layer, whose tensor-core
-accumulation order differs and whose intermediate is BF16 in both, must agree to 2^-9 of the largest output.
+accumulation order differs and whose intermediate is BF16 in both, must agree to 2^-9 of the largest output. The
+fragment-order workloads (projection at 1 and 8 tokens, prefill layer at 2048 and 8192 tokens) run on mma.m16n8k16 in
+both libraries with the same k order and must be bit-equal too.
 Skipped when the reference build of the driver is not present (it is not part of the repository)."""
 import os
 import subprocess
@@ -32,3 +34,17 @@ def test_outputs_match_the_reference_kernels(tmp_path):
             assert np.abs(a.astype(np.float64) - b).max() <= 2.0 ** -9 * np.abs(b).max()
         else:
             assert np.array_equal(a.view(np.uint32), b.view(np.uint32)), n
+
+
+@pytest.mark.skipif(not (os.path.exists(OURS) and os.path.exists(REF)), reason="baseline/_ref/api_bench_{ours,ref} not built")
+def test_fragment_order_outputs_match_the_reference_kernels(tmp_path):
+    for exe, tag in ((REF, "ref_"), (OURS, "ours_")):
+        env = dict(os.environ, API_BENCH_DUMP=str(tmp_path / tag))
+        subprocess.run([exe, "frag_order", "3"], check=True, env=env, stdout=subprocess.DEVNULL, timeout=600)
+    names = sorted(f[len("ref_"):] for f in os.listdir(tmp_path) if f.startswith("ref_"))
+    assert names == ["fo_lm_head_1.f32", "fo_lm_head_8.f32", "fo_moe_prefill_2048.f32", "fo_moe_prefill_8192.f32"]
+    for n in names:
+        a = np.fromfile(tmp_path / ("ours_" + n), np.float32)
+        b = np.fromfile(tmp_path / ("ref_" + n), np.float32)
+        assert a.shape == b.shape and np.isfinite(a).all()
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32)), n
