@@ -188,7 +188,8 @@ __global__ void __launch_bounds__(256) k_fo_gemv(const PairView w, int C, Cols p
 // Shared memory holds the 8 activation rows as BF16, each padded by 8 elements so that the B-fragment reads of a warp
 // fall into 32 different banks; columns beyond ncols are zero.
 constexpr int XPAD = 8;
-__global__ void __launch_bounds__(256) k_fo_gemv_mma(const PairView w, int C, Cols p, int ncols) {
+constexpr int FO_BARS = 512; // room for two mbarriers per warp of the staged kernel (up to 32 warps)
+__global__ void __launch_bounds__(512) k_fo_gemv_mma(const PairView w, int C, Cols p, int ncols, int64_t n_units) {
     extern __shared__ __align__(16) unsigned char smem[];
     uint32_t * lut = (uint32_t *) smem;
     bf16 * xs = (bf16 *) (smem + 4 * HP_MAX_PAIRS);
@@ -203,16 +204,45 @@ __global__ void __launch_bounds__(256) k_fo_gemv_mma(const PairView w, int C, Co
     __syncthreads();
     const int g = lane >> 2, t = lane & 3;
     const bf16 * xl = xs + g * XS + 2 * t; // B fragment: token g, k = 2t, 2t+1 (and + 8) of every tile
-    const int64_t bands = p.nrows / BAND;
-    for (int64_t b = (int64_t) blockIdx.x * nwarp + warp; b < bands; b += (int64_t) gridDim.x * nwarp) {
+    const int64_t bands = p.nrows / BAND, stride = (int64_t) gridDim.x * nwarp;
+    // while a unit is decoded, the next unit's stream start and first three words are loaded and its plane and stream
+    // bytes are pulled into L2
+    bool preloaded = false;
+    const uint32_t * pfirst = nullptr;
+    uint32_t p0 = 0, p1 = 0, p2 = 0;
+    for (int64_t b = (int64_t) blockIdx.x * nwarp + warp; b < bands; b += stride) {
         const int64_t gband = p.row0 / BAND + b;
         float d[4] = {0.f, 0.f, 0.f, 0.f};
         for (int slab = 0; slab < C; slab++) {
+            const int64_t unit = gband * C + slab;
+            const int64_t nu = slab + 1 < C ? unit + 1 : b + stride < bands ? (gband + stride) * C : -1;
+            uint32_t ub_n = 0, ub_n1 = 0, lr_n = 0;
+            if (nu >= 0) {
+                ub_n = __ldg(w.ubase + nu);
+                ub_n1 = nu + 1 < n_units ? __ldg(w.ubase + nu + 1) : ub_n;
+                lr_n = __ldg(w.lrel + nu * 32 + lane);
+                if (lane == 0) { bulk_prefetch_l2(w.plane + nu * (BAND * CHUNK), BAND * CHUNK); }
+            }
             PairReader rd;
-            rd.open(w, gband * C + slab, lane);
-            const uint8_t * pl = w.plane + gband * BAND * (int64_t) K + (int64_t) slab * (16 * 512) + 16 * lane;
+            if (preloaded) { rd.open_loaded(pfirst, p0, p1, p2); } else { rd.open(w, unit, lane); }
+            preloaded = false;
+            const uint8_t * pl = w.plane + unit * (BAND * CHUNK) + 16 * lane;
             uint4 nxt = ld_stream16(pl);
+#pragma unroll 1
             for (int pp = 0; pp < 16; pp++) {
+                if (nu >= 0) {
+                    if (pp == 3 && lane == 0 && ub_n1 > ub_n) {
+                        const uint32_t first = ub_n & ~3u;
+                        bulk_prefetch_l2(w.stream + first, ((ub_n1 - first + 3u) & ~3u) * 4u);
+                    }
+                    if (pp == 9) {
+                        pfirst = w.stream + (ub_n + lr_n);
+                        p0 = __ldg(pfirst);
+                        p1 = __ldg(pfirst + 1);
+                        p2 = __ldg(pfirst + 2);
+                        preloaded = true;
+                    }
+                }
                 const uint4 cur = nxt;
                 if (pp + 1 < 16) { nxt = ld_stream16(pl + (pp + 1) * 512); }
                 uint32_t e[8], a[8];
@@ -468,21 +498,21 @@ __global__ void __launch_bounds__(FO_WARPS * 32, 1) k_fo_mm_ids(const FoBatch p)
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
-// The same product with the streams staged: persistent blocks of 8 warps, a warp walks bands and copies each slab's
+// The same product with the streams staged: one persistent block per SM of up to 32 warps, a warp walks bands and copies each slab's
 // stream block into its own shared-memory buffer with one bulk async copy (two buffers in turn, so the next slab's copy
 // runs under the current slab's decoding; bounded wait, as in gemv_staged.cu), reads it with the staged reader and
 // prefetches the plane bytes one tile pair ahead. Serves 1..8 dense BF16 columns. A slab whose streams do not fit the
 // buffer (more than 3 bits per weight) is read straight from global memory.
 constexpr uint32_t FO_CAP = (BAND * CHUNK * 3 / 8 + 64 + 15) & ~15u;
 
-__global__ void __launch_bounds__(256) k_fo_gemv_staged(const PairView w, const AuxHeader * hdr, int C, Cols p, int ncols, const Opaque k) {
+__global__ void __launch_bounds__(1024) k_fo_gemv_staged(const PairView w, const AuxHeader * hdr, int C, Cols p, int ncols, const Opaque k) {
     extern __shared__ __align__(128) unsigned char smem[];
     uint32_t * lut = (uint32_t *) smem;
     uint64_t * bars = (uint64_t *) (smem + 4 * HP_MAX_PAIRS);            // two per warp
     const int K = C * CHUNK, XS = K + XPAD;
-    bf16 * xs = (bf16 *) (smem + 4 * HP_MAX_PAIRS + 128);
+    bf16 * xs = (bf16 *) (smem + 4 * HP_MAX_PAIRS + FO_BARS);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
-    unsigned char * buf = smem + 4 * HP_MAX_PAIRS + 128 + (size_t) 8 * XS * 2 + (size_t) warp * 2 * FO_CAP;
+    unsigned char * buf = smem + 4 * HP_MAX_PAIRS + FO_BARS + (size_t) 8 * XS * 2 + (size_t) warp * 2 * FO_CAP;
     stage_lut(lut, w.lut);
     if (lane == 0) { mbar_init(smem_u32(bars + 2 * warp), 1); mbar_init(smem_u32(bars + 2 * warp + 1), 1); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -529,6 +559,11 @@ __global__ void __launch_bounds__(256) k_fo_gemv_staged(const PairView w, const 
                 stage(nxt, (slab + 1) & 1);
             }
             const uint8_t * pl = w.plane + gband * BAND * (int64_t) K + (int64_t) slab * (16 * 512) + 16 * lane;
+            if (lane == 0) { // the next unit's plane bytes into L2 (the next slab, or the first slab of this warp's next band)
+                const int64_t nb = b + (int64_t) gridDim.x * nwarp;
+                if (slab + 1 < C) { bulk_prefetch_l2(pl + 16 * 512, 16 * 512); }
+                else if (nb < bands) { bulk_prefetch_l2(w.plane + (p.row0 / BAND + nb) * BAND * (int64_t) K, 16 * 512); }
+            }
             auto body = [&](auto & rd, uint32_t lut_arg) {
                 uint4 nx = ld_stream16(pl);
                 for (int pp = 0; pp < 16; pp++) {
@@ -603,22 +638,34 @@ void fo_gemv_t(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st
         const int C = (int) (w.K / CHUNK);
         const int64_t bands = p.nrows / BAND, sms = device_info().sms;
         const size_t x_bytes = (size_t) 8 * (w.K + XPAD) * 2;
-        const size_t shm_staged = 4 * HP_MAX_PAIRS + 128 + x_bytes + (size_t) 8 * 2 * FO_CAP;
-        const bool big = bands >= sms * 16 && (uintptr_t) p.x % 16 == 0 && p.x_tok % 16 == 0;
+        // One persistent block per SM with as many warps as the shared memory holds stream buffers for (28 with K = 2048;
+        // the decode chains need the occupancy), then the fewest warps that still finish in the same number of bands
+        // per warp, so that no warp slows the others down for nothing.
+        static const int forced_warps = getenv("BF16N_FO_STAGED_WARPS") ? atoi(getenv("BF16N_FO_STAGED_WARPS")) : 0;
+        const size_t shm_fixed = 4 * HP_MAX_PAIRS + FO_BARS + x_bytes;
+        const size_t optin = (size_t) device_info().smem_optin;
+        int staged_warps = optin > shm_fixed ? (int) std::min<size_t>(32, (optin - shm_fixed) / (2 * FO_CAP)) : 0;
+        if (staged_warps > 0) {
+            const int64_t rounds = (bands + sms * staged_warps - 1) / (sms * staged_warps);
+            staged_warps = (int) ((bands + sms * rounds - 1) / (sms * rounds));
+        }
+        if (forced_warps > 0) { staged_warps = std::min(32, forced_warps); }
+        const size_t shm_staged = shm_fixed + (size_t) staged_warps * 2 * FO_CAP;
+        const bool big = bands >= sms * 16 && (uintptr_t) p.x % 16 == 0 && p.x_tok % 16 == 0 && staged_warps >= 8 &&
+                         shm_staged <= optin;
         for (int c0 = 0; c0 < a.ncols; c0 += 8) {
             Cols q = p;
             q.x += c0 * p.x_tok;
             q.y += c0 * p.y_tok;
             const int nc = std::min(8, a.ncols - c0);
             if (big) {
-                const int per_sm = std::max(1, (int) (device_info().smem_optin / (shm_staged + 1024)));
                 const Opaque k = {1u, 4u, ~0u, 32u};
-                launch_chained(k_fo_gemv_staged, dim3((unsigned) (sms * per_sm)), dim3(256), shm_staged, st, pair_view(w),
+                launch_chained(k_fo_gemv_staged, dim3((unsigned) sms), dim3(staged_warps * 32), shm_staged, st, pair_view(w),
                                (const AuxHeader *) w.aux, C, q, nc, k);
             } else {
                 const int warps = bands >= sms * 32 ? 8 : bands >= sms * 8 ? 4 : 2;
                 const dim3 grid((unsigned) std::min<int64_t>((bands + warps - 1) / warps, sms * 8));
-                launch_chained(k_fo_gemv_mma, grid, dim3(warps * 32), 4 * HP_MAX_PAIRS + x_bytes, st, pair_view(w), C, q, nc);
+                launch_chained(k_fo_gemv_mma, grid, dim3(warps * 32), 4 * HP_MAX_PAIRS + x_bytes, st, pair_view(w), C, q, nc, w.rows / BAND * C);
             }
         }
         return;
