@@ -227,11 +227,11 @@ static void frag_order(int reps) {
 
 // ---- config 3: MoE decode layer through the operator chain of the reference's Python layer
 // (mmv gate, mmv up with expert ids, swiglu, mmv down, moe_combine): 256 experts, top-8, T tokens
-static void moe_decode(int reps) {
+static void moe_decode(int reps, bool fo = false) {
     const int E = 256, k = 8, H = 2048, N = 512;
-    const Dev gate = make((int64_t) E * N, H, bf16n::FMT_HUFPAIR, 8, true, 11);
-    const Dev up = make((int64_t) E * N, H, bf16n::FMT_HUFPAIR, 8, true, 12);
-    const Dev down = make((int64_t) E * H, N, bf16n::FMT_HUFPAIR, 16, false, 13);
+    const Dev gate = make((int64_t) E * N, H, bf16n::FMT_HUFPAIR, fo ? 16 : 8, !fo, 11, fo);
+    const Dev up = make((int64_t) E * N, H, bf16n::FMT_HUFPAIR, fo ? 16 : 8, !fo, 12, fo);
+    const Dev down = make((int64_t) E * H, N, bf16n::FMT_HUFPAIR, 16, false, 13, fo);
     for (int T : {1, 2, 4}) {
         const int rot = 16; // routings rotated so that consecutive steps read different experts (weights exceed L2)
         std::mt19937_64 g(100 + T);
@@ -267,8 +267,9 @@ static void moe_decode(int reps) {
             bf16n::moe_combine(ys, d_w, false, y, false, T, k, H, 0);
         };
         const double us = median_us(reps, step);
-        printf("{\"impl\": \"%s\", \"workload\": \"MoE decode, routed experts only, %d token(s), operator chain of 5 launches\", \"us\": %.2f, "
-               "\"sum_abs_y\": %.6e}\n", IMPL_NAME, T, us, checksum(y, (size_t) T * H, "moe_decode_" + std::to_string(T)));
+        printf("{\"impl\": \"%s\", \"workload\": \"MoE decode, routed experts only%s, %d token(s), operator chain of 5 launches\", \"us\": %.2f, "
+               "\"sum_abs_y\": %.6e}\n", IMPL_NAME, fo ? ", fragment-order experts" : "", T, us,
+               checksum(y, (size_t) T * H, std::string(fo ? "fo_" : "") + "moe_decode_" + std::to_string(T)));
     }
 }
 
@@ -325,5 +326,6 @@ int main(int argc, char ** argv) {
     if (what == "moe_prefill" || what == "all") { moe_prefill(reps); }
     if (what == "small" || what == "all") { small(reps); }
     if (what == "frag_order" || what == "more") { frag_order(reps); }
+    if (what == "frag_order_decode" || what == "more") { moe_decode(reps, true); }
     return 0;
 }
