@@ -182,6 +182,90 @@ __global__ void __launch_bounds__(256) k_fo_gemv(const PairView w, int C, Cols p
     }
 }
 
+// One routed column per blockIdx.y for matrices of few bands (the routed experts of a decode step): the K / 512 slabs
+// of a band go to as many warps, so that the dependent decode chain a warp walks is one unit long instead of K / 512;
+// a block holds `nb` bands. The slabs' partial sums meet in shared memory and are added in slab order. A warp here runs
+// nearly alone on its SM and its unit comes cold from HBM, so everything it will read is requested up front: the unit's
+// plane and stream bytes into L2, the stream start and its first three words into registers (all of that under the
+// staging of the table and the activations), and the plane is read four tile pairs ahead.
+template <typename TX>
+__global__ void __launch_bounds__(256) k_fo_gemv_split(const PairView w, int C, Cols p, int nb, int64_t n_units) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    uint32_t * lut = (uint32_t *) smem;
+    const int64_t K = (int64_t) C * CHUNK;
+    float * xs = (float *) (smem + 4 * HP_MAX_PAIRS);
+    float * part = xs + K; // [band of the block][slab][16 rows]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int j = warp / C, slab = warp - j * C;
+    grid_dependency_wait(); // activations and expert ids may come from the kernel before this one
+    const TX * xg; OutVec out; int64_t rbase;
+    column<TX>(p, blockIdx.y, xg, out, rbase);
+    const int64_t bands = p.nrows / BAND;
+    auto request = [&](int64_t unit, const uint32_t *& first, uint32_t & p0, uint32_t & p1, uint32_t & p2) {
+        if (lane == 0) { bulk_prefetch_l2(w.plane + unit * (BAND * CHUNK), BAND * CHUNK); }
+        const uint32_t ub = __ldg(w.ubase + unit), lr = __ldg(w.lrel + unit * 32 + lane);
+        if (lane == 0 && unit + 1 < n_units) {
+            const uint32_t ub1 = __ldg(w.ubase + unit + 1), from = ub & ~3u;
+            if (ub1 > ub) { bulk_prefetch_l2(w.stream + from, ((ub1 - from + 3u) & ~3u) * 4u); }
+        }
+        first = w.stream + (ub + lr);
+        p0 = __ldg(first); p1 = __ldg(first + 1); p2 = __ldg(first + 2);
+    };
+    const uint32_t * first = nullptr;
+    uint32_t p0 = 0, p1 = 0, p2 = 0;
+    if ((int64_t) blockIdx.x * nb + j < bands) { request((rbase / BAND + (int64_t) blockIdx.x * nb + j) * C + slab, first, p0, p1, p2); }
+    stage_lut(lut, w.lut);
+    for (int i = threadIdx.x; i < K; i += blockDim.x) { xs[i] = to_f32(xg[i]); }
+    __syncthreads();
+    const int cq = 2 * (lane & 3);
+    for (int64_t b0 = (int64_t) blockIdx.x * nb; b0 < bands; b0 += (int64_t) gridDim.x * nb) {
+        const int64_t b = b0 + j;
+        const bool active = b < bands;
+        float acc[2] = {0.f, 0.f};
+        if (active) {
+            const int64_t unit = (rbase / BAND + b) * C + slab;
+            if (b0 != (int64_t) blockIdx.x * nb) { request(unit, first, p0, p1, p2); }
+            PairReader rd;
+            rd.open_loaded(first, p0, p1, p2);
+            const uint8_t * pl = w.plane + unit * (BAND * CHUNK) + 16 * lane;
+            uint4 ring[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) { ring[i] = ld_stream16(pl + i * 512); }
+            for (int pp4 = 0; pp4 < 16; pp4 += 4) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int pp = pp4 + i;
+                    const uint4 cur = ring[i];
+                    if (pp + 4 < 16) { ring[i] = ld_stream16(pl + (pp + 4) * 512); }
+                    uint32_t e[8], wv[8];
+                    rd.take8(lut, e);
+                    assemble8(cur, e, wv);
+#pragma unroll
+                    for (int q8 = 0; q8 < 8; q8++) {
+                        const int q = q8 & 3;
+                        const float2 xv = *(const float2 *) (xs + (slab * 32 + 2 * pp + (q8 >> 2)) * 16 + cq + 8 * (q >> 1));
+                        acc[q & 1] = fmaf(bf16hi_f32(wv[q8]), xv.y, fmaf(bf16lo_f32(wv[q8]), xv.x, acc[q & 1]));
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            float v = acc[h];
+            v += __shfl_xor_sync(FULL, v, 1);
+            v += __shfl_xor_sync(FULL, v, 2);
+            if ((lane & 3) == 0) { part[(j * C + slab) * 16 + (lane >> 2) + 8 * h] = v; }
+        }
+        __syncthreads();
+        if (slab == 0 && active && lane < 16) {
+            float v = part[j * C * 16 + lane];
+            for (int s2 = 1; s2 < C; s2++) { v += part[(j * C + s2) * 16 + lane]; }
+            out.put(b * BAND + lane, v);
+        }
+        __syncthreads();
+    }
+}
+
 // Up to 8 dense BF16 columns on the tensor cores: a lane's four symbols of a tile are exactly its A registers of
 // mma.m16n8k16 (that is what the layout is for), the activations are the B operand (k x 8 tokens) and a band's
 // D[16 rows, 8 tokens] accumulates in four registers per lane, so eight tokens cost one decode and one MMA per tile.
@@ -629,7 +713,16 @@ template <typename TX>
 void fo_gemv_t(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st) {
     Cols p = make_cols(a);
     if (a.ids) {
-        launch_fo<1, TX>(w, p, a.ncols, st);
+        const int C = (int) (w.K / CHUNK);
+        const int64_t bands = p.nrows / BAND;
+        if (C <= 8 && bands * a.ncols < (int64_t) device_info().sms * 64) { // few bands: a band's slabs side by side
+            const int nb = std::max(1, 8 / C);
+            const size_t shm = 4 * HP_MAX_PAIRS + (size_t) w.K * 4 + (size_t) nb * C * 16 * 4;
+            launch_chained(k_fo_gemv_split<TX>, dim3((unsigned) ((bands + nb - 1) / nb), (unsigned) a.ncols), dim3(nb * C * 32), shm, st,
+                           pair_view(w), C, p, nb, w.rows / BAND * C);
+        } else {
+            launch_fo<1, TX>(w, p, a.ncols, st);
+        }
         return;
     }
     if (a.x_bf16 && (a.ncols >= 2 || p.nrows / BAND >= (int64_t) device_info().sms * 16)) {
@@ -693,6 +786,7 @@ void fo_init() {
     ATTR((k_fo_gemv<1, float>)); ATTR((k_fo_gemv<2, float>)); ATTR((k_fo_gemv<4, float>)); ATTR((k_fo_gemv<8, float>));
     ATTR((k_fo_gemv<1, bf16>)); ATTR((k_fo_gemv<2, bf16>)); ATTR((k_fo_gemv<4, bf16>)); ATTR((k_fo_gemv<8, bf16>));
     ATTR(k_fo_gemv_mma);
+    ATTR(k_fo_gemv_split<float>); ATTR(k_fo_gemv_split<bf16>);
     ATTR(k_fo_gemv_staged);
     ATTR(k_fo_mm_ids<false>); ATTR(k_fo_mm_ids<true>);
 #undef ATTR
