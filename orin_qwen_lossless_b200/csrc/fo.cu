@@ -184,50 +184,57 @@ __global__ void __launch_bounds__(256) k_fo_gemv(const PairView w, int C, Cols p
 
 // One routed column per blockIdx.y for matrices of few bands (the routed experts of a decode step): the K / 512 slabs
 // of a band go to as many warps, so that the dependent decode chain a warp walks is one unit long instead of K / 512;
-// a block holds `nb` bands. The slabs' partial sums meet in shared memory and are added in slab order. A warp here runs
-// nearly alone on its SM and its unit comes cold from HBM, so everything it will read is requested up front: the unit's
-// plane and stream bytes into L2, the stream start and its first three words into registers (all of that under the
-// staging of the table and the activations), and the plane is read four tile pairs ahead.
+// a block holds `nb` bands, a warp decodes exactly one unit. The slabs' partial sums meet in shared memory and are added
+// in slab order. A warp here runs nearly alone on its SM and its unit comes cold from HBM; read lane by lane, every
+// lane's stream line would stall the warp for a trip to L2 at a different moment. So the unit's stream block is copied
+// into the warp's shared-memory buffer with one bulk copy and its plane pulled into L2, both started before the table
+// and the activations are staged, and the plane is read four tile pairs ahead. A unit whose streams do not fit the
+// buffer (more than 3 bits per weight) is read from global memory.
+constexpr uint32_t FO_SPLIT_CAP = (BAND * CHUNK * 3 / 8 + 64 + 15) & ~15u;
 template <typename TX>
-__global__ void __launch_bounds__(256) k_fo_gemv_split(const PairView w, int C, Cols p, int nb, int64_t n_units) {
-    extern __shared__ __align__(16) unsigned char smem[];
+__global__ void __launch_bounds__(256) k_fo_gemv_split(const PairView w, const AuxHeader * hdr, int C, Cols p, int nb, const Opaque k) {
+    extern __shared__ __align__(128) unsigned char smem[];
     uint32_t * lut = (uint32_t *) smem;
+    uint64_t * bars = (uint64_t *) (smem + 4 * HP_MAX_PAIRS); // one per warp
     const int64_t K = (int64_t) C * CHUNK;
-    float * xs = (float *) (smem + 4 * HP_MAX_PAIRS);
+    float * xs = (float *) (smem + 4 * HP_MAX_PAIRS + 128);
     float * part = xs + K; // [band of the block][slab][16 rows]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    unsigned char * buf = (unsigned char *) (part + nb * C * 16) + (size_t) warp * FO_SPLIT_CAP;
     const int j = warp / C, slab = warp - j * C;
+    const uint32_t bar = smem_u32(bars + warp);
+    if (lane == 0) { mbar_init(bar, 1); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncwarp();
     grid_dependency_wait(); // activations and expert ids may come from the kernel before this one
     const TX * xg; OutVec out; int64_t rbase;
     column<TX>(p, blockIdx.y, xg, out, rbase);
-    const int64_t bands = p.nrows / BAND;
-    auto request = [&](int64_t unit, const uint32_t *& first, uint32_t & p0, uint32_t & p1, uint32_t & p2) {
-        if (lane == 0) { bulk_prefetch_l2(w.plane + unit * (BAND * CHUNK), BAND * CHUNK); }
-        const uint32_t ub = __ldg(w.ubase + unit), lr = __ldg(w.lrel + unit * 32 + lane);
-        if (lane == 0 && unit + 1 < n_units) {
-            const uint32_t ub1 = __ldg(w.ubase + unit + 1), from = ub & ~3u;
-            if (ub1 > ub) { bulk_prefetch_l2(w.stream + from, ((ub1 - from + 3u) & ~3u) * 4u); }
+    const int64_t bands = p.nrows / BAND, b = (int64_t) blockIdx.x * nb + j;
+    const bool active = b < bands;
+    const int64_t unit = active ? (rbase / BAND + b) * C + slab : 0;
+    uint32_t w0 = 0, my = 0, bytes = 0;
+    if (active) {
+        const uint32_t n_units = (uint32_t) hdr->n_a, n_words = (uint32_t) hdr->n_b;
+        w0 = __ldg(w.ubase + unit);
+        const uint32_t w1 = unit + 1 < (int64_t) n_units ? __ldg(w.ubase + unit + 1) : n_words, start = w0 & ~3u;
+        bytes = ((w1 - start + 4u + 3u) & ~3u) * 4u;
+        my = __ldg(w.lrel + unit * 32 + lane);
+        if (lane == 0) {
+            if (bytes <= FO_SPLIT_CAP) {
+                mbar_expect_tx(bar, bytes);
+                bulk_g2s(smem_u32(buf), w.stream + start, bytes, bar);
+            }
+            bulk_prefetch_l2(w.plane + unit * (BAND * CHUNK), BAND * CHUNK);
         }
-        first = w.stream + (ub + lr);
-        p0 = __ldg(first); p1 = __ldg(first + 1); p2 = __ldg(first + 2);
-    };
-    const uint32_t * first = nullptr;
-    uint32_t p0 = 0, p1 = 0, p2 = 0;
-    if ((int64_t) blockIdx.x * nb + j < bands) { request((rbase / BAND + (int64_t) blockIdx.x * nb + j) * C + slab, first, p0, p1, p2); }
+    }
     stage_lut(lut, w.lut);
     for (int i = threadIdx.x; i < K; i += blockDim.x) { xs[i] = to_f32(xg[i]); }
     __syncthreads();
     const int cq = 2 * (lane & 3);
-    for (int64_t b0 = (int64_t) blockIdx.x * nb; b0 < bands; b0 += (int64_t) gridDim.x * nb) {
-        const int64_t b = b0 + j;
-        const bool active = b < bands;
-        float acc[2] = {0.f, 0.f};
-        if (active) {
-            const int64_t unit = (rbase / BAND + b) * C + slab;
-            if (b0 != (int64_t) blockIdx.x * nb) { request(unit, first, p0, p1, p2); }
-            PairReader rd;
-            rd.open_loaded(first, p0, p1, p2);
-            const uint8_t * pl = w.plane + unit * (BAND * CHUNK) + 16 * lane;
+    float acc[2] = {0.f, 0.f};
+    if (active) {
+        const uint8_t * pl = w.plane + unit * (BAND * CHUNK) + 16 * lane;
+        auto body = [&](auto & rd, uint32_t lut_arg) {
             uint4 ring[4];
 #pragma unroll
             for (int i = 0; i < 4; i++) { ring[i] = ld_stream16(pl + i * 512); }
@@ -238,7 +245,7 @@ __global__ void __launch_bounds__(256) k_fo_gemv_split(const PairView w, int C, 
                     const uint4 cur = ring[i];
                     if (pp + 4 < 16) { ring[i] = ld_stream16(pl + (pp + 4) * 512); }
                     uint32_t e[8], wv[8];
-                    rd.take8(lut, e);
+                    rd.take8(lut_arg, k, e);
                     assemble8(cur, e, wv);
 #pragma unroll
                     for (int q8 = 0; q8 < 8; q8++) {
@@ -248,21 +255,35 @@ __global__ void __launch_bounds__(256) k_fo_gemv_split(const PairView w, int C, 
                     }
                 }
             }
+        };
+        if (bytes <= FO_SPLIT_CAP) {
+            const uint32_t landed = mbar_wait(bar, 0u);
+            if (landed) {
+                StagedReader rd;
+                rd.open(smem_u32(buf) + 4 * (w0 - (w0 & ~3u) + my), landed);
+                body(rd, smem_u32(lut));
+            } else if (lane == 0) {
+                atomicOr(&g_wait_expired, 1u); // the copy never arrived: the sums stay zero and the flag reports it
+            }
+        } else {
+            GlobalReader rd;
+            rd.lut = lut;
+            rd.rd.open(w, unit, lane);
+            body(rd, 0u);
         }
+    }
 #pragma unroll
-        for (int h = 0; h < 2; h++) {
-            float v = acc[h];
-            v += __shfl_xor_sync(FULL, v, 1);
-            v += __shfl_xor_sync(FULL, v, 2);
-            if ((lane & 3) == 0) { part[(j * C + slab) * 16 + (lane >> 2) + 8 * h] = v; }
-        }
-        __syncthreads();
-        if (slab == 0 && active && lane < 16) {
-            float v = part[j * C * 16 + lane];
-            for (int s2 = 1; s2 < C; s2++) { v += part[(j * C + s2) * 16 + lane]; }
-            out.put(b * BAND + lane, v);
-        }
-        __syncthreads();
+    for (int h = 0; h < 2; h++) {
+        float v = acc[h];
+        v += __shfl_xor_sync(FULL, v, 1);
+        v += __shfl_xor_sync(FULL, v, 2);
+        if ((lane & 3) == 0) { part[(j * C + slab) * 16 + (lane >> 2) + 8 * h] = v; }
+    }
+    __syncthreads();
+    if (slab == 0 && active && lane < 16) {
+        float v = part[j * C * 16 + lane];
+        for (int s2 = 1; s2 < C; s2++) { v += part[(j * C + s2) * 16 + lane]; }
+        out.put(b * BAND + lane, v);
     }
 }
 
@@ -717,9 +738,10 @@ void fo_gemv_t(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st
         const int64_t bands = p.nrows / BAND;
         if (C <= 8 && bands * a.ncols < (int64_t) device_info().sms * 64) { // few bands: a band's slabs side by side
             const int nb = std::max(1, 8 / C);
-            const size_t shm = 4 * HP_MAX_PAIRS + (size_t) w.K * 4 + (size_t) nb * C * 16 * 4;
+            const size_t shm = 4 * HP_MAX_PAIRS + 128 + (size_t) w.K * 4 + (size_t) nb * C * 16 * 4 + (size_t) nb * C * FO_SPLIT_CAP;
+            const Opaque k = {1u, 4u, ~0u, 32u};
             launch_chained(k_fo_gemv_split<TX>, dim3((unsigned) ((bands + nb - 1) / nb), (unsigned) a.ncols), dim3(nb * C * 32), shm, st,
-                           pair_view(w), C, p, nb, w.rows / BAND * C);
+                           pair_view(w), (const AuxHeader *) w.aux, C, p, nb, k);
         } else {
             launch_fo<1, TX>(w, p, a.ncols, st);
         }

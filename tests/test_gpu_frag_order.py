@@ -90,13 +90,18 @@ def test_large_matrix_kernel(ops, K, T):
     assert torch.equal(ops.mmv(x[:1].contiguous(), w)[0], y[0])  # a column does not depend on its batch
 
 
-def test_routed_columns(ops):
-    E, rows_e, K, T, k = 4, 512, 512, 3, 2
-    bits = o.weights_like(E * rows_e, K, 77)
+@pytest.mark.parametrize("K,rows_e", [(512, 512), (2048, 80), (1024, 48)])
+@pytest.mark.parametrize("fp32_x", [False, True])
+def test_routed_columns(ops, K, rows_e, fp32_x):
+    """Routed columns (expert ids): the kernel that puts a band's slabs on separate warps, 1, 4 and 2 slabs per band,
+    bands that do not fill the last block, BF16 and FP32 activations."""
+    E, T, k = 4, 3, 2
+    bits = o.weights_like(E * rows_e, K, 77 + K)
     w = fo(ops, bits)
     ids = torch.tensor([[0, 3], [2, 2], [1, 0]], dtype=torch.int32, device="cuda")
     x, x64 = act((T, k, K), 4)
-    y = ops.mmv(x, w, ids, rows_e)
+    y = ops.mmv(x.float() if fp32_x else x, w, ids, rows_e)
+    assert y.shape == (T, k, rows_e)
     w64 = o.bf16_bits_to_f32(bits).astype(np.float64).reshape(E, rows_e, K)
     for t in range(T):
         for s_ in range(k):

@@ -52,3 +52,19 @@ def test_fragment_order_outputs_match_the_reference_kernels(tmp_path):
             assert np.abs(a.astype(np.float64) - b).max() <= 2.0 ** -16 * np.abs(b).max(), n
         else:
             assert np.array_equal(a.view(np.uint32), b.view(np.uint32)), n
+
+
+@pytest.mark.skipif(not (os.path.exists(OURS) and os.path.exists(REF)), reason="baseline/_ref/api_bench_{ours,ref} not built")
+def test_fragment_order_decode_chain_matches_the_reference_kernels(tmp_path):
+    """Routed-expert decode chain (mmv with expert ids x 3, swiglu, combine) over fragment-order experts: a band's slabs are
+    summed on separate warps here, so the FP32 results agree to 2^-16 of the largest output instead of bit for bit."""
+    for exe, tag in ((REF, "ref_"), (OURS, "ours_")):
+        env = dict(os.environ, API_BENCH_DUMP=str(tmp_path / tag))
+        subprocess.run([exe, "frag_order_decode", "3"], check=True, env=env, stdout=subprocess.DEVNULL, timeout=600)
+    names = sorted(f[len("ref_"):] for f in os.listdir(tmp_path) if f.startswith("ref_"))
+    assert names == ["fo_moe_decode_1.f32", "fo_moe_decode_2.f32", "fo_moe_decode_4.f32"]
+    for n in names:
+        a = np.fromfile(tmp_path / ("ours_" + n), np.float32)
+        b = np.fromfile(tmp_path / ("ref_" + n), np.float32)
+        assert a.shape == b.shape and np.isfinite(a).all()
+        assert np.abs(a.astype(np.float64) - b).max() <= 2.0 ** -16 * np.abs(b).max(), n
