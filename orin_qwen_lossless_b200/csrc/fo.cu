@@ -733,7 +733,8 @@ void launch_fo(const bf16n_weight & w, const Cols & p, int ncols_grid, cudaStrea
 template <typename TX>
 void fo_gemv_t(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st) {
     Cols p = make_cols(a);
-    if (a.ids) {
+    // routed columns, and a single dense column of a small matrix: the kernels with one decode per column
+    if (a.ids || (a.ncols == 1 && p.nrows / BAND < (int64_t) device_info().sms * 16)) {
         const int C = (int) (w.K / CHUNK);
         const int64_t bands = p.nrows / BAND;
         if (C <= 8 && bands * a.ncols < (int64_t) device_info().sms * 64) { // few bands: a band's slabs side by side
@@ -743,7 +744,7 @@ void fo_gemv_t(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st
             launch_chained(k_fo_gemv_split<TX>, dim3((unsigned) ((bands + nb - 1) / nb), (unsigned) a.ncols), dim3(nb * C * 32), shm, st,
                            pair_view(w), (const AuxHeader *) w.aux, C, p, nb, k);
         } else {
-            launch_fo<1, TX>(w, p, a.ncols, st);
+            launch_fo<1, TX>(w, p, a.ids ? a.ncols : 1, st);
         }
         return;
     }

@@ -15,6 +15,7 @@
 // Units that do not fit the buffer (codes much longer than average) are decoded straight from global memory.
 // Products are summed in the format's order (see gemv.cu), so results equal the general kernel's bit for bit.
 #include "staged.cuh"
+#include <cstdlib>
 #include "launch.h"
 
 namespace b16 {
@@ -162,7 +163,10 @@ bool gemv_staged_applies(const bf16n_weight & w, const bf16n_mmv_args & a) {
     if (w.format != FMT_HUFPAIR || w.cm || w.fo || !(C == 1 || C == 2 || C == 4) || a.nrows <= 0) { return false; }
     const int64_t units = a.nrows / w.R;
     const int64_t room = (device_info().smem_optin - FIXED_SMEM) / buffer_bytes(w);
-    return room >= 8 && units >= (int64_t) device_info().sms * 8 * std::max(1, a.ncols);
+    // from 256 units on: below 8 units per SM the kernel still pays, because a warp that reads its lane streams straight
+    // from global memory stalls on every lane's cache line at a different moment (8192 x 2048, R = 16: 43 -> 16 us)
+    static const int64_t min_units = getenv("BF16N_STAGED_MIN_UNITS") ? atoll(getenv("BF16N_STAGED_MIN_UNITS")) : 256;
+    return room >= 8 && units >= min_units * std::max(1, a.ncols);
 }
 
 void gemv_staged(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st, const bf16n_peer_out * peers) {
@@ -178,7 +182,10 @@ void gemv_staged(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t 
         const double eff = (double) units / (double) (rounds * slots) * (nw >= 12 ? 1.0 : 0.97);
         if (eff > best_eff + 1e-9) { best_eff = eff; best = nw; }
     }
-    const dim3 grid((unsigned) sms, (unsigned) a.ncols);
+    if (units < sms * 8) { // few units: one per warp, spread over all SMs
+        best = (int) std::max<int64_t>(1, std::min<int64_t>(max_warps, (units + sms - 1) / sms));
+    }
+    const dim3 grid((unsigned) std::min<int64_t>(sms, (units + best - 1) / best), (unsigned) a.ncols);
     const size_t shm = FIXED_SMEM + (size_t) best * cap;
     const AuxHeader * hdr = (const AuxHeader *) w.aux;
     const PairView v = pair_view(w);
