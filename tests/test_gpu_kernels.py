@@ -383,11 +383,13 @@ def test_cuda_graph_replay_equals_eager(ops, dense):
 
 
 @pytest.mark.parametrize("K,R,rows", [(2048, 16, 20480), (1024, 8, 12288), (512, 16, 24576), (2048, 4, 6144),
-                                      (2048, 16, 40976), (1024, 8, 20480), (512, 16, 40960), (2048, 2, 5120)])
+                                      (2048, 16, 40976), (1024, 8, 20480), (512, 16, 40960), (2048, 2, 5120),
+                                      (2048, 16, 8192), (2048, 8, 4096), (1024, 16, 4112), (512, 16, 16384)])
 def test_mmv_large_matrix_path(ops, K, R, rows):
-    """Matrices with many units per SM take the persistent kernels that stage lane streams in shared memory (whole units
-    by bulk copy from 8 units per SM, per-lane rings with two units per warp from 16 units per SM and BF16
-    activations; 40976 rows = an odd number of units): same bits as the reference summation order, BF16 and FP32
+    """Matrices from 256 units on take the persistent kernels that stage lane streams in shared memory (whole units
+    by bulk copy: one unit per warp over all SMs below 8 units per SM, several above; per-lane rings with two units per
+    warp from 16 units per SM and BF16 activations; 40976 rows = an odd number of units, 4112 rows = 257 units): same
+    bits as the reference summation order, BF16 and FP32
     activations, BF16 output = rounding of the FP32 output."""
     w = o.weights_like(rows, K, rows + K, outliers=True)
     enc = up(ops, w, HP, R)
