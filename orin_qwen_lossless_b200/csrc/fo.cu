@@ -191,16 +191,22 @@ __global__ void __launch_bounds__(256) k_fo_gemv(const PairView w, int C, Cols p
 // and the activations are staged, and the plane is read four tile pairs ahead. A unit whose streams do not fit the
 // buffer (more than 3 bits per weight) is read from global memory.
 constexpr uint32_t FO_SPLIT_CAP = (BAND * CHUNK * 3 / 8 + 64 + 15) & ~15u;
-template <typename TX>
-__global__ void __launch_bounds__(256) k_fo_gemv_split(const PairView w, const AuxHeader * hdr, int C, Cols p, int nb, const Opaque k) {
+constexpr int FO_SPLIT_XPAD = 8; // BF16 elements of padding per activation row of the tensor-core form (as XPAD below)
+// MMA = false: one column (routed or dense) on FMAs, FP32 or BF16 activations. MMA = true: up to 8 dense BF16 columns on
+// mma.m16n8k16 (the activations are the B operand, columns beyond ncols are zero rows in shared memory).
+template <typename TX, bool MMA>
+__global__ void __launch_bounds__(256) k_fo_gemv_split(const PairView w, const AuxHeader * hdr, int C, Cols p, int nb, int ncols, const Opaque k) {
     extern __shared__ __align__(128) unsigned char smem[];
     uint32_t * lut = (uint32_t *) smem;
     uint64_t * bars = (uint64_t *) (smem + 4 * HP_MAX_PAIRS); // one per warp
     const int64_t K = (int64_t) C * CHUNK;
-    float * xs = (float *) (smem + 4 * HP_MAX_PAIRS + 128);
-    float * part = xs + K; // [band of the block][slab][16 rows]
+    const int XS = (int) K + FO_SPLIT_XPAD;
+    float * xs = (float *) (smem + 4 * HP_MAX_PAIRS + 128);              // MMA: 8 rows of XS BF16 values instead
+    bf16 * xh = (bf16 *) xs;
+    float * part = MMA ? (float *) (xh + 8 * XS) : xs + K;               // [band of the block][slab][16 rows | 32 lanes x 4]
+    constexpr int PART = MMA ? 128 : 16;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    unsigned char * buf = (unsigned char *) (part + nb * C * 16) + (size_t) warp * FO_SPLIT_CAP;
+    unsigned char * buf = (unsigned char *) (part + nb * C * PART) + (size_t) warp * FO_SPLIT_CAP;
     const int j = warp / C, slab = warp - j * C;
     const uint32_t bar = smem_u32(bars + warp);
     if (lane == 0) { mbar_init(bar, 1); }
@@ -208,7 +214,7 @@ __global__ void __launch_bounds__(256) k_fo_gemv_split(const PairView w, const A
     __syncwarp();
     grid_dependency_wait(); // activations and expert ids may come from the kernel before this one
     const TX * xg; OutVec out; int64_t rbase;
-    column<TX>(p, blockIdx.y, xg, out, rbase);
+    column<TX>(p, MMA ? 0 : blockIdx.y, xg, out, rbase);
     const int64_t bands = p.nrows / BAND, b = (int64_t) blockIdx.x * nb + j;
     const bool active = b < bands;
     const int64_t unit = active ? (rbase / BAND + b) * C + slab : 0;
@@ -228,12 +234,20 @@ __global__ void __launch_bounds__(256) k_fo_gemv_split(const PairView w, const A
         }
     }
     stage_lut(lut, w.lut);
-    for (int i = threadIdx.x; i < K; i += blockDim.x) { xs[i] = to_f32(xg[i]); }
+    if constexpr (MMA) {
+        for (int i = threadIdx.x; i < 8 * (int) K; i += blockDim.x) {
+            const int n = i / (int) K, c = i - n * (int) K;
+            xh[n * XS + c] = n < ncols ? ((const bf16 *) (p.x + n * p.x_tok))[c] : __float2bfloat16(0.f);
+        }
+    } else {
+        for (int i = threadIdx.x; i < K; i += blockDim.x) { xs[i] = to_f32(xg[i]); }
+    }
     __syncthreads();
-    const int cq = 2 * (lane & 3);
-    float acc[2] = {0.f, 0.f};
+    const int cq = 2 * (lane & 3), g8 = lane >> 2, t4 = lane & 3;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f}; // FMA form: [0], [1] = rows g8, g8 + 8 of this lane's columns; MMA form: the D fragment
     if (active) {
         const uint8_t * pl = w.plane + unit * (BAND * CHUNK) + 16 * lane;
+        const bf16 * xl = xh + g8 * XS + 2 * t4; // B fragment: token g8, k = 2 t4, + 1 (and + 8) of every tile
         auto body = [&](auto & rd, uint32_t lut_arg) {
             uint4 ring[4];
 #pragma unroll
@@ -247,11 +261,23 @@ __global__ void __launch_bounds__(256) k_fo_gemv_split(const PairView w, const A
                     uint32_t e[8], wv[8];
                     rd.take8(lut_arg, k, e);
                     assemble8(cur, e, wv);
+                    if constexpr (MMA) {
 #pragma unroll
-                    for (int q8 = 0; q8 < 8; q8++) {
-                        const int q = q8 & 3;
-                        const float2 xv = *(const float2 *) (xs + (slab * 32 + 2 * pp + (q8 >> 2)) * 16 + cq + 8 * (q >> 1));
-                        acc[q & 1] = fmaf(bf16hi_f32(wv[q8]), xv.y, fmaf(bf16lo_f32(wv[q8]), xv.x, acc[q & 1]));
+                        for (int kk = 0; kk < 2; kk++) {
+                            const int col = (slab * 32 + 2 * pp + kk) * 16;
+                            const uint32_t b0 = *(const uint32_t *) (xl + col), b1 = *(const uint32_t *) (xl + col + 8);
+                            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+                                         "{%0, %1, %2, %3};"
+                                         : "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])
+                                         : "r"(wv[4 * kk]), "r"(wv[4 * kk + 1]), "r"(wv[4 * kk + 2]), "r"(wv[4 * kk + 3]), "r"(b0), "r"(b1));
+                        }
+                    } else {
+#pragma unroll
+                        for (int q8 = 0; q8 < 8; q8++) {
+                            const int q = q8 & 3;
+                            const float2 xv = *(const float2 *) (xs + (slab * 32 + 2 * pp + (q8 >> 2)) * 16 + cq + 8 * (q >> 1));
+                            acc[q & 1] = fmaf(bf16hi_f32(wv[q8]), xv.y, fmaf(bf16lo_f32(wv[q8]), xv.x, acc[q & 1]));
+                        }
                     }
                 }
             }
@@ -272,17 +298,36 @@ __global__ void __launch_bounds__(256) k_fo_gemv_split(const PairView w, const A
             body(rd, 0u);
         }
     }
+    float * mine = part + (j * C + slab) * PART;
+    if constexpr (MMA) {
 #pragma unroll
-    for (int h = 0; h < 2; h++) {
-        float v = acc[h];
-        v += __shfl_xor_sync(FULL, v, 1);
-        v += __shfl_xor_sync(FULL, v, 2);
-        if ((lane & 3) == 0) { part[(j * C + slab) * 16 + (lane >> 2) + 8 * h] = v; }
+        for (int i = 0; i < 4; i++) { mine[i * 32 + lane] = acc[i]; }
+    } else {
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            float v = acc[h];
+            v += __shfl_xor_sync(FULL, v, 1);
+            v += __shfl_xor_sync(FULL, v, 2);
+            if ((lane & 3) == 0) { mine[(lane >> 2) + 8 * h] = v; }
+        }
     }
     __syncthreads();
-    if (slab == 0 && active && lane < 16) {
-        float v = part[j * C * 16 + lane];
-        for (int s2 = 1; s2 < C; s2++) { v += part[(j * C + s2) * 16 + lane]; }
+    if (slab != 0 || !active) { return; }
+    const float * sums = part + j * C * PART;
+    if constexpr (MMA) { // D fragment: [0], [1] = row g8, tokens 2 t4, + 1; [2], [3] = row g8 + 8
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            float v = sums[i * 32 + lane];
+            for (int s2 = 1; s2 < C; s2++) { v += sums[s2 * PART + i * 32 + lane]; }
+            const int n = 2 * t4 + (i & 1);
+            if (n < ncols) {
+                const OutVec o = {p.y + n * p.y_tok, p.y_bf16};
+                o.put(b * BAND + g8 + 8 * (i >> 1), v);
+            }
+        }
+    } else if (lane < 16) {
+        float v = sums[lane];
+        for (int s2 = 1; s2 < C; s2++) { v += sums[s2 * PART + lane]; }
         out.put(b * BAND + lane, v);
     }
 }
@@ -741,8 +786,8 @@ void fo_gemv_t(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st
             const int nb = std::max(1, 8 / C);
             const size_t shm = 4 * HP_MAX_PAIRS + 128 + (size_t) w.K * 4 + (size_t) nb * C * 16 * 4 + (size_t) nb * C * FO_SPLIT_CAP;
             const Opaque k = {1u, 4u, ~0u, 32u};
-            launch_chained(k_fo_gemv_split<TX>, dim3((unsigned) ((bands + nb - 1) / nb), (unsigned) a.ncols), dim3(nb * C * 32), shm, st,
-                           pair_view(w), (const AuxHeader *) w.aux, C, p, nb, k);
+            launch_chained(k_fo_gemv_split<TX, false>, dim3((unsigned) ((bands + nb - 1) / nb), (unsigned) a.ncols), dim3(nb * C * 32), shm, st,
+                           pair_view(w), (const AuxHeader *) w.aux, C, p, nb, 1, k);
         } else {
             launch_fo<1, TX>(w, p, a.ids ? a.ncols : 1, st);
         }
@@ -778,6 +823,15 @@ void fo_gemv_t(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st
                 const Opaque k = {1u, 4u, ~0u, 32u};
                 launch_chained(k_fo_gemv_staged, dim3((unsigned) sms), dim3(staged_warps * 32), shm_staged, st, pair_view(w),
                                (const AuxHeader *) w.aux, C, q, nc, k);
+            } else if (C <= 8) { // small and mid-size matrices: a band's slabs on separate warps, streams staged
+                if constexpr (sizeof(TX) == 2) {
+                    const int nb = std::max(1, 8 / C);
+                    const size_t shm = 4 * HP_MAX_PAIRS + 128 + (size_t) 8 * (w.K + FO_SPLIT_XPAD) * 2 + (size_t) nb * C * 128 * 4 +
+                                       (size_t) nb * C * FO_SPLIT_CAP;
+                    const Opaque k = {1u, 4u, ~0u, 32u};
+                    launch_chained(k_fo_gemv_split<bf16, true>, dim3((unsigned) ((bands + nb - 1) / nb)), dim3(nb * C * 32), shm, st,
+                                   pair_view(w), (const AuxHeader *) w.aux, C, q, nb, nc, k);
+                }
             } else {
                 const int warps = bands >= sms * 32 ? 8 : bands >= sms * 8 ? 4 : 2;
                 const dim3 grid((unsigned) std::min<int64_t>((bands + warps - 1) / warps, sms * 8));
@@ -809,7 +863,7 @@ void fo_init() {
     ATTR((k_fo_gemv<1, float>)); ATTR((k_fo_gemv<2, float>)); ATTR((k_fo_gemv<4, float>)); ATTR((k_fo_gemv<8, float>));
     ATTR((k_fo_gemv<1, bf16>)); ATTR((k_fo_gemv<2, bf16>)); ATTR((k_fo_gemv<4, bf16>)); ATTR((k_fo_gemv<8, bf16>));
     ATTR(k_fo_gemv_mma);
-    ATTR(k_fo_gemv_split<float>); ATTR(k_fo_gemv_split<bf16>);
+    ATTR((k_fo_gemv_split<float, false>)); ATTR((k_fo_gemv_split<bf16, false>)); ATTR((k_fo_gemv_split<bf16, true>));
     ATTR(k_fo_gemv_staged);
     ATTR(k_fo_mm_ids<false>); ATTR(k_fo_mm_ids<true>);
 #undef ATTR
