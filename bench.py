@@ -593,6 +593,31 @@ def run_moe_prefill(args):
         dist.destroy_process_group()
 
 
+def run_dense_mid(args):
+    """Mid-size dense projections (8-32 M weights: what the policy gives HUFPAIR below the vocabulary projection), R as
+    the policy picks it for the lane-major layout and 16-row bands for fragment order; 1, 4 and 8 BF16 tokens; every
+    shape as a CUDA graph of 20 GEMVs over rotating copies so that weights come from HBM."""
+    import torch
+    from orin_qwen_lossless_b200 import ops
+    dev = torch.device("cuda", 0)
+    ops.init()
+    for rows, K, R in ((4096, 2048, 8), (8192, 2048, 16), (16384, 2048, 16)):
+        for fo in (False, True):
+            copies = [_enc(ops, rows, K, 3, 16 if fo else R, False, 900 + c, dev, fo) for c in range(8)]  # 8 x >= 11 MB, rotated
+            line = {"workload": f"dense {rows}x{K} HUFPAIR, " + ("fragment order" if fo else f"lane-major R={R}"),
+                    "compressed_bytes": copies[0].nbytes}
+            for T in (1, 4, 8):
+                x = torch.randn(T, K, device=dev).to(torch.bfloat16)
+                ys = [torch.empty(T, rows, device=dev) for _ in copies]
+
+                def step():
+                    for i in range(20):
+                        ops.mmv(x, copies[i % 8], out=ys[i % 8])
+
+                line[f"us_{T}_tok"] = round(_time_graph(torch, step, max(10, args.steps // 20), inner=20), 2)
+            print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -604,12 +629,13 @@ def main():
     ap.add_argument("--cublas", action="store_true", help="also time a stock BF16 GEMV of the uncompressed matrix")
     ap.add_argument("--fo", action="store_true", help="moe_prefill: experts in the fragment-order layout (mma.sync batched kernel)")
     ap.add_argument("--nccl", action="store_true", help="N > 1, moe_decode: all-reduce with NCCL instead of the fused peer stores")
-    ap.add_argument("--workload", default="lm_head", choices=["lm_head", "small", "moe_decode", "moe_prefill"],
+    ap.add_argument("--workload", default="lm_head", choices=["lm_head", "small", "moe_decode", "moe_prefill", "dense_mid"],
                     help="lm_head is the headline contract line; the others print extra lines for the other baseline configs "
                          "(small: 1 GPU; the MoE workloads run expert-parallel under torchrun)")
     args = ap.parse_args()
     if args.workload != "lm_head":
-        return {"small": run_small, "moe_decode": run_moe_decode, "moe_prefill": run_moe_prefill}[args.workload](args)
+        return {"small": run_small, "moe_decode": run_moe_decode, "moe_prefill": run_moe_prefill,
+                "dense_mid": run_dense_mid}[args.workload](args)
     if args.impl == "reference":
         run_reference(args)
     else:
