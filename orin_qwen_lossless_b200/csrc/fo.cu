@@ -779,7 +779,10 @@ template <typename TX>
 void fo_gemv_t(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st) {
     Cols p = make_cols(a);
     // routed columns, and a single dense column of a small matrix: the kernels with one decode per column
-    if (a.ids || (a.ncols == 1 && p.nrows / BAND < (int64_t) device_info().sms * 16)) {
+    // From 16 bands per SM on, BF16 activations take the persistent kernel; below, it was measured level with or behind
+    // the split kernels (16384 x 2048: 34.6 against 22.4 us at one token, 35.9 against 35.6 at eight). Development switch.
+    static const int64_t big_per_sm = getenv("BF16N_FO_BIG_BANDS_PER_SM") ? atoll(getenv("BF16N_FO_BIG_BANDS_PER_SM")) : 16;
+    if (a.ids || (a.ncols == 1 && (p.nrows / BAND < (int64_t) device_info().sms * big_per_sm || !a.x_bf16))) {
         const int C = (int) (w.K / CHUNK);
         const int64_t bands = p.nrows / BAND;
         if (C <= 8 && bands * a.ncols < (int64_t) device_info().sms * 64) { // few bands: a band's slabs side by side
@@ -793,7 +796,7 @@ void fo_gemv_t(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st
         }
         return;
     }
-    if (a.x_bf16 && (a.ncols >= 2 || p.nrows / BAND >= (int64_t) device_info().sms * 16)) {
+    if (a.x_bf16 && (a.ncols >= 2 || p.nrows / BAND >= (int64_t) device_info().sms * big_per_sm)) {
         // BF16 activations: the tensor-core kernels, 8 columns per decode. Large matrices (at least 16 bands per SM) take
         // the persistent kernel with staged streams, also for a single column.
         const int C = (int) (w.K / CHUNK);
@@ -812,7 +815,7 @@ void fo_gemv_t(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st
         }
         if (forced_warps > 0) { staged_warps = std::min(32, forced_warps); }
         const size_t shm_staged = shm_fixed + (size_t) staged_warps * 2 * FO_CAP;
-        const bool big = bands >= sms * 16 && (uintptr_t) p.x % 16 == 0 && p.x_tok % 16 == 0 && staged_warps >= 8 &&
+        const bool big = bands >= sms * big_per_sm && (uintptr_t) p.x % 16 == 0 && p.x_tok % 16 == 0 && staged_warps >= 1 &&
                          shm_staged <= optin;
         for (int c0 = 0; c0 < a.ncols; c0 += 8) {
             Cols q = p;
