@@ -84,10 +84,24 @@ int bf16n_choose(int64_t rows, int64_t K, int64_t n_matrices, int engine, int mo
 
 /* ---- device side ---------------------------------------------------------------------------------------------- */
 
-/* Once per process and device, before the first launch and before any graph capture: device attributes and the
- * kernels' shared-memory limits. Replaces bf16n::init / bf16n::sm_count (launch.h:45-46, core/src/launch.cu:270-311). */
+/* Once per process, with the process's GPU current, before the first launch and before any graph capture: device
+ * attributes and the kernels' shared-memory limits. One process drives one device (one process per GPU): every later
+ * call checks that the device bf16n_init ran on is still the current one and returns BF16N_EINVAL otherwise.
+ * Replaces bf16n::init / bf16n::sm_count (launch.h:45-46, core/src/launch.cu:270-311). */
 int bf16n_init(void);
 int bf16n_sm_count(int * out);
+
+/* Every wait inside a kernel is bounded (bulk copies completing on an mbarrier, tensor-core commits). When one runs out
+ * the kernel sets a status word, writes NaN where the affected work item's outputs go and finishes, so the context stays
+ * usable. This call synchronises the stream, returns the status words since the last call as a bit mask and clears
+ * them: bit 0 the bulk-copy staged GEMV, bit 1 the MoE decode unit kernels, bit 2 the fragment-order kernels, bit 3 the
+ * batched (prefill) kernel. 0 means every launch so far wrote complete outputs. Not capturable (it synchronises).
+ * The reference has no bounded waits and nothing like this. */
+#define BF16N_FAULT_GEMV_STAGED 1u
+#define BF16N_FAULT_MOE_DECODE 2u
+#define BF16N_FAULT_FRAG_ORDER 4u
+#define BF16N_FAULT_PREFILL 8u
+int bf16n_fault_status(unsigned int * flags, void * stream);
 
 /* GEMV (<= a few columns), dense or routed by expert ids. multi_col != 0: dense batches of 2..4 columns decode the
  * matrix once per group of 4. Replaces bf16n::mmv (launch.h:50, launch.cu:313-325). */
@@ -206,9 +220,12 @@ int bf16n_exchange_destroy(void * base);
 /* bf16n_mmv whose output also goes to the peers (dense row-major HUFPAIR matrices; one kernel does the product, the
  * peer stores and the announcement). a->y must point into this GPU's exchange payload at the offset the peers use. */
 int bf16n_mmv_peers(const bf16n_weight * w, const bf16n_mmv_args * a, const bf16n_peer_out * peers, void * stream);
-/* Waits on the stream until every peer in rank_mask (bit r = rank r) has announced its next epoch; bounded (about two
- * seconds), after which header word 19 is set and the stream continues. */
+/* Waits on the stream until every peer in rank_mask (bit r = rank r) has announced its next epoch; bounded (two
+ * seconds unless bf16n_set_peer_wait_limit_ms changed it), after which header word 19 is set and the stream continues. */
 int bf16n_peer_wait(uint32_t * local_header, int rank_mask, void * stream);
+/* How long bf16n_peer_wait and the kernels that wait for their peers themselves (wait_mask) may spin, 1..60000 ms. The
+ * limit is a launch argument: it applies to launches made (or captured) after this call. */
+int bf16n_set_peer_wait_limit_ms(unsigned int ms);
 /* bf16n_moe_decode on an expert-parallel rank whose last kernel (the slot-order combine) also stores the rank's partial
  * [n_tok, H] output into every peer (y and peers->y[r] are this rank's slot in the exchange payloads), announces it and,
  * with peers->wait_mask, ends only when the peers' partial outputs have arrived. */

@@ -30,9 +30,19 @@ MAGIC = 0x4E363142
 _u8p = C.POINTER(C.c_uint8)
 
 
+def reference_checkout() -> str | None:
+    """Where the reference project's sources lie: $BF16N_REFERENCE, else a directory named `reference` beside this
+    repository; None when neither holds core/src/encode.cpp (then a prebuilt oracle/_ref is used if present)."""
+    for cand in (os.environ.get("BF16N_REFERENCE"), os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")):
+        if cand and os.path.exists(os.path.join(cand, "core", "src", "encode.cpp")):
+            return cand
+    return None
+
+
 def build() -> None:
     """Compile the oracle (and, where the reference checkout exists, oracle/_ref) with the Makefile beside this file."""
-    subprocess.run(["make", "-s", "-C", HERE], check=True, stdout=subprocess.DEVNULL)
+    ref = reference_checkout()
+    subprocess.run(["make", "-s", "-C", HERE] + ([f"REF={ref}"] if ref else []), check=True, stdout=subprocess.DEVNULL)
 
 
 def _load(path: str):

@@ -78,6 +78,8 @@ SIGNATURES = {
     "bf16n_peer_sum": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "bf16n_peer_wait": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "bf16n_peer_expired": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
+    "bf16n_set_peer_wait_limit_ms": (C.c_int, [C.c_uint]),
+    "bf16n_fault_status": (C.c_int, [C.POINTER(C.c_uint), C.c_void_p]),
 }
 
 _lib = None

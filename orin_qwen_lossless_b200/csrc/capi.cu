@@ -4,6 +4,7 @@
 #include "launch.h"
 #include "policy.h"
 
+#include <atomic>
 #include <cstring>
 #include <mutex>
 
@@ -15,6 +16,9 @@ DeviceInfo g_info;
 std::once_flag g_once;
 int g_init_status = BF16N_OK;
 std::string g_init_error;
+int g_device = -1;                         // the device bf16n_init ran on: the only one this process may launch on
+unsigned int * g_fault_words[4] = {};      // bit i of bf16n_fault_status: gemv_staged, moe_decode, fragment order, prefill
+std::atomic<uint64_t> g_peer_wait_ns{2000000000ull};
 
 template <typename F>
 int guarded(F && f) {
@@ -38,6 +42,7 @@ void ensure_init() {
         try {
             int dev = 0;
             cuda_ok(cudaGetDevice(&dev), "cudaGetDevice");
+            g_device = dev;
             cuda_ok(cudaDeviceGetAttribute(&g_info.sms, cudaDevAttrMultiProcessorCount, dev), "SM count");
             cuda_ok(cudaDeviceGetAttribute(&g_info.smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev), "shared memory limit");
             gemv_init();
@@ -45,12 +50,24 @@ void ensure_init() {
             moe_decode_init();
             prefill_init();
             fo_init();
+            g_fault_words[0] = gemv_staged_fault_word();
+            g_fault_words[1] = moe_decode_fault_word();
+            g_fault_words[2] = fo_fault_word();
+            g_fault_words[3] = prefill_fault_word();
         } catch (const std::exception & e) {
             g_init_status = BF16N_ECUDA;
             g_init_error = e.what();
         }
     });
     if (g_init_status != BF16N_OK) { throw std::runtime_error(g_init_error); }
+    // The kernels' shared-memory limits, the SM count the grids are sized from and the fault words belong to the device
+    // that was current at the first call: one process drives one GPU, and a launch from another device is refused.
+    int dev = -1;
+    cuda_ok(cudaGetDevice(&dev), "cudaGetDevice");
+    if (dev != g_device) {
+        fail_invalid("this process initialised device " + std::to_string(g_device) + " and the current device is " +
+                     std::to_string(dev) + ": one device per process");
+    }
 }
 
 void check_weight(const bf16n_weight & w) {
@@ -86,6 +103,7 @@ void check_x(const bf16n_weight & w, const bf16n_mmv_args & a) {
 } // namespace
 
 const DeviceInfo & device_info() { return g_info; }
+namespace dev { uint64_t peer_wait_limit_ns() { return g_peer_wait_ns.load(std::memory_order_relaxed); } }
 
 } // namespace b16
 
@@ -145,6 +163,29 @@ int bf16n_choose(int64_t rows, int64_t K, int64_t n_matrices, int engine, int mo
 }
 
 int bf16n_init(void) { return guarded([] { ensure_init(); }); }
+
+int bf16n_fault_status(unsigned int * flags, void * stream) {
+    return guarded([&] {
+        require(flags != nullptr, "fault_status: null argument");
+        ensure_init();
+        cudaStream_t st = (cudaStream_t) stream;
+        unsigned int seen[4] = {0, 0, 0, 0};
+        for (int i = 0; i < 4; i++) {
+            cuda_ok(cudaMemcpyAsync(&seen[i], g_fault_words[i], sizeof(unsigned int), cudaMemcpyDeviceToHost, st), "fault word read");
+            cuda_ok(cudaMemsetAsync(g_fault_words[i], 0, sizeof(unsigned int), st), "fault word clear");
+        }
+        cuda_ok(cudaStreamSynchronize(st), "fault word read");
+        *flags = 0;
+        for (int i = 0; i < 4; i++) { if (seen[i]) { *flags |= 1u << i; } }
+    });
+}
+
+int bf16n_set_peer_wait_limit_ms(unsigned int ms) {
+    return guarded([&] {
+        require(ms >= 1 && ms <= 60000, "peer wait limit: 1..60000 ms");
+        g_peer_wait_ns.store((uint64_t) ms * 1000000ull, std::memory_order_relaxed);
+    });
+}
 int bf16n_sm_count(int * out) { return guarded([&] { ensure_init(); *out = g_info.sms; }); }
 
 int bf16n_mmv(const bf16n_weight * w, const bf16n_mmv_args * a, void * stream, int multi_col) {
@@ -302,6 +343,8 @@ static void moe_decode_checked(const bf16n_weight * gate, const bf16n_weight * u
                                int n_tok, int n_used, int expert_lo, int n_experts_local, float * scratch, size_t scratch_bytes,
                                void * y, int y_bf16, void * stream, const bf16n_peer_out * peers) {
     ensure_init();
+    require(gate && up && down, "moe_decode: null weight");
+    require(n_tok <= 0 || (x && y && topk_ids && topk_weights && scratch), "moe_decode: null argument");
     check_weight(*gate); check_weight(*up); check_weight(*down);
     require(moe_decode_supported(*gate, *up, *down),
             "moe_decode: gate/up must be chunk-major HUFPAIR R = 8 K = 2048 and down row-major HUFPAIR R = 16 K = 512");
@@ -359,6 +402,8 @@ int bf16n_moe_decode_static(const bf16n_weight * gate, const bf16n_weight * up, 
                             int n_tok, int n_used, int expert_lo, int n_experts_local, void * y, int y_bf16, void * stream) {
     return guarded([&] {
         ensure_init();
+        require(gate && up && down, "moe_decode: null weight");
+        require(n_tok <= 0 || (x && y && topk_ids && topk_weights), "moe_decode: null argument");
         check_weight(*gate); check_weight(*up); check_weight(*down);
         require(moe_decode_supported(*gate, *up, *down),
                 "moe_decode: gate/up must be chunk-major HUFPAIR R = 8 K = 2048 and down row-major HUFPAIR R = 16 K = 512");

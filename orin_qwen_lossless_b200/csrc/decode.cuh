@@ -93,6 +93,7 @@ struct PeerOut {
     uint32_t * flag[MAX_PEERS];   // this rank's slot in each peer's exchange header
     uint32_t * hdr;               // this rank's own exchange header (block counter, epochs): words of bf16n_c.h's layout
     int wait_mask;                // ranks whose announcement of the same epoch the last block awaits before the kernel ends
+    uint64_t wait_ns;             // how long that wait may take before the header's expired word is set (bf16n_set_peer_wait_limit_ms)
 };
 constexpr int XH_DONE = 16, XH_SENT = 17, XH_WAITED = 18, XH_EXPIRED = 19; // header words (0..7: the peers' flags)
 
@@ -136,7 +137,7 @@ __device__ __forceinline__ void peers_done(const PeerOut & o) {
             }
             // Optionally the kernel also stands in for the consumer's wait: it ends only when the peers' outputs of the
             // same epoch have arrived here. A peer publishes before it waits, so no rank waits for a rank that waits
-            // for it. Bounded: after about two seconds the header's expired word is set and the kernel ends anyway.
+            // for it. Bounded: after wait_ns (two seconds by default) the header's expired word is set and the kernel ends anyway.
             if (o.wait_mask) {
                 uint64_t t0 = 0;
                 bool all = false;
@@ -152,7 +153,7 @@ __device__ __forceinline__ void peers_done(const PeerOut & o) {
                     if (!all && (i & 1023u) == 1023u) {
                         uint64_t now;
                         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-                        if (t0 == 0) { t0 = now; } else if (now - t0 > 2000000000ull) { break; }
+                        if (t0 == 0) { t0 = now; } else if (now - t0 > o.wait_ns) { break; }
                     }
                 }
                 if (!all) { o.hdr[XH_EXPIRED] = 1u; }
@@ -405,6 +406,8 @@ inline NibView nib_view(const bf16n_weight & w, int64_t shift_rows = 0) {
             (const uint32_t *) (w.aux + w.off_c) + shift_rows, (const uint32_t *) (w.aux + w.off_d)};
 }
 
+uint64_t peer_wait_limit_ns(); // capi.cu: the limit set by bf16n_set_peer_wait_limit_ms (default two seconds)
+
 inline PeerOut make_peer_out(const bf16n_peer_out * peers) {
     PeerOut o = {};
     if (peers) {
@@ -415,6 +418,7 @@ inline PeerOut make_peer_out(const bf16n_peer_out * peers) {
         }
         o.hdr = peers->local_header;
         o.wait_mask = peers->wait_mask;
+        o.wait_ns = peer_wait_limit_ns();
     }
     return o;
 }

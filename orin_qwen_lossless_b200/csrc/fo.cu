@@ -288,8 +288,10 @@ __global__ void __launch_bounds__(256) k_fo_gemv_split(const PairView w, const A
                 StagedReader rd;
                 rd.open(smem_u32(buf) + 4 * (w0 - (w0 & ~3u) + my), landed);
                 body(rd, smem_u32(lut));
-            } else if (lane == 0) {
-                atomicOr(&g_wait_expired, 1u); // the copy never arrived: the sums stay zero and the flag reports it
+            } else { // the copy never arrived: the flag reports it and the band's outputs become NaN
+                if (lane == 0) { atomicOr(&g_wait_expired, 1u); }
+#pragma unroll
+                for (int i = 0; i < 4; i++) { acc[i] = __int_as_float(0x7fc00000); }
             }
         } else {
             GlobalReader rd;
@@ -694,14 +696,15 @@ __global__ void __launch_bounds__(1024) k_fo_gemv_staged(const PairView w, const
     const int g8 = lane >> 2, t4 = lane & 3;
     const bf16 * xl = xs + g8 * XS + 2 * t4;
     uint32_t parity = 0u; // bit b: phase of buffer b's barrier
+    bool dead = false;    // a bulk copy of this warp never arrived: no further copies, NaN outputs
     const int64_t bands = p.nrows / BAND;
     for (int64_t b = (int64_t) blockIdx.x * nwarp + warp; b < bands; b += (int64_t) gridDim.x * nwarp) {
         const int64_t gband = p.row0 / BAND + b;
         float d[4] = {0.f, 0.f, 0.f, 0.f};
         Geo cur = geometry(gband * C);
         __syncwarp(); // every lane is done with both buffers (previous band)
-        stage(cur, 0);
-        for (int slab = 0; slab < C; slab++) {
+        if (!dead) { stage(cur, 0); }
+        for (int slab = 0; slab < C && !dead; slab++) {
             Geo nxt = {0, 0, 0};
             if (slab + 1 < C) {
                 nxt = geometry(gband * C + slab + 1);
@@ -736,9 +739,10 @@ __global__ void __launch_bounds__(1024) k_fo_gemv_staged(const PairView w, const
             if (cur.bytes <= FO_CAP) {
                 const int bi = slab & 1;
                 const uint32_t landed = mbar_wait(smem_u32(bars + 2 * warp + bi), (parity >> bi) & 1u);
-                if (!landed) {
+                if (!landed) { // the copy never arrived: this band and the warp's later bands are written as NaN
                     if (lane == 0) { atomicOr(&g_wait_expired, 1u); }
-                    return;
+                    dead = true;
+                    break;
                 }
                 parity ^= 1u << bi;
                 StagedReader rd;
@@ -757,7 +761,7 @@ __global__ void __launch_bounds__(1024) k_fo_gemv_staged(const PairView w, const
             const int n = 2 * t4 + (i & 1);
             if (n < ncols) {
                 const OutVec o = {p.y + n * p.y_tok, p.y_bf16};
-                o.put(b * BAND + g8 + 8 * (i >> 1), d[i]);
+                o.put(b * BAND + g8 + 8 * (i >> 1), dead ? __int_as_float(0x7fc00000) : d[i]);
             }
         }
     }
@@ -780,8 +784,8 @@ void fo_gemv_t(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st
     Cols p = make_cols(a);
     // routed columns, and a single dense column of a small matrix: the kernels with one decode per column
     // From 16 bands per SM on, BF16 activations take the persistent kernel; below, it was measured level with or behind
-    // the split kernels (16384 x 2048: 34.6 against 22.4 us at one token, 35.9 against 35.6 at eight). Development switch.
-    static const int64_t big_per_sm = getenv("BF16N_FO_BIG_BANDS_PER_SM") ? atoll(getenv("BF16N_FO_BIG_BANDS_PER_SM")) : 16;
+    // the split kernels (16384 x 2048: 34.6 against 22.4 us at one token, 35.9 against 35.6 at eight).
+    constexpr int64_t big_per_sm = 16;
     if (a.ids || (a.ncols == 1 && (p.nrows / BAND < (int64_t) device_info().sms * big_per_sm || !a.x_bf16))) {
         const int C = (int) (w.K / CHUNK);
         const int64_t bands = p.nrows / BAND;
@@ -805,7 +809,6 @@ void fo_gemv_t(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st
         // One persistent block per SM with as many warps as the shared memory holds stream buffers for (28 with K = 2048;
         // the decode chains need the occupancy), then the fewest warps that still finish in the same number of bands
         // per warp, so that no warp slows the others down for nothing.
-        static const int forced_warps = getenv("BF16N_FO_STAGED_WARPS") ? atoi(getenv("BF16N_FO_STAGED_WARPS")) : 0;
         const size_t shm_fixed = 4 * HP_MAX_PAIRS + FO_BARS + x_bytes;
         const size_t optin = (size_t) device_info().smem_optin;
         int staged_warps = optin > shm_fixed ? (int) std::min<size_t>(32, (optin - shm_fixed) / (2 * FO_CAP)) : 0;
@@ -813,7 +816,6 @@ void fo_gemv_t(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st
             const int64_t rounds = (bands + sms * staged_warps - 1) / (sms * staged_warps);
             staged_warps = (int) ((bands + sms * rounds - 1) / (sms * rounds));
         }
-        if (forced_warps > 0) { staged_warps = std::min(32, forced_warps); }
         const size_t shm_staged = shm_fixed + (size_t) staged_warps * 2 * FO_CAP;
         const bool big = bands >= sms * big_per_sm && (uintptr_t) p.x % 16 == 0 && p.x_tok % 16 == 0 && staged_warps >= 1 &&
                          shm_staged <= optin;
@@ -859,6 +861,8 @@ void fo_gemv_t(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st
 }
 
 } // namespace
+
+BF16N_DEFINE_FAULT_WORD(fo_fault_word)
 
 void fo_init() {
     const int optin = device_info().smem_optin;

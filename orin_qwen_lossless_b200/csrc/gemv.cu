@@ -521,10 +521,8 @@ dim3 row_geometry(int64_t work, int ncols) { // 8 warps per block, one work item
 // Mid-size dense HUFPAIR matrices (256 units up to 4 per SM) with several columns: one staged decode per column over all
 // SMs instead of the general kernel's shared decode, whose warps read their lane streams straight from global memory
 // (4096 x 2048, R = 8: 29 -> 19 us at 4 tokens, 54 -> 33 us at 8; from 1024 units on the two forms are level).
-// Development switch: BF16N_MID_BY_COLUMN=0 turns it off.
 static bool mid_size_by_column(const bf16n_weight & w, const bf16n_mmv_args & a, int64_t units) {
-    static const bool on = !(getenv("BF16N_MID_BY_COLUMN") && atoi(getenv("BF16N_MID_BY_COLUMN")) == 0);
-    if (!on || units > (int64_t) device_info().sms * 4) { return false; }
+    if (units > (int64_t) device_info().sms * 4) { return false; }
     bf16n_mmv_args one = a;
     one.ncols = 1;
     return gemv_staged_applies(w, one);
@@ -550,6 +548,9 @@ void launch_gemv(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t 
                 default: fail_invalid("unsupported chunk-major K/R");
             }
 #undef CM
+        } else if (gemv_rings_enabled() && gemv_rings_applies(w, a)) {
+            gemv_rings(w, a, st, multi_col, peers); // large matrices, BF16 activations: 1, 2 or 4 columns per decode
+            return;
         } else if (!a.ids && a.ncols > 1 && multi_col && !mid_size_by_column(w, a, units)) {
             unit_geometry(units, 1, 16, grid, threads);
             for (int c0 = 0; c0 < a.ncols; c0 += 4) {
@@ -566,9 +567,6 @@ void launch_gemv(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t 
                 }
 #undef MC
             }
-        } else if (gemv_rings_enabled() && gemv_rings_applies(w, a)) {
-            gemv_rings(w, a, st, peers);
-            return;
         } else if (gemv_staged_applies(w, a) || (!a.ids && a.ncols > 1 && mid_size_by_column(w, a, units))) {
             gemv_staged(w, a, st, peers);
             return;

@@ -1,23 +1,37 @@
-// Large-matrix decode+GEMV for BF16 activations (the vocabulary projection): per-lane shared-memory rings.
+// Large-matrix decode+GEMV for BF16 activations (the vocabulary projection): per-lane shared-memory rings, activations
+// in tensor memory.
 //
-// Decoding a lane stream is a serial chain (table lookup -> code length -> next lookup) of about 18 instructions per
-// pair of weights, most of them on the half-rate integer pipes, so the kernel is bound by instruction issue and by the
-// shared-memory pipe (random table lookups conflict about 4 ways), not by HBM. What helps is many independent chains per
-// SM and few registers per chain:
-//   * one unit per warp and up to 28 warps per block (72 registers per thread): the activations live in shared memory
-//     (BF16, natural order, conflict-free 8-byte reads at base + immediate) and the plane is prefetched one row ahead;
+// Decoding a lane stream is a serial chain (table lookup -> code length -> next lookup) of about 16 instructions per
+// pair of weights. The kernel is bound by the shared-memory pipe (a random 4-byte lookup in the table costs three to
+// four bank-conflict wavefronts) and by instruction issue, not by HBM. What helps is many independent chains per SM,
+// few registers per chain, and everything that is not a table lookup kept off the shared-memory pipe:
+//   * one unit per warp and up to 28 warps per block (72 registers per thread);
+//   * the activations a lane multiplies with are the same for every row, so they sit in tensor memory (tcgen05.st once,
+//     tcgen05.ld of four words per half chunk into two register sets in turn): TMEM is read through its own pipe, which
+//     this kernel otherwise leaves idle, and the reads cost the shared-memory pipe nothing;
+//   * four copies of the code table, interleaved word by word (entry i of copy r at word 4 i + r; lane l reads copy
+//     l % 4): only the eight lanes that share a copy can collide on a bank;
 //   * a chain's stream footprint is a 128-byte ring per lane (4 KB per warp) filled with cp.async 16-byte granules,
 //     topped up at every row start to more than 96 bytes ahead of the read pointer; a row consumes at most 48 bytes
 //     (32 codes of up to 12 bits) and everything copied before the previous row start has landed (wait_group 0 at the
 //     row start, a row of work after the copies were issued), so the words a row reads are always complete;
+//   * the ring is read as a window of three consecutive words and a bit offset: one funnel shift per view of the
+//     stream, no shift of the window per code, and a refill is two register moves and one load;
 //   * ring addressing: byte offset from the unit's 16-byte aligned start, modulo 128, XOR a per-lane constant that also
-//     carries the lane's ring base: one logic op per address, and lanes that read in step hit different banks;
-//   * BF16 x BF16 + FP32 fma on the activations and the merged weights (exact products, one rounding: the same bits as
-//     an FP32 fma of the widened values), the same summation order as every other kernel of the format.
+//     carries the lane's ring base: one logic op per address;
+//   * 2 or 4 dense columns share one decode (each column's activations in its own TMEM columns, four accumulators per
+//     column), bitwise equal to the single-column results;
+//   * the same summation order as every other kernel of the format (four accumulators per lane by column mod 4,
+//     (a0 + a1) + (a2 + a3), xor butterfly), FP32 fma of exact BF16 products.
 #include "decode.cuh"
 #include "launch.h"
 
-#include <cstdlib>
+#ifndef RV_WARPS
+#define RV_WARPS 28
+#endif
+#ifndef RV_XF32
+#define RV_XF32 0
+#endif
 
 namespace b16 {
 namespace {
@@ -29,6 +43,8 @@ struct Opaque { uint32_t one, four, minus_one, thirty_two, sixteen; }; // see ge
 
 constexpr int RING_BYTES = 128;
 constexpr uint32_t RING_TARGET = 96; // fetch while at most this many bytes are ahead of the read pointer
+constexpr int LUT_COPIES = 4;
+constexpr int LUT_BYTES = 4 * HP_MAX_PAIRS * LUT_COPIES;
 
 __device__ __forceinline__ uint32_t smem_u32(const void * p) { return (uint32_t) __cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint32_t imad(uint32_t a, uint32_t b, uint32_t c) {
@@ -36,9 +52,8 @@ __device__ __forceinline__ uint32_t imad(uint32_t a, uint32_t b, uint32_t c) {
     asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
     return d;
 }
-// Ring read. Not volatile, so that the two chains of a warp can be interleaved by the instruction scheduler; `token`
-// is a value produced by the last cp.async wait, which keeps the read after that wait (the data dependency is the
-// only ordering the compiler sees).
+// Ring read. Not volatile, so that the instruction scheduler may move it; `token` is a value produced by the last
+// cp.async wait, which keeps the read after that wait (the data dependency is the only ordering the compiler sees).
 __device__ __forceinline__ uint32_t lds32(uint32_t addr, uint32_t token) {
     uint32_t v;
     asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr), "r"(token));
@@ -47,6 +62,11 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr, uint32_t token) {
 __device__ __forceinline__ uint32_t lds32_ro(uint32_t addr) { // table reads: never written after the block barrier
     uint32_t v;
     asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 lds128_ro(uint32_t addr) {
+    uint4 v;
+    asm("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
 __device__ __forceinline__ uint32_t shl_wrap_hi(uint32_t lo, uint32_t hi, uint32_t n) {
@@ -70,17 +90,43 @@ __device__ __forceinline__ uint32_t cp_async_wait_all() { // returns the token r
     return token;
 }
 
+// Tensor memory as a per-lane register file extension: lane l of a warp reads columns [col, col + 4) of TMEM lane
+// 32 * (warp % 4) + l.
+__device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t cols) { // cols: a power of two, 32..512
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_free(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_st4(uint32_t addr, const uint4 & v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld4(uint32_t addr, uint4 & v) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+}
+// the loaded registers are operands of the wait, so no use of them can be scheduled above it
+__device__ __forceinline__ void tmem_ld_wait(uint4 & v) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w) :: "memory");
+}
+__device__ __forceinline__ void tmem_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
 // One lane stream read through the lane's ring. Offsets are bytes from `base` (the unit's stream start rounded down to
-// 16 bytes); only their low 7 bits address the ring.
+// 16 bytes); only their low 7 bits address the ring. The stream is seen through a window of three consecutive words
+// (hi, lo, ahead) and a bit offset `o` into hi whose low five bits position the view and whose bit 5 toggles when the
+// offset passes a word. Only bits 0..5 of `o` are meaningful (table entries carry their length in the low bits and
+// exponents above), which is all the funnel shifts and the word-crossing test read.
 struct RingReader {
     const uint8_t * base; // global
     uint32_t key;         // ring base | lane swizzle
     uint32_t fetched;     // offset of the next granule to copy
     uint32_t next;        // offset of the next word to read
-    uint32_t hi, lo, ahead, v, t;
+    uint32_t hi, lo, ahead, o;
     uint32_t token;       // from the last cp.async wait
 
-    // copy granules until more than RING_TARGET bytes are ahead of the read pointer (at most `rounds` granules)
+    // copy granules until more than RING_TARGET bytes are ahead of the read pointer (at most ROUNDS granules)
     template <int ROUNDS>
     __device__ __forceinline__ void top_up(const Opaque & k) {
         int32_t avail = (int32_t) imad(next, k.minus_one, fetched); // negative right after open()
@@ -102,27 +148,23 @@ struct RingReader {
     }
     __device__ __forceinline__ void first_words() {
         hi = lds32(ring_addr(next, key), token);
-        ahead = lds32(ring_addr(next + 4, key), token);
-        next += 8; lo = 0; v = 32; t = 0;
+        lo = lds32(ring_addr(next + 4, key), token);
+        ahead = lds32(ring_addr(next + 8, key), token);
+        next += 12; o = 0;
     }
+    // two codes: their table entries. `lut`: this lane's copy of the table (entries 16 bytes apart)
     __device__ __forceinline__ void take2(uint32_t lut, const Opaque & k, uint32_t & e0, uint32_t & e1) {
-        v = imad(t, k.minus_one, v);
-        const uint32_t place = __funnelshift_r(0u, 1u, v);
-        if (!(v & 32u)) {
-            uint64_t b;
-            asm("mov.b64 %0, {%1, %2};" : "=l"(b) : "r"(lo), "r"(hi));
-            asm("mad.wide.u32 %0, %1, %2, %0;" : "+l"(b) : "r"(ahead), "r"(place));
-            asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(b));
+        const uint32_t v1 = shl_wrap_hi(lo, hi, o);          // 32 valid bits from the offset on: two codes are at most 24
+        e0 = lds32_ro(imad(v1 >> (32 - HP_LMAX), k.sixteen, lut));
+        const uint32_t v2 = shl_wrap_hi(0u, v1, e0);
+        e1 = lds32_ro(imad(v2 >> (32 - HP_LMAX), k.sixteen, lut));
+        const uint32_t o2 = o + e0 + e1;
+        if ((o ^ o2) & 32u) {                                // the offset passed a word: slide the window
+            hi = lo; lo = ahead;
             ahead = lds32(ring_addr(next, key), token);
             next = imad(k.four, k.one, next);
-            v = imad(k.thirty_two, k.one, v);
         }
-        e0 = lds32_ro(imad(hi >> (32 - HP_LMAX), k.four, lut));
-        const uint32_t second = shl_wrap_hi(lo, hi, e0);
-        e1 = lds32_ro(imad(second >> (32 - HP_LMAX), k.four, lut));
-        t = imad(e0, k.one, e1);
-        hi = shl_wrap_hi(lo, hi, t);
-        lo = shl_wrap_hi(0u, lo, t);
+        o = o2;
     }
 };
 
@@ -134,31 +176,70 @@ __device__ __forceinline__ void fma_bf16x2(uint32_t w, uint32_t x, float & lo, f
         "fma.rn.f32.bf16 %1, wh, xh, %1; }"
         : "+f"(lo), "+f"(hi) : "r"(w), "r"(x));
 }
-__device__ __forceinline__ uint2 lds64_ro(uint32_t addr) {
-    uint2 v;
-    asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-    return v;
+
+constexpr bool XF32 = RV_XF32 != 0;  // activations widened to FP32 in tensor memory (plain fma) or kept as BF16 pairs (mixed fma)
+__host__ __device__ constexpr int tmem_cols(int C, int NC) { // per lane: 8 C words of BF16 pairs (16 C as FP32) per column, rounded up to a power of two >= 32
+    int need = NC * C * (XF32 ? 16 : 8), cols = 32;
+    while (cols < need) { cols *= 2; }
+    return cols;
 }
 
-// One unit per warp, as many warps as the register file allows: the activations live in shared memory (BF16, natural
-// order: lane l's four activations of column quad j of chunk c are the 8 bytes at ((c*4 + j)*32 + l)*8, so every read
-// is base + immediate and conflict-free) and the plane is prefetched one row ahead chunk by chunk.
-template <int C, int NT, bool PEERS = false> // PEERS: the output also goes to the other GPUs (a separate instantiation: the plain kernel carries none of it)
+// One unit per warp. NC dense columns share the decode (NC = 1 also serves routed columns: blockIdx.y picks the column).
+template <int C, int NT, int NC, bool PEERS = false> // PEERS: the output also goes to the other GPUs (a separate instantiation: the plain kernel carries none of it)
 __global__ void __launch_bounds__(NT, 1) k_pair_gemv_rings(const PairView w, int R, Cols p, const Opaque k) {
     constexpr int K = C * CHUNK;
+    constexpr int XW = C * (XF32 ? 16 : 8);   // TMEM words per column and lane
+    constexpr int STEP = XF32 ? 2 : 4;        // codes served by one four-word TMEM load
+    constexpr int STEPS = 8 * C / STEP * NC;  // loads per row
+    constexpr uint32_t TCOLS = tmem_cols(C, NC);
     extern __shared__ __align__(128) unsigned char smem[];
-    uint32_t * lut = (uint32_t *) smem; // 16 KB table | K BF16 activations | one 4 KB ring set per warp
+    __shared__ uint32_t tmem_slot;
+    uint32_t * lut = (uint32_t *) smem; // four interleaved tables | NC x K BF16 activations | one 4 KB ring set per warp
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     const uint32_t lut_s = smem_u32(lut);
-    const uint32_t xs = lut_s + 4 * HP_MAX_PAIRS + lane * 8;
+    const uint32_t lut_l = lut_s + (lane & 3) * 4;
+    const uint32_t xs = lut_s + LUT_BYTES + lane * 16;
     // ring of lane l: 128 bytes at l * 128; granule index XOR (l & 7) spreads lanes that read in step over the banks
-    const uint32_t key = (lut_s + 4 * HP_MAX_PAIRS + 2 * K + (uint32_t) warp * (32 * RING_BYTES) + lane * RING_BYTES) | ((lane & 7) << 4);
+    const uint32_t key = (lut_s + LUT_BYTES + NC * 2 * K + (uint32_t) warp * (32 * RING_BYTES) + lane * RING_BYTES) | ((lane & 7) << 4);
 
     const bf16 * xg; OutVec out; int64_t rbase;
-    column<bf16>(p, blockIdx.y, xg, out, rbase);
-    for (int i = threadIdx.x; i < HP_MAX_PAIRS / 4; i += blockDim.x) { ((uint4 *) lut)[i] = __ldg((const uint4 *) w.lut + i); }
-    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) { ((uint4 *) (smem + 4 * HP_MAX_PAIRS))[i] = __ldg((const uint4 *) xg + i); }
+    column<bf16>(p, NC == 1 ? blockIdx.y : 0, xg, out, rbase);
+    if (warp == 0) { tmem_alloc(smem_u32(&tmem_slot), TCOLS); }
+    for (int i = threadIdx.x; i < HP_MAX_PAIRS; i += blockDim.x) { const uint32_t e = __ldg(w.lut + i); ((uint4 *) lut)[i] = make_uint4(e, e, e, e); }
+    // 16 bytes per (column n, chunk c, half h, lane l): the lane's activations of column quads 2h and 2h+1 of the chunk
+    for (int i = threadIdx.x; i < NC * (K / 4); i += blockDim.x) {
+        const int n = i / (K / 4), r = i - n * (K / 4);
+        const int c = r >> 7, j = (r >> 5) & 3, l = r & 31; // quad j of chunk c, lane l: columns c*512 + 128*j + 4*l + {0..3}
+        const uint2 v = __ldg((const uint2 *) ((const char *) xg + n * p.x_tok) + (c * CHUNK + 128 * j + 4 * l) / 4);
+        *(uint2 *) (smem + LUT_BYTES + n * 2 * K + ((c * 2 + (j >> 1)) * 32 + l) * 16 + (j & 1) * 8) = v;
+    }
+    tmem_fence_before();
     __syncthreads();
+    tmem_fence_after();
+    // activations into tensor memory: warps 0..3 fill the four lane quarters (a warp reads the quarter warp % 4)
+    const uint32_t tmem_base = tmem_slot;
+    const uint32_t tmem_x = tmem_base + ((uint32_t) (warp & 3) << 21); // lane field (bits 16 and up): 32 * (warp % 4)
+    if (warp < 4) {
+#pragma unroll
+        for (int i = 0; i < NC * 2 * C; i++) {
+            const uint4 v = lds128_ro(xs + i * 512);
+            if (XF32) {
+                tmem_st4(tmem_x + 8 * i, make_uint4(v.x << 16, v.x & 0xFFFF0000u, v.y << 16, v.y & 0xFFFF0000u));
+                tmem_st4(tmem_x + 8 * i + 4, make_uint4(v.z << 16, v.z & 0xFFFF0000u, v.w << 16, v.w & 0xFFFF0000u));
+            } else {
+                tmem_st4(tmem_x + 4 * i, v);
+            }
+        }
+        tmem_st_wait();
+    }
+    tmem_fence_before();
+    __syncthreads();
+    tmem_fence_after();
+
+    // step s of a row = (group of STEP codes, column n): its four words are at column n * XW + 4 * (group index)
+    auto x_addr = [&](int s) { return tmem_x + (s % NC) * XW + 4 * (s / NC); };
+    uint4 xa, xb = make_uint4(0, 0, 0, 0);
+    tmem_ld4(x_addr(0), xa);
 
     const int64_t units = p.nrows / R;
     for (int64_t u = (int64_t) blockIdx.x * nwarp + warp; u < units; u += (int64_t) gridDim.x * nwarp) {
@@ -175,14 +256,18 @@ __global__ void __launch_bounds__(NT, 1) k_pair_gemv_rings(const PairView w, int
         for (int c = 0; c < C; c++) { nx[c] = ld_stream16(pl + c * CHUNK); }
         rd.token = cp_async_wait_all();
         rd.first_words();
-        float mine = 0.f;
+        float mine[NC];
+#pragma unroll
+        for (int n = 0; n < NC; n++) { mine[n] = 0.f; }
         for (int rr = 0; rr < R; rr++) {
             if (rr) {
                 rd.token = cp_async_wait_all(); // copies issued one row ago
                 rd.template top_up<3>(k);
                 cp_async_commit();
             }
-            float a[4] = {0.f, 0.f, 0.f, 0.f};
+            float a[NC][4];
+#pragma unroll
+            for (int n = 0; n < NC; n++) { a[n][0] = a[n][1] = a[n][2] = a[n][3] = 0.f; }
             const uint8_t * nrow = pl + (rr + 1 < R ? rr + 1 : rr) * K;
 #pragma unroll
             for (int c = 0; c < C; c++) {
@@ -192,44 +277,91 @@ __global__ void __launch_bounds__(NT, 1) k_pair_gemv_rings(const PairView w, int
 #pragma unroll
                 for (int half = 0; half < 2; half++) {
                     uint32_t e[4];
-                    rd.take2(lut_s, k, e[0], e[1]);
-                    rd.take2(lut_s, k, e[2], e[3]);
+                    rd.take2(lut_l, k, e[0], e[1]);
+                    rd.take2(lut_l, k, e[2], e[3]);
+                    uint32_t wv[4]; // BF16 pairs: columns {0, 1} and {2, 3} of quads 2 half and 2 half + 1
 #pragma unroll
                     for (int jj = 0; jj < 2; jj++) {
-                        const int j = 2 * half + jj;
-                        const uint2 xq = lds64_ro(xs + (c * 4 + j) * 256);
-                        fma_bf16x2(merge_sm_exp(spread_lo(pw[j]), e[2 * jj]), xq.x, a[0], a[1]);
-                        fma_bf16x2(merge_sm_exp(spread_hi(pw[j]), e[2 * jj + 1]), xq.y, a[2], a[3]);
+                        wv[2 * jj] = merge_sm_exp(spread_lo(pw[2 * half + jj]), e[2 * jj]);
+                        wv[2 * jj + 1] = merge_sm_exp(spread_hi(pw[2 * half + jj]), e[2 * jj + 1]);
+                    }
+                    if (XF32) {
+                        float wf[8];
+#pragma unroll
+                        for (int i = 0; i < 4; i++) { wf[2 * i] = bf16lo_f32(wv[i]); wf[2 * i + 1] = bf16hi_f32(wv[i]); }
+#pragma unroll
+                        for (int jj = 0; jj < 2; jj++) {
+#pragma unroll
+                            for (int n = 0; n < NC; n++) {
+                                const int s = ((c * 2 + half) * 2 + jj) * NC + n;
+                                uint4 & cur = (s & 1) ? xb : xa;
+                                uint4 & nxt = (s & 1) ? xa : xb;
+                                tmem_ld_wait(cur);
+                                tmem_ld4(x_addr((s + 1) % STEPS), nxt);
+                                a[n][0] = fmaf(wf[4 * jj], __uint_as_float(cur.x), a[n][0]);
+                                a[n][1] = fmaf(wf[4 * jj + 1], __uint_as_float(cur.y), a[n][1]);
+                                a[n][2] = fmaf(wf[4 * jj + 2], __uint_as_float(cur.z), a[n][2]);
+                                a[n][3] = fmaf(wf[4 * jj + 3], __uint_as_float(cur.w), a[n][3]);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int n = 0; n < NC; n++) { // two register sets in turn: wait for this step's, start the next step's load, use this one
+                            const int s = (c * 2 + half) * NC + n;
+                            uint4 & cur = (s & 1) ? xb : xa;
+                            uint4 & nxt = (s & 1) ? xa : xb;
+                            tmem_ld_wait(cur);
+                            tmem_ld4(x_addr((s + 1) % STEPS), nxt);
+                            fma_bf16x2(wv[0], cur.x, a[n][0], a[n][1]);
+                            fma_bf16x2(wv[1], cur.y, a[n][2], a[n][3]);
+                            fma_bf16x2(wv[2], cur.z, a[n][0], a[n][1]);
+                            fma_bf16x2(wv[3], cur.w, a[n][2], a[n][3]);
+                        }
                     }
                 }
             }
-            const float s = warp_sum((a[0] + a[1]) + (a[2] + a[3]));
-            if (lane == rr) { mine = s; }
+#pragma unroll
+            for (int n = 0; n < NC; n++) {
+                const float s = warp_sum((a[n][0] + a[n][1]) + (a[n][2] + a[n][3]));
+                if (lane == rr) { mine[n] = s; }
+            }
         }
         if (lane < R) {
-            out.put(u * R + lane, mine);
-            if (PEERS) { peers_put(p, blockIdx.y, u * R + lane, mine); }
+#pragma unroll
+            for (int n = 0; n < NC; n++) {
+                const OutVec o = {out.p + n * p.y_tok, out.bf16};
+                o.put(u * R + lane, mine[n]);
+                if (PEERS) { peers_put(p, (NC == 1 ? (int) blockIdx.y : 0) + n, u * R + lane, mine[n]); }
+            }
         }
     }
+    tmem_ld_wait(xa);
+    tmem_fence_before();
+    __syncthreads();
+    if (warp == 0) { tmem_free(tmem_base, TCOLS); }
     if (PEERS) { peers_done(p); }
 }
 
 constexpr int RING_SET = 32 * RING_BYTES;
-int fixed_smem(int64_t K) { return 4 * HP_MAX_PAIRS + 2 * (int) K; }
+int fixed_smem(int64_t K, int nc) { return LUT_BYTES + nc * 2 * (int) K; }
 
 } // namespace
 
-static int g_warps = 28; // most warps per block; BF16N_RINGS_WARPS overrides it (0: off, the bulk-copy kernel takes over)
+static int g_warps = RV_WARPS; // most warps per block
+
+// (chunks, threads per block the register budget is set for, columns per decode)
+#define RINGS_FOR_EACH(X) X(1, 896, 1) X(2, 896, 1) X(4, 896, 1) X(4, 768, 1) X(4, 768, 2) X(4, 640, 4) X(2, 768, 2) X(2, 640, 4) X(1, 768, 2) X(1, 640, 4)
 
 void gemv_rings_init() {
     const int optin = device_info().smem_optin;
-#define ATTR(KERNEL) cuda_ok(cudaFuncSetAttribute(KERNEL, cudaFuncAttributeMaxDynamicSharedMemorySize, optin), #KERNEL)
-    ATTR((k_pair_gemv_rings<1, 896>)); ATTR((k_pair_gemv_rings<2, 896>)); ATTR((k_pair_gemv_rings<4, 896>));
-    ATTR((k_pair_gemv_rings<4, 768>)); ATTR((k_pair_gemv_rings<4, 1024>));
-    ATTR((k_pair_gemv_rings<1, 896, true>)); ATTR((k_pair_gemv_rings<2, 896, true>)); ATTR((k_pair_gemv_rings<4, 896, true>));
-    ATTR((k_pair_gemv_rings<4, 768, true>)); ATTR((k_pair_gemv_rings<4, 1024, true>));
+    auto allow = [optin](const void * kernel) { // the opt-in limit covers static and dynamic shared memory together
+        cudaFuncAttributes fa;
+        cuda_ok(cudaFuncGetAttributes(&fa, kernel), "rings attributes");
+        cuda_ok(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, optin - (int) fa.sharedSizeBytes), "rings shared memory");
+    };
+#define ATTR(CC, NT, NC) allow((const void *) k_pair_gemv_rings<CC, NT, NC>); allow((const void *) k_pair_gemv_rings<CC, NT, NC, true>);
+    RINGS_FOR_EACH(ATTR)
 #undef ATTR
-    if (const char * e = getenv("BF16N_RINGS_WARPS")) { g_warps = atoi(e); }
 }
 
 bool gemv_rings_enabled() { return g_warps > 0; }
@@ -238,31 +370,55 @@ bool gemv_rings_enabled() { return g_warps > 0; }
 bool gemv_rings_applies(const bf16n_weight & w, const bf16n_mmv_args & a) {
     const int64_t C = w.K / CHUNK;
     if (w.format != FMT_HUFPAIR || w.cm || w.fo || !(C == 1 || C == 2 || C == 4) || a.nrows <= 0 || !a.x_bf16) { return false; }
-    return a.nrows / w.R >= (int64_t) device_info().sms * 16 * std::max(1, a.ncols);
+    const int groups = a.ids ? a.ncols : (a.ncols + 3) / 4; // dense columns share a decode four at a time
+    return a.nrows / w.R >= (int64_t) device_info().sms * 16 * std::max(1, groups);
 }
 
-void gemv_rings(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st, const bf16n_peer_out * peers) {
-    const Cols p = make_cols(a, peers);
-    const int64_t units = a.nrows / w.R, sms = device_info().sms;
-    const int max_warps = std::min(g_warps, w.K == 2048 ? 32 : 28);
+namespace {
+
+// nc dense columns starting at p.x / p.y (nc = 1: also `ncols_grid` routed or dense columns, one decode each)
+void launch_rings(const bf16n_weight & w, const Cols & p, int nc, int ncols_grid, cudaStream_t st) {
+    const int64_t units = p.nrows / w.R, sms = device_info().sms;
+    const int cap = nc == 1 ? (w.K == 2048 ? g_warps : std::min(g_warps, 28)) : nc == 2 ? std::min(g_warps, 24) : std::min(g_warps, 20);
+    const int max_warps = std::max(4, cap);
     int best = max_warps;
     double best_eff = 0.0;
-    for (int nw = max_warps; nw >= max_warps - 3; nw--) { // static round-robin: waste least of the last round
+    for (int nw = max_warps; nw >= std::max(4, max_warps - 3); nw--) { // static round-robin: waste least of the last round
         const int64_t slots = sms * nw, rounds = (units + slots - 1) / slots;
         const double eff = (double) units / (double) (rounds * slots) * (1.0 - 0.01 * (max_warps - nw));
         if (eff > best_eff + 1e-9) { best_eff = eff; best = nw; }
     }
-    const dim3 grid((unsigned) sms, (unsigned) a.ncols);
-    const size_t shm = fixed_smem(w.K) + (size_t) best * RING_SET;
+    const dim3 grid((unsigned) sms, (unsigned) ncols_grid);
+    const size_t shm = fixed_smem(w.K, nc) + (size_t) best * RING_SET;
     const Opaque k = {1u, 4u, ~0u, 32u, 16u};
     const PairView v = pair_view(w);
-#define GO(CC, NT) if (p.peers.n) { k_pair_gemv_rings<CC, NT, true><<<grid, best * 32, shm, st>>>(v, w.R, p, k); } \
-                   else { k_pair_gemv_rings<CC, NT, false><<<grid, best * 32, shm, st>>>(v, w.R, p, k); }
-    if (w.K == 2048 && best > 28) { GO(4, 1024); }
-    else if (w.K == 2048 && best <= 24) { GO(4, 768); }
-    else { switch (w.K / CHUNK) { case 1: GO(1, 896); break; case 2: GO(2, 896); break; default: GO(4, 896); break; } }
+#define GO(CC, NT, NC) if (p.peers.n) { k_pair_gemv_rings<CC, NT, NC, true><<<grid, best * 32, shm, st>>>(v, w.R, p, k); } \
+                       else { k_pair_gemv_rings<CC, NT, NC, false><<<grid, best * 32, shm, st>>>(v, w.R, p, k); }
+    const int C = (int) (w.K / CHUNK);
+    if (nc == 4) { switch (C) { case 1: GO(1, 640, 4); break; case 2: GO(2, 640, 4); break; default: GO(4, 640, 4); break; } }
+    else if (nc == 2) { switch (C) { case 1: GO(1, 768, 2); break; case 2: GO(2, 768, 2); break; default: GO(4, 768, 2); break; } }
+    else if (C == 4 && best <= 24) { GO(4, 768, 1); }
+    else { switch (C) { case 1: GO(1, 896, 1); break; case 2: GO(2, 896, 1); break; default: GO(4, 896, 1); break; } }
 #undef GO
     check_launch();
+}
+
+} // namespace
+
+void gemv_rings(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st, bool multi_col, const bf16n_peer_out * peers) {
+    const Cols p = make_cols(a, peers);
+    if (a.ids || a.ncols == 1 || !multi_col || (peers && peers->n_peers > 0)) { // one decode per column
+        launch_rings(w, p, 1, a.ncols, st);
+        return;
+    }
+    for (int c0 = 0; c0 < a.ncols;) { // dense columns: four, two or one per decode
+        const int left = a.ncols - c0, nc = left >= 4 ? 4 : left >= 2 ? 2 : 1;
+        Cols q = p;
+        q.x += c0 * p.x_tok;
+        q.y += c0 * p.y_tok;
+        launch_rings(w, q, nc, 1, st);
+        c0 += nc;
+    }
 }
 
 } // namespace b16

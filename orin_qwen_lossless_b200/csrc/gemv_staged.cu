@@ -78,6 +78,7 @@ __global__ void __launch_bounds__(512, 1) k_pair_gemv_staged(const PairView w, c
     __syncthreads();
 
     uint32_t parity = 0;
+    bool dead = false; // a bulk copy of this warp never arrived: no further copies, NaN outputs
     const int64_t units = p.nrows / R, stride = (int64_t) gridDim.x * nwarp;
     // stream geometry of a unit: first word rounded down to 16 bytes, bytes to stage (with look-ahead words: the stream
     // is padded), this lane's first word inside the staged block
@@ -97,7 +98,7 @@ __global__ void __launch_bounds__(512, 1) k_pair_gemv_staged(const PairView w, c
     for (; u < units; u += stride) {
         const int64_t gu = rbase / R + u;
         const uint8_t * pl = w.plane + gu * R * (C * CHUNK) + 16 * lane;
-        const bool staged = cur.bytes <= cap_bytes;
+        const bool staged = !dead && cur.bytes <= cap_bytes;
         if (staged) {
             __syncwarp(); // every lane is done with the previous unit's words
             if (lane == 0) {
@@ -114,13 +115,18 @@ __global__ void __launch_bounds__(512, 1) k_pair_gemv_staged(const PairView w, c
             if (lane == 0) { bulk_prefetch_l2(w.stream + nxt.start, nxt.bytes); }
             if (lane < PLANE_AHEAD * C * CHUNK / 128) { prefetch_l2(w.plane + gn * R * (C * CHUNK) + 128 * lane); }
         }
-        float mine;
+        float mine = __int_as_float(0x7fc00000);
+        uint32_t landed = 0;
         if (staged) {
-            const uint32_t landed = mbar_wait(bar, parity);
-            if (!landed) {
+            landed = mbar_wait(bar, parity);
+            if (!landed) { // the copy never arrived: report it; this unit and the warp's later units are written as NaN
                 if (lane == 0) { atomicOr(&g_wait_expired, 1u); }
-                return;
+                dead = true;
             }
+        }
+        if (dead) {
+            // nothing to compute; the block still reaches its end (and, with peers, its announcement)
+        } else if (staged) {
             parity ^= 1u;
             StagedReader rd;
             rd.open(smem_u32(buf) + 4 * cur.my, landed);
@@ -147,6 +153,8 @@ uint32_t buffer_bytes(const bf16n_weight & w) { return (uint32_t) ((w.R * w.K * 
 
 } // namespace
 
+BF16N_DEFINE_FAULT_WORD(gemv_staged_fault_word)
+
 void gemv_staged_init() {
     const int optin = device_info().smem_optin;
 #define ATTR(KERNEL) cuda_ok(cudaFuncSetAttribute(KERNEL, cudaFuncAttributeMaxDynamicSharedMemorySize, optin), #KERNEL)
@@ -165,7 +173,7 @@ bool gemv_staged_applies(const bf16n_weight & w, const bf16n_mmv_args & a) {
     const int64_t room = (device_info().smem_optin - FIXED_SMEM) / buffer_bytes(w);
     // from 256 units on: below 8 units per SM the kernel still pays, because a warp that reads its lane streams straight
     // from global memory stalls on every lane's cache line at a different moment (8192 x 2048, R = 16: 43 -> 16 us)
-    static const int64_t min_units = getenv("BF16N_STAGED_MIN_UNITS") ? atoll(getenv("BF16N_STAGED_MIN_UNITS")) : 256;
+    constexpr int64_t min_units = 256;
     return room >= 8 && units >= min_units * std::max(1, a.ncols);
 }
 

@@ -56,6 +56,12 @@ void expand_compare(const bf16n_weight & w, int64_t row0, int64_t nrows, const u
 void gather_rows(const bf16n_weight & w, const void * ids, int64_t ids_s0, int64_t n, void * dst, bool dst_bf16, int64_t dst_s1,
                  int64_t row0, cudaStream_t st);
 
+// device addresses of the words the kernels set when one of their bounded waits runs out (bf16n_fault_status)
+unsigned int * gemv_staged_fault_word();
+unsigned int * moe_decode_fault_word();
+unsigned int * fo_fault_word();
+unsigned int * prefill_fault_word();
+
 // gemv_staged.cu
 void gemv_staged_init();
 bool gemv_staged_applies(const bf16n_weight & w, const bf16n_mmv_args & a);
@@ -65,7 +71,7 @@ void gemv_staged(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t 
 void gemv_rings_init();
 bool gemv_rings_enabled();
 bool gemv_rings_applies(const bf16n_weight & w, const bf16n_mmv_args & a);
-void gemv_rings(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st, const bf16n_peer_out * peers = nullptr);
+void gemv_rings(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st, bool multi_col, const bf16n_peer_out * peers = nullptr);
 
 // fo.cu: fragment-order HUFPAIR tensors
 void fo_init();

@@ -168,13 +168,14 @@ __global__ void __launch_bounds__(256) k_expert_units(const ExpertMat m0, const 
     float mine;
     if (staged) {
         const uint32_t landed = mbar_wait(bar, 0);
-        if (!landed) {
+        if (!landed) { // the copy never arrived: report it and leave NaN where the unit's rows go
             if (lane == 0) { atomicOr(&g_wait_expired, 1u); }
-            return;
+            mine = __int_as_float(0x7fc00000);
+        } else {
+            StagedReader rd;
+            rd.open(smem_u32(buf) + 4 * my, landed);
+            mine = rows(rd, smem_u32(lut));
         }
-        StagedReader rd;
-        rd.open(smem_u32(buf) + 4 * my, landed);
-        mine = rows(rd, smem_u32(lut));
     } else {
         GlobalReader rd;
         rd.lut = lut;
@@ -266,9 +267,10 @@ bool moe_decode_supported(const bf16n_weight & gate, const bf16n_weight & up, co
     return gate_shape_ok(gate) && gate_shape_ok(up) && down_shape_ok(down) && gate.rows == up.rows;
 }
 
+BF16N_DEFINE_FAULT_WORD(moe_decode_fault_word)
+
 void moe_decode_init() {
     // instantiate and set the shared-memory attribute of every variant outside of any stream capture
-    if (const char * e = getenv("BF16N_PLANE_STAGED_WARPS")) { g_plane_staged_warps_per_sm = atoi(e); } // tuning knob, read once
     ExpertMat none = {};
     ExpertCols p = {};
     p.rows_per_expert = 16; p.cap_bytes = 16;

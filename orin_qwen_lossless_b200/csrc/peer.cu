@@ -9,7 +9,7 @@ namespace {
 using namespace dev;
 
 // One thread per possible peer: spins (bounded) until that peer's epoch reaches the next one this rank waits for.
-__global__ void __launch_bounds__(32) k_peer_wait(uint32_t * hdr, int rank_mask) {
+__global__ void __launch_bounds__(32) k_peer_wait(uint32_t * hdr, int rank_mask, uint64_t limit_ns) {
     const int r = threadIdx.x;
     const uint32_t want = hdr[XH_WAITED] + 1u;
     bool ok = true;
@@ -23,7 +23,7 @@ __global__ void __launch_bounds__(32) k_peer_wait(uint32_t * hdr, int rank_mask)
             if ((i & 1023u) == 1023u) {
                 uint64_t now;
                 asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-                if (t0 == 0) { t0 = now; } else if (now - t0 > 2000000000ull) { break; }
+                if (t0 == 0) { t0 = now; } else if (now - t0 > limit_ns) { break; }
             }
         }
     }
@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(32) k_peer_wait(uint32_t * hdr, int rank_mask)
 } // namespace
 
 void peer_wait(uint32_t * local_header, int rank_mask, cudaStream_t st) {
-    k_peer_wait<<<1, 32, 0, st>>>(local_header, rank_mask);
+    k_peer_wait<<<1, 32, 0, st>>>(local_header, rank_mask, dev::peer_wait_limit_ns());
     check_launch();
 }
 

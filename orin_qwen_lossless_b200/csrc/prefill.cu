@@ -34,7 +34,7 @@ namespace {
 using namespace dev;
 using bf16 = __nv_bfloat16;
 
-__device__ unsigned int g_prefill_fault; // a bounded wait expired (diagnostic)
+__device__ unsigned int g_prefill_fault; // a bounded wait expired (bf16n_fault_status reads and clears it)
 
 constexpr int DEC_WARPS = 16, GATHER_WARPS = 3, GATHERERS = GATHER_WARPS * 32;
 constexpr int MMA_WARP = DEC_WARPS + GATHER_WARPS;   // the last warp
@@ -434,6 +434,12 @@ constexpr int G_TOK = 2;                      // token groups per pass
 constexpr int SLOTS_GLU = 3, SLOTS_ONE = 4;   // what fits beside two tables / one table
 
 } // namespace
+
+unsigned int * prefill_fault_word() {
+    unsigned int * p = nullptr;
+    cuda_ok(cudaGetSymbolAddress((void **) &p, g_prefill_fault), "fault word address");
+    return p;
+}
 
 void prefill_init() {
     cuda_ok(cudaFuncSetAttribute(k_prefill<4, 8, true, true, G_TOK, SLOTS_GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -10,7 +10,16 @@ namespace dev {
 
 using bf16 = __nv_bfloat16;
 
-static __device__ unsigned int g_wait_expired; // a bounded mbarrier wait ran out (diagnostic, one copy per translation unit)
+// Set when a bounded mbarrier wait ran out (one copy per translation unit; bf16n_fault_status reads and clears them).
+// The outputs of the work item whose wait expired are written as NaN.
+static __device__ unsigned int g_wait_expired;
+// defines `unsigned int * NAME()`: the device address of this translation unit's word (device current, outside capture)
+#define BF16N_DEFINE_FAULT_WORD(NAME)                                                           \
+    unsigned int * NAME() {                                                                     \
+        unsigned int * p = nullptr;                                                             \
+        cuda_ok(cudaGetSymbolAddress((void **) &p, dev::g_wait_expired), "fault word address"); \
+        return p;                                                                               \
+    }
 
 constexpr uint32_t WAIT_LIMIT = 1u << 20; // try_wait polls before a warp gives up on its bulk copy
 

@@ -209,6 +209,30 @@ def _check_ids(ids: torch.Tensor) -> None:
         raise RuntimeError("bf16n: ids must be contiguous along the slot dimension")
 
 
+def _check_out(out: torch.Tensor, shape: tuple, dtype: torch.dtype, device: torch.device, what: str) -> int:
+    """A caller-supplied output: the result's shape and dtype, on the weight's device (or pinned host memory, which is
+    mapped into the device's address space), last dimension contiguous, outer dimensions dense over the rows, 16-byte
+    aligned base and row stride. Returns the byte stride between rows of the first dimension."""
+    if tuple(out.shape) != tuple(shape) or out.dtype != dtype:
+        raise RuntimeError(f"bf16n.{what}: out must have shape {tuple(shape)} and dtype {dtype}, got {tuple(out.shape)} {out.dtype}")
+    if out.device.type == "cpu":
+        if not (out.is_pinned() and out.is_contiguous()):
+            raise RuntimeError(f"bf16n.{what}: a host output must be pinned and contiguous")
+    elif out.device != device:
+        raise RuntimeError(f"bf16n.{what}: out is on {out.device}, the weight on {device}")
+    if out.numel() and out.stride(-1) != 1:
+        raise RuntimeError(f"bf16n.{what}: out must be contiguous along its last dimension")
+    for d in range(1, out.dim() - 1):  # [tokens, slots, rows]: slots dense over the rows
+        if out.stride(d) != out.shape[d + 1] * out.stride(d + 1):
+            raise RuntimeError(f"bf16n.{what}: out must be dense below its first dimension")
+    row = out.stride(0) * out.element_size() if out.dim() > 1 else 0
+    if out.data_ptr() % 16 or row % 16:
+        raise RuntimeError(f"bf16n.{what}: out and its row stride must be 16-byte aligned")
+    if out.dim() > 1 and out.shape[0] > 1 and out.stride(0) < out.numel() // out.shape[0]:
+        raise RuntimeError(f"bf16n.{what}: rows of out overlap")
+    return row
+
+
 def _mmv_common(x, w: Weight, ids, rows_per_matrix: int, out_bf16: bool, glu: bool, multi_col: bool = True,
                 out: torch.Tensor | None = None) -> torch.Tensor:
     cw = w.c()
@@ -229,14 +253,11 @@ def _mmv_common(x, w: Weight, ids, rows_per_matrix: int, out_bf16: bool, glu: bo
         n_out = rpm // 2 if glu else rpm
         T = x.shape[0]
         y = torch.empty((T, n_out), dtype=odt, device=w.plane.device) if out is None else out
-        if out is not None and out.device.type == "cpu":
-            # pinned host memory is mapped into the device's address space: the kernel stores its results there itself
-            if not (out.is_pinned() and out.is_contiguous() and out.dtype == odt and tuple(out.shape) == (T, n_out)):
-                raise RuntimeError("bf16n.mmv: a host output must be pinned, contiguous and of the result's shape and dtype")
+        y_row = n_out * osz if out is None else _check_out(out, (T, n_out), odt, w.plane.device, "mmv")
         if T == 0:
             return y
         a.y, a.ncols = y.data_ptr(), T
-        a.x_tok, a.y_tok = x.stride(0) * x.element_size(), n_out * osz
+        a.x_tok, a.y_tok = x.stride(0) * x.element_size(), y_row
         a.n_used, a.x_per_slot = 1, 1
         a.rows_per_matrix, a.nrows = rpm, n_out
     else:
@@ -251,7 +272,8 @@ def _mmv_common(x, w: Weight, ids, rows_per_matrix: int, out_bf16: bool, glu: bo
         n_out = rows_per_matrix // 2 if glu else rows_per_matrix
         if not ((x.dim() == 2 and x.shape[0] == T) or (x.dim() == 3 and x.shape[0] == T and x.shape[1] == n_used)):
             raise RuntimeError("bf16n.mmv: x must be [tokens, K] or [tokens, n_used, K]")
-        y = torch.empty((T, n_used, n_out), dtype=odt, device=x.device) if out is None else out
+        y = torch.empty((T, n_used, n_out), dtype=odt, device=w.plane.device) if out is None else out
+        y_tok = n_used * n_out * osz if out is None else _check_out(out, (T, n_used, n_out), odt, w.plane.device, "mmv")
         if T == 0 or n_used == 0:
             return y
         a.y, a.ncols = y.data_ptr(), T * n_used
@@ -260,7 +282,7 @@ def _mmv_common(x, w: Weight, ids, rows_per_matrix: int, out_bf16: bool, glu: bo
         a.x_tok = x.stride(0) * x.element_size()
         a.x_per_slot = n_used if x.dim() == 3 else 1
         a.x_slot = x.stride(1) * x.element_size() if x.dim() == 3 else 0
-        a.y_tok, a.y_slot = n_used * n_out * osz, n_out * osz
+        a.y_tok, a.y_slot = y_tok, n_out * osz
         a.rows_per_matrix, a.nrows = rows_per_matrix, n_out
     with torch.cuda.device(w.plane.device):
         if glu:
@@ -520,7 +542,18 @@ def moe_decode(x: torch.Tensor, gate: Weight, up: Weight, down: Weight, n_expert
         raise RuntimeError("bf16n.moe_decode: topk_ids int32 / topk_weights f32, contiguous [tokens, top_k]")
     if scratch is None:
         scratch = moe_decode_scratch(T, top_k, gate, down, n_local, dev)
-    y = torch.empty((T, H), dtype=out_dtype, device=dev) if out is None else out
+    elif not (scratch.is_cuda and scratch.device == dev and scratch.dtype == torch.float32 and scratch.is_contiguous()):
+        raise RuntimeError("bf16n.moe_decode: scratch must be a contiguous f32 CUDA tensor on the weights' device")
+    if topk_ids.device != dev or topk_weights.device != dev or tuple(topk_ids.shape) != (T, top_k) or tuple(topk_weights.shape) != (T, top_k):
+        raise RuntimeError("bf16n.moe_decode: topk_ids / topk_weights must be [tokens, top_k] on the weights' device")
+    if out is None:
+        y = torch.empty((T, H), dtype=out_dtype, device=dev)
+    else:
+        y = out
+        if _check_out(out, (T, H), out.dtype, dev, "moe_decode") != H * out.element_size() and T > 1:
+            raise RuntimeError("bf16n.moe_decode: out must be contiguous")
+        if out.dtype not in (torch.float32, torch.bfloat16) or out.device.type != "cuda":
+            raise RuntimeError("bf16n.moe_decode: out must be an f32 or bf16 CUDA tensor")
     args = (C.byref(cg), C.byref(cu), C.byref(cd), x.data_ptr(), int(x.dtype == torch.bfloat16), x.stride(0) * x.element_size(),
             router_logits.data_ptr() if router_logits is not None else None, n_experts, topk_ids.data_ptr(), topk_weights.data_ptr(),
             T, top_k, expert_lo, n_local, scratch.data_ptr(), scratch.numel() * 4, y.data_ptr(), int(y.dtype == torch.bfloat16))
