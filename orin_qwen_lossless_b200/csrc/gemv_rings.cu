@@ -26,12 +26,6 @@
 #include "decode.cuh"
 #include "launch.h"
 
-#ifndef RV_WARPS
-#define RV_WARPS 28
-#endif
-#ifndef RV_XF32
-#define RV_XF32 0
-#endif
 
 namespace b16 {
 namespace {
@@ -177,9 +171,11 @@ __device__ __forceinline__ void fma_bf16x2(uint32_t w, uint32_t x, float & lo, f
         : "+f"(lo), "+f"(hi) : "r"(w), "r"(x));
 }
 
-constexpr bool XF32 = RV_XF32 != 0;  // activations widened to FP32 in tensor memory (plain fma) or kept as BF16 pairs (mixed fma)
-__host__ __device__ constexpr int tmem_cols(int C, int NC) { // per lane: 8 C words of BF16 pairs (16 C as FP32) per column, rounded up to a power of two >= 32
-    int need = NC * C * (XF32 ? 16 : 8), cols = 32;
+// Measured alternatives that lost (248320 x 2048, one column, 174 us as built): activations widened to FP32 in tensor
+// memory with plain fma 183 us (three more instructions per pair of weights); 32 warps of 64 registers 192 us; plane
+// bytes prefetched two chunks ahead instead of a row 179 us; activations read from shared memory 184 us; one table 178 us.
+__host__ __device__ constexpr int tmem_cols(int C, int NC) { // per lane: 8 C words of BF16 pairs per column, rounded up to a power of two >= 32
+    int need = NC * C * 8, cols = 32;
     while (cols < need) { cols *= 2; }
     return cols;
 }
@@ -188,9 +184,8 @@ __host__ __device__ constexpr int tmem_cols(int C, int NC) { // per lane: 8 C wo
 template <int C, int NT, int NC, bool PEERS = false> // PEERS: the output also goes to the other GPUs (a separate instantiation: the plain kernel carries none of it)
 __global__ void __launch_bounds__(NT, 1) k_pair_gemv_rings(const PairView w, int R, Cols p, const Opaque k) {
     constexpr int K = C * CHUNK;
-    constexpr int XW = C * (XF32 ? 16 : 8);   // TMEM words per column and lane
-    constexpr int STEP = XF32 ? 2 : 4;        // codes served by one four-word TMEM load
-    constexpr int STEPS = 8 * C / STEP * NC;  // loads per row
+    constexpr int XW = C * 8;           // TMEM words per column and lane
+    constexpr int STEPS = 2 * C * NC;   // four-word TMEM loads per row: one per (half chunk, column)
     constexpr uint32_t TCOLS = tmem_cols(C, NC);
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ uint32_t tmem_slot;
@@ -222,13 +217,7 @@ __global__ void __launch_bounds__(NT, 1) k_pair_gemv_rings(const PairView w, int
     if (warp < 4) {
 #pragma unroll
         for (int i = 0; i < NC * 2 * C; i++) {
-            const uint4 v = lds128_ro(xs + i * 512);
-            if (XF32) {
-                tmem_st4(tmem_x + 8 * i, make_uint4(v.x << 16, v.x & 0xFFFF0000u, v.y << 16, v.y & 0xFFFF0000u));
-                tmem_st4(tmem_x + 8 * i + 4, make_uint4(v.z << 16, v.z & 0xFFFF0000u, v.w << 16, v.w & 0xFFFF0000u));
-            } else {
-                tmem_st4(tmem_x + 4 * i, v);
-            }
+            tmem_st4(tmem_x + 4 * i, lds128_ro(xs + i * 512));
         }
         tmem_st_wait();
     }
@@ -236,7 +225,7 @@ __global__ void __launch_bounds__(NT, 1) k_pair_gemv_rings(const PairView w, int
     __syncthreads();
     tmem_fence_after();
 
-    // step s of a row = (group of STEP codes, column n): its four words are at column n * XW + 4 * (group index)
+    // step s of a row = (half chunk, column n): its four words are at TMEM column n * XW + 4 * (half chunk index)
     auto x_addr = [&](int s) { return tmem_x + (s % NC) * XW + 4 * (s / NC); };
     uint4 xa, xb = make_uint4(0, 0, 0, 0);
     tmem_ld4(x_addr(0), xa);
@@ -251,7 +240,7 @@ __global__ void __launch_bounds__(NT, 1) k_pair_gemv_rings(const PairView w, int
         }
         cp_async_commit();
         const uint8_t * pl = w.plane + g * R * K + 16 * lane;
-        uint4 nx[C];
+        uint4 nx[C]; // plane bytes one row ahead of the decode
 #pragma unroll
         for (int c = 0; c < C; c++) { nx[c] = ld_stream16(pl + c * CHUNK); }
         rd.token = cp_async_wait_all();
@@ -285,38 +274,17 @@ __global__ void __launch_bounds__(NT, 1) k_pair_gemv_rings(const PairView w, int
                         wv[2 * jj] = merge_sm_exp(spread_lo(pw[2 * half + jj]), e[2 * jj]);
                         wv[2 * jj + 1] = merge_sm_exp(spread_hi(pw[2 * half + jj]), e[2 * jj + 1]);
                     }
-                    if (XF32) {
-                        float wf[8];
 #pragma unroll
-                        for (int i = 0; i < 4; i++) { wf[2 * i] = bf16lo_f32(wv[i]); wf[2 * i + 1] = bf16hi_f32(wv[i]); }
-#pragma unroll
-                        for (int jj = 0; jj < 2; jj++) {
-#pragma unroll
-                            for (int n = 0; n < NC; n++) {
-                                const int s = ((c * 2 + half) * 2 + jj) * NC + n;
-                                uint4 & cur = (s & 1) ? xb : xa;
-                                uint4 & nxt = (s & 1) ? xa : xb;
-                                tmem_ld_wait(cur);
-                                tmem_ld4(x_addr((s + 1) % STEPS), nxt);
-                                a[n][0] = fmaf(wf[4 * jj], __uint_as_float(cur.x), a[n][0]);
-                                a[n][1] = fmaf(wf[4 * jj + 1], __uint_as_float(cur.y), a[n][1]);
-                                a[n][2] = fmaf(wf[4 * jj + 2], __uint_as_float(cur.z), a[n][2]);
-                                a[n][3] = fmaf(wf[4 * jj + 3], __uint_as_float(cur.w), a[n][3]);
-                            }
-                        }
-                    } else {
-#pragma unroll
-                        for (int n = 0; n < NC; n++) { // two register sets in turn: wait for this step's, start the next step's load, use this one
-                            const int s = (c * 2 + half) * NC + n;
-                            uint4 & cur = (s & 1) ? xb : xa;
-                            uint4 & nxt = (s & 1) ? xa : xb;
-                            tmem_ld_wait(cur);
-                            tmem_ld4(x_addr((s + 1) % STEPS), nxt);
-                            fma_bf16x2(wv[0], cur.x, a[n][0], a[n][1]);
-                            fma_bf16x2(wv[1], cur.y, a[n][2], a[n][3]);
-                            fma_bf16x2(wv[2], cur.z, a[n][0], a[n][1]);
-                            fma_bf16x2(wv[3], cur.w, a[n][2], a[n][3]);
-                        }
+                    for (int n = 0; n < NC; n++) { // two register sets in turn: wait for this step's, start the next step's load, use this one
+                        const int s = (c * 2 + half) * NC + n;
+                        uint4 & cur = (s & 1) ? xb : xa;
+                        uint4 & nxt = (s & 1) ? xa : xb;
+                        tmem_ld_wait(cur);
+                        tmem_ld4(x_addr((s + 1) % STEPS), nxt);
+                        fma_bf16x2(wv[0], cur.x, a[n][0], a[n][1]);
+                        fma_bf16x2(wv[1], cur.y, a[n][2], a[n][3]);
+                        fma_bf16x2(wv[2], cur.z, a[n][0], a[n][1]);
+                        fma_bf16x2(wv[3], cur.w, a[n][2], a[n][3]);
                     }
                 }
             }
@@ -347,7 +315,7 @@ int fixed_smem(int64_t K, int nc) { return LUT_BYTES + nc * 2 * (int) K; }
 
 } // namespace
 
-static int g_warps = RV_WARPS; // most warps per block
+constexpr int g_warps = 28; // most warps per block (72 registers per thread)
 
 // (chunks, threads per block the register budget is set for, columns per decode)
 #define RINGS_FOR_EACH(X) X(1, 896, 1) X(2, 896, 1) X(4, 896, 1) X(4, 768, 1) X(4, 768, 2) X(4, 640, 4) X(2, 768, 2) X(2, 640, 4) X(1, 768, 2) X(1, 640, 4)
