@@ -1,20 +1,32 @@
-"""Benchmark of the BF16N hot path on B200: the vocabulary projection (lm_head) decode+GEMV.
+"""Benchmark of the BF16N hot path on B200: the vocabulary projection (lm_head) decode+GEMV, with the MoE layer and the
+small-matrix graph of the same metric carried in the same line.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-moe] [--no-cpu]
 
-Workload (the configuration the headline metric is quoted on): a 248320 x 2048 BF16 matrix, weights N(0, 0.02) rounded
-to BF16 (seeded, synthetic), pair-Huffman coded with R = 16 as the shape policy chooses, multiplied by one BF16 N(0,1)
-activation vector with FP32 accumulation and FP32 logits. With N > 1 ranks the rows are split into N shards (one
-process per GPU), each rank multiplies its shard and an NCCL all-gather assembles the logits.
+Workload of the headline number (the configuration the metric is quoted on): a 248320 x 2048 BF16 matrix, weights
+N(0, 0.02) rounded to BF16 (seeded, synthetic), pair-Huffman coded with R = 16 as the shape policy chooses, multiplied by
+one BF16 N(0,1) activation vector with FP32 accumulation and FP32 logits. With N > 1 ranks the rows are split into N
+shards (one process per GPU); each rank's GEMV kernel stores its logits into every GPU itself (no collective).
+
+A "block" is exactly --steps steps between barriers and device synchronisation, timed with CUDA events (max over
+ranks); at least 30 blocks and one second of them are run and the line reports their median, minimum and maximum. A
+shard smaller than 256 MB is multiplied from several copies at different addresses, used in turn, so that L2 cannot
+serve it (config.l2 says what was done).
 
 One JSON line on stdout (rank 0):
   value    GB/s of compressed bytes (plane + aux + x + y) per second with everything resident in HBM
-  e2e      the same through ops.linear_host: the activation comes from pinned host memory and the logits go back to it
-           inside the timed region, every step
+  e2e      the same with the activation in pinned host memory and the logits back in host memory every step (one GPU:
+           ops.linear_host; several: sharded.HostGatheredLinear, one host buffer shared by the ranks)
   roofline achieved / measured copy bandwidth for the GEMV kernel (one launch per step)
+  cublas_bf16_gemv_us   the stock BF16 GEMV of the same (uncompressed) shard on the same GPU
+  multi_token           the same matrix with 2 and 4 activation columns (one decode for all of them)
+  moe      the MoE layer: decode at 1 / 2 / 4 tokens and prefill at 2048 / 8192 tokens (expert-parallel over the ranks),
+           each with microseconds, bytes or flops, fraction of the roofline and a parity figure against the FP64 oracle
+  small_matrices        the graph of 144 NIBBLE GEMVs (one GPU)
   cpu_baseline  the CPU oracle's decode+GEMV on this box's host threads (bounded sample)
 `--impl reference` times the CPU arm only (the reference ships no CPU GEMV, so this is the oracle's port of its decoder
 and summation; the encoder timed beside it is the reference's own when oracle/_ref is present).
+`--workload small | moe_decode | moe_prefill | dense_mid` print those blocks on their own.
 """
 from __future__ import annotations
 
@@ -111,7 +123,10 @@ def measured_peak():
 CPU_SAMPLE_ROWS = 65536   # rows of the workload the CPU arm decodes and multiplies per pass (179 MB compressed)
 
 
-def cpu_arm(rows_sample: int, reps: int):
+METRIC = "lm_head_248320x2048_bf16n_decode_gemv_compressed_GBps"
+
+
+def cpu_arm(rows_sample: int, reps: int, warmup: int = 1):
     """The CPU arm: encode (reference encoder when oracle/_ref is present, else the oracle's restatement) and the
     oracle's decode+GEMV on all host threads, on the first `rows_sample` rows of the workload."""
     from oracle import cpu_oracle as o
@@ -126,8 +141,12 @@ def cpu_arm(rows_sample: int, reps: int):
     units = rows_sample // R
     nbytes = plane.size + aux.size + K * 2 + rows_sample * 4
     t0 = time.perf_counter()
-    o.decode_gemv_mt(plane, aux, x, 0, units, threads)       # warm-up pass, also sizes the run: about 20 s of CPU work at most
-    reps = max(1, min(reps, max(3, int(20.0 / max(time.perf_counter() - t0, 1e-4)))))
+    o.decode_gemv_mt(plane, aux, x, 0, units, threads)       # first warm-up pass, also sizes the run: about 20 s of CPU work at most
+    one = max(time.perf_counter() - t0, 1e-4)
+    warmup = max(1, min(warmup, max(1, int(5.0 / one))))
+    for _ in range(warmup - 1):
+        o.decode_gemv_mt(plane, aux, x, 0, units, threads)
+    reps = max(1, min(reps, max(3, int(20.0 / one))))
     times = []
     for _ in range(reps):
         t0 = time.perf_counter()
@@ -137,7 +156,7 @@ def cpu_arm(rows_sample: int, reps: int):
     return {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
             "sample": f"first {rows_sample} of {ROWS} rows ({nbytes / 1e6:.1f} MB compressed), median of {reps} passes of "
                       f"{dt:.3f} s; encoder ({'reference' if o.have_ref() else 'oracle'}) {rows_sample * K * 2 / t_enc / 1e9:.2f} GB/s of BF16 input",
-            "ms_per_step": dt * 1e3, "encode_s": t_enc, "passes": reps}, nbytes
+            "ms_per_step": dt * 1e3, "encode_s": t_enc, "passes": reps, "warmup": warmup}, nbytes
 
 
 def reference_kernels():
@@ -160,9 +179,9 @@ def run_reference(args):
     if rank != 0:
         return
     rows_sample = CPU_SAMPLE_ROWS
-    base, nbytes = cpu_arm(rows_sample, max(1, args.steps))
-    line = {"impl": "reference", "metric": "lm_head_248320x2048_bf16n_decode_gemv_compressed_GBps", "value": base["value"],
-            "unit": "GB/s", "n_gpus": args.gpus, "steps": base["passes"], "warmup": 1, "ms_per_step": base["ms_per_step"],
+    base, nbytes = cpu_arm(rows_sample, max(1, args.steps), max(0, args.warmup))
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"],
+            "unit": "GB/s", "n_gpus": args.gpus, "steps": base["passes"], "warmup": base["warmup"], "ms_per_step": base["ms_per_step"],
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "lm_head 248320x2048 HUFPAIR R=16, batch-1 decode GEMV (CPU arm: bounded row sample)",
                        "rows_sample": rows_sample},
@@ -170,6 +189,10 @@ def run_reference(args):
             "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
+
+
+L2_ROTATE_BELOW = 256e6   # working sets smaller than this are served from rotating copies so that L2 cannot hold them
+MIN_BLOCKS, MIN_TIMED_S = 30, 1.0
 
 
 def run_ours(args):
@@ -202,6 +225,9 @@ def run_ours(args):
         raise SystemExit("bench.py: GPU decode of the encoded shard is not bit-exact")
     del w
     shard_bytes = plane.numel() + aux.numel()
+    # a shard that L2 (126 MB) could serve is multiplied from rotating copies at different addresses
+    n_copies = 1 if shard_bytes >= L2_ROTATE_BELOW else max(3, int(np.ceil(2 * L2_ROTATE_BELOW / shard_bytes)))
+    copies = [enc] + [ops.upload(plane, aux, meta, dev) for _ in range(n_copies - 1)]
     counts = torch.tensor([shard_bytes], dtype=torch.int64, device=dev)
     if world > 1:
         dist.all_reduce(counts)
@@ -217,16 +243,23 @@ def run_ours(args):
     width = max(b - a for a, b in per)
     gathered = torch.empty((world, width), dtype=torch.float32, device=dev)
     mine = gathered[rank, : r1 - r0].view(1, r1 - r0) if world > 1 else logits
+    turn = [0]
+
+    def next_copy():
+        turn[0] = (turn[0] + 1) % n_copies
+        return copies[turn[0]]
 
     def step_nccl():
-        ops.mmv(x, enc, out=mine)
+        ops.mmv(x, next_copy(), out=mine)
         if world > 1:
             dist.all_gather_into_tensor(gathered.view(-1), gathered[rank])
 
     # N > 1, the product: the GEMV kernel stores its logits into every GPU's gathered buffer itself (peer stores over
-    # NVLink, epoch flags; the kernel ends when the peers' logits have arrived); no collective. Two steps (the two buffers in turn) form one CUDA graph.
-    fused = graph2 = None
+    # NVLink, epoch flags; the kernel ends when the peers' logits have arrived); no collective. One CUDA graph holds an
+    # even number of steps (the two exchange buffers in turn) that also walks through the rotating copies.
+    fused = graph = None
     fused_note = None
+    per_call = 1
     if world > 1:
         from orin_qwen_lossless_b200 import sharded
         try:
@@ -239,37 +272,55 @@ def run_ours(args):
             fused.close()
             fused, fused_note = None, "exchange buffers unavailable on another rank"
     if fused:
-        last = [fused(x) for _ in range(2)]
+        per_call = 2 * n_copies if n_copies > 1 else 2
+        last = [fused(x, next_copy()) for _ in range(per_call)]
         torch.cuda.synchronize()
-        graph2 = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph2):
-            last = [fused(x) for _ in range(2)]
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            last = [fused(x, next_copy()) for _ in range(per_call)]
 
     def step():
         if fused:
-            graph2.replay()     # two steps
+            graph.replay()     # per_call steps
         else:
             step_nccl()
 
-    per_call = 2 if fused else 1   # steps per call of step()
-    y_host = torch.empty((1, rows if world == 1 else world * (fused.width if fused else width)), dtype=torch.float32).pin_memory()
+    # end to end: activation from pinned host memory, logits back in host memory, every step
+    hosted = None
+    y_host = None
+    if world == 1:
+        y_host = torch.empty((1, rows), dtype=torch.float32).pin_memory()
+    else:
+        from orin_qwen_lossless_b200 import sharded
+        try:   # every rank's kernel stores its shard into one pinned host buffer shared by the processes of the node
+            hosted = sharded.HostGatheredLinear(enc, rows, R, 1)
+        except (RuntimeError, OSError) as e:
+            fused_note = (fused_note + "; " if fused_note else "") + f"shared host buffer unavailable: {e}"
+        agree = torch.tensor([0 if hosted else 1], dtype=torch.int32, device=dev)
+        dist.all_reduce(agree)
+        if int(agree.item()) and hosted:
+            hosted.close()
+            hosted = None
+        if hosted is None:
+            y_host = torch.empty((1, world * (fused.width if fused else width)), dtype=torch.float32).pin_memory()
 
     def step_e2e():
         if world == 1:
             # one GPU: ops.linear_host without a device buffer for the logits: x is copied in (4 KB), the kernel stores
             # the logits into the pinned host buffer itself, so the D2H traffic is the kernel's own stores
-            ops.linear_host(x_host, enc, y_host, x)
+            ops.linear_host(x_host, next_copy(), y_host, x)
             torch.cuda.current_stream().synchronize()  # a decode step consumes its logits on the host
+            return
+        if hosted is not None:
+            hosted.w = next_copy()
+            hosted.step(x_host, x)   # copy in, GEMV straight into the shared host buffer, synchronise, wait for every rank's epoch word
             return
         x.copy_(x_host, non_blocking=True)
         if fused:
-            y_dev_full = fused(x).view(1, -1)
-        elif world > 1:
-            step_nccl()
-            y_dev_full = gathered.view(1, -1)
+            y_dev_full = fused(x, next_copy()).view(1, -1)
         else:
             step_nccl()
-            y_dev_full = logits
+            y_dev_full = gathered.view(1, -1)
         y_host.copy_(y_dev_full, non_blocking=True)
         torch.cuda.current_stream().synchronize()  # a decode step consumes its logits on the host
 
@@ -278,44 +329,75 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps):
+    def timed(fn, calls):
+        """One block: `calls` calls of fn between barriers and device synchronisation; CUDA-event milliseconds (this rank)."""
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(steps):
+        for _ in range(calls):
             fn()
         e1.record()
         barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        return e0.elapsed_time(e1)
+
+    def blocks(fn, calls, steps_per_call=1):
+        """At least MIN_BLOCKS blocks and MIN_TIMED_S seconds of them; per block the max over ranks. Returns the sorted
+        per-step milliseconds of the blocks."""
+        first = timed(fn, calls)
+        n = max(MIN_BLOCKS, int(np.ceil(MIN_TIMED_S * 1e3 / max(first, 1e-3))))
+        if world > 1:   # every rank must run the same number of blocks
+            nb = torch.tensor([n], dtype=torch.int64, device=dev)
+            dist.all_reduce(nb, op=dist.ReduceOp.MAX)
+            n = int(nb.item())
+        n = min(n, 2000)
+        ms = torch.tensor([timed(fn, calls) for _ in range(n)], dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
+        return sorted((ms / (calls * steps_per_call)).tolist())
 
+    calls = max(1, args.steps // per_call)
+    steps = calls * per_call                      # exactly what a block times (equal to --steps when it divides)
     for _ in range(max(args.warmup, 3)):
         step()
     sampler = ClockSampler(local) if rank == 0 else None
-    ms_total = timed(step, args.steps // per_call) / (args.steps // per_call * per_call) * args.steps
+    per_step = blocks(step, calls, per_call)
+    ms_step = statistics.median(per_step)
     nccl_us = None
     if world > 1:   # for comparison: the same shards with an NCCL all-gather behind the kernel (eager launches)
         for _ in range(3):
             step_nccl()
-        nccl_us = timed(step_nccl, args.steps) / args.steps * 1e3
+        nccl_us = statistics.median(blocks(step_nccl, args.steps)) * 1e3
     # the GEMV launch alone (no collective), per launch, on the launching stream: the roofline figure
-    kernel_ms = ms_total / args.steps if world == 1 else timed(lambda: ops.mmv(x, enc, out=mine), args.steps) / args.steps
+    kernel_ms = ms_step if world == 1 else statistics.median(blocks(lambda: ops.mmv(x, next_copy(), out=mine), args.steps))
     for _ in range(3):
         step_e2e()
-    ms_e2e = timed(step_e2e, args.steps)
+    e2e_steps = blocks(step_e2e, args.steps)
+    ms_e2e = statistics.median(e2e_steps)
     clocks = sampler.stop() if sampler else None
 
+    # multi-token batches on the same matrix (the verify batch of speculative decoding): 2 and 4 columns share one decode
+    multi_tok = None
+    if world == 1:
+        multi_tok = {}
+        g = torch.Generator().manual_seed(0xAC8)
+        x4 = torch.randn((4, K), generator=g).to(torch.bfloat16).to(dev)
+        singles = [ops.mmv(x4[i:i + 1], enc) for i in range(4)]
+        for T in (2, 4):
+            yT = torch.empty((T, rows), dtype=torch.float32, device=dev)
+            for _ in range(3):
+                ops.mmv(x4[:T], enc, out=yT)
+            us = statistics.median(blocks(lambda: ops.mmv(x4[:T], next_copy(), out=yT), max(1, args.steps // 4))) * 1e3
+            same = all(torch.equal(yT[i].view(torch.int32), singles[i][0].view(torch.int32)) for i in range(T))
+            multi_tok[str(T)] = {"us_per_step": us, "ratio_to_one_token": us / (ms_step * 1e3), "bitwise_equal_to_single_token": bool(same)}
+        del singles
+
     # comparator on the same GPU: a stock BF16 GEMV (cuBLAS through torch) over the uncompressed shard
-    cublas_us = None
-    if args.cublas:
-        wd = gen_rows(r0, r1).to(dev)
-        yb = torch.empty((1, r1 - r0), dtype=torch.bfloat16, device=dev)
-        for _ in range(5):
-            torch.mm(x, wd.t(), out=yb)
-        cublas_us = timed(lambda: torch.mm(x, wd.t(), out=yb), args.steps) / args.steps * 1e3
-        del wd
+    wd = gen_rows(r0, r1).to(dev)
+    yb = torch.empty((1, r1 - r0), dtype=torch.bfloat16, device=dev)
+    for _ in range(5):
+        torch.mm(x, wd.t(), out=yb)
+    cublas_us = statistics.median(blocks(lambda: torch.mm(x, wd.t(), out=yb), args.steps)) * 1e3
+    del wd
 
     # parity of what was timed, on a sample of rows, against the FP64 oracle (rank 0, its own shard)
     parity = None
@@ -327,32 +409,55 @@ def run_ours(args):
         y64, s = o.gemv_f64(wb, xf)
         got = (last[-1][rank, 0, :n] if fused else mine[0, :n]).float().cpu().numpy()
         parity = {"rows_checked": n, "max_err_over_sum_abs": float((np.abs(got - y64) / s).max()), "roundtrip_bit_exact": bool(ok)}
+        if hosted is not None or world == 1:
+            got_h = (hosted._bufs[(hosted.epoch - 1) & 1][0, :n] if hosted is not None else y_host[0, :n]).numpy()
+            parity["e2e_max_err_over_sum_abs"] = float((np.abs(got_h - y64) / s).max())
 
     expired = fused.xchg.expired() if fused else False
-    fused_used = fused is not None
+    faults = ops.fault_status()
+    fused_used, hosted_used = fused is not None, hosted is not None
+    fused_width = fused.width if fused else width
+    if hosted is not None:
+        hosted.close()
     if fused:
         fused.close()
+    del copies, enc
+    torch.cuda.empty_cache()
+
+    # the rest of the metric: the MoE layer (decode at 1 / 2 / 4 tokens, prefill at 2048 / 8192 tokens; expert-parallel
+    # over the ranks) and the small-matrix graph (one GPU)
+    moe = None
+    small = None
+    if not args.no_moe:
+        moe = moe_block(args, torch, dist, ops, rank, world, dev)
+        if world == 1:
+            small = small_block(args, torch, ops, dev)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
     if expired:
         raise SystemExit("bench.py: a wait for a peer's logits expired")
-    ms_step = ms_total / args.steps
+    if faults:
+        raise SystemExit(f"bench.py: a bounded wait inside a kernel expired (fault status {faults})")
     peak, peak_src = measured_peak()
     achieved = shard_algo_bytes / (kernel_ms * 1e-3) / 1e9
+    l2 = ("inputs larger than L2 (compressed matrix %.0f MB per GPU, one copy)" % (shard_bytes / 1e6) if n_copies == 1 else
+          "%d copies of the %.0f MB shard at different addresses, used in turn (%.0f MB between reuses; L2 is 126 MB)"
+          % (n_copies, shard_bytes / 1e6, n_copies * shard_bytes / 1e6))
     line = {
-        "metric": "lm_head_248320x2048_bf16n_decode_gemv_compressed_GBps",
+        "metric": METRIC,
         "value": algo_bytes / (ms_step * 1e-3) / 1e9, "unit": "GB/s",
-        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+        "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"lm_head {rows}x{K} HUFPAIR R={R}, batch-1 decode GEMV, BF16 activation, FP32 logits"
                                + (f", rows sharded over {world} GPUs, logits stored into every GPU's buffer by the GEMV kernel "
                                   "(peer stores + epoch flags, no collective)" if fused_used else
                                   f", rows sharded over {world} GPUs + NCCL all-gather ({fused_note})" if world > 1 else ""),
-                   "l2": "inputs larger than L2 (compressed matrix %.0f MB per GPU)" % (shard_bytes / 1e6),
-                   "compressed_bytes": total_weight_bytes, "bf16_bytes": rows * K * 2,
+                   "l2": l2, "compressed_bytes": total_weight_bytes, "bf16_bytes": rows * K * 2,
                    "ratio": total_weight_bytes / (rows * K * 2)},
+        "blocks": {"n": len(per_step), "steps_per_block": steps, "ms_per_step_min": per_step[0], "ms_per_step_median": ms_step,
+                   "ms_per_step_max": per_step[-1], "timed_s": sum(per_step) * steps / 1e3},
         "us_per_step": ms_step * 1e3,
         "bf16_equivalent_GBps": (rows * K * 2 + K * 2 + rows * 4) / (ms_step * 1e-3) / 1e9,
         "frac_of_nominal_8TBps": algo_bytes / (ms_step * 1e-3) / 8e12 / world,
@@ -360,16 +465,24 @@ def run_ours(args):
                      "traffic": DRAM_TRAFFIC_RATIO * shard_algo_bytes,
                      "traffic_source": "ncu capture of a 65536-row case scaled by rows (profiles/lm_head_gemv_ncu.md)", "peak_source": peak_src, "kernel_us": kernel_ms * 1e3,
                      "algorithmic_bytes_per_launch": shard_algo_bytes},
-        "e2e": {"value": algo_bytes / (ms_e2e / args.steps * 1e-3) / 1e9, "unit": "GB/s",
-                "h2d_bytes_per_step": K * 2, "d2h_bytes_per_step": int(y_host.numel() * 4), "us_per_step": ms_e2e / args.steps * 1e3},
-        "gpu_launches": args.steps,   # one kernel per step at every N
+        "e2e": {"value": algo_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
+                "h2d_bytes_per_step": K * 2, "d2h_bytes_per_step": int(rows * 4 if (hosted_used or world == 1) else world * fused_width * 4),
+                "us_per_step": ms_e2e * 1e3, "us_per_step_min": e2e_steps[0] * 1e3, "us_per_step_max": e2e_steps[-1] * 1e3,
+                "how": ("activation copied in from pinned host memory, logits stored by the GEMV kernel straight into pinned host memory"
+                        + (" shared by the ranks of the node (every rank writes its shard; epoch words in the buffer tell every process when all shards are there)"
+                           if hosted_used else "") if (hosted_used or world == 1) else
+                        "activation copied in, gathered logits copied out behind the kernel") + ", stream synchronised every step"},
+        "gpu_launches": steps,   # one kernel per step at every N
         "nccl_allgather_us_per_step": nccl_us,
         "cublas_bf16_gemv_us": cublas_us,
+        "vs_cublas_bf16_gemv": cublas_us / (kernel_ms * 1e3),
+        "multi_token": multi_tok,
+        "moe": moe, "small_matrices": small,
         "clocks": clocks, "parity": parity,
         "host": {"gen_s": t_gen, "encode_s": t_enc, "encode_GBps_bf16": (r1 - r0) * K * 2 / t_enc / 1e9, "threads": os.cpu_count()},
     }
     if world == 1 and not args.no_cpu:
-        base, _ = cpu_arm(CPU_SAMPLE_ROWS, 100)
+        base, _ = cpu_arm(CPU_SAMPLE_ROWS, 100, 1)
         line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
         line["reference_kernels_same_gpu"] = reference_kernels()
     print(json.dumps(line), flush=True)
@@ -377,9 +490,19 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-# ------------------------------------------------------------------ secondary workloads (configs 2, 3, 4 of the baseline)
+# ------------------------------------------------------------------ the other configurations of the metric (MoE layer, small matrices)
 
-def _enc(ops, rows, K, fmt, R, cm, seed, dev, fo=False):
+def measured_tensor_peaks():
+    """(burst, sustained) dense BF16 TFLOP/s of this pool's B200s from MEASURED_PEAKS.json, else the earlier measurement."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured (MEASURED_PEAKS.json)"
+    return 1590.0, 1400.0, "fallback (earlier measurement on this pool)"
+
+
+def _enc(ops, rows, K, fmt, R, cm, seed, dev, fo=False, keep=False):
     import torch
     g = torch.Generator().manual_seed(seed)
     w = torch.empty((rows, K), dtype=torch.bfloat16)
@@ -388,11 +511,14 @@ def _enc(ops, rows, K, fmt, R, cm, seed, dev, fo=False):
         n = min(step, rows - r0)
         w[r0:r0 + n] = (torch.randn((n, K), generator=g) * 0.02).to(torch.bfloat16)
     plane, aux, meta = ops.encode(w, fmt, R, cm, fo)
-    return ops.upload(plane, aux, meta, dev)
+    enc = ops.upload(plane, aux, meta, dev)
+    return (enc, w) if keep else enc
 
 
-def _time_graph(torch, fn, reps, inner=1):
-    """Median-free mean over `reps` replays of a CUDA graph of `fn`; returns microseconds per inner step."""
+def _time_graph(torch, fn, reps, inner=1, min_s=0.3):
+    """A CUDA graph of `fn`, replayed back to back: every sample times enough replays to last about 5 ms (so that the
+    launch of a replay overlaps the one before it, as in a decode loop), at least max(reps, 30) samples and min_s seconds
+    of them. Returns (median, min, max) microseconds per inner step."""
     s = torch.cuda.Stream()
     fn()
     torch.cuda.synchronize()
@@ -403,49 +529,67 @@ def _time_graph(torch, fn, reps, inner=1):
     for _ in range(3):
         g.replay()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(reps):
-        g.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    return e0.elapsed_time(e1) * 1e3 / reps / inner
+
+    def sample(m):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(m):
+            g.replay()
+        e1.record()
+        e1.synchronize()
+        return e0.elapsed_time(e1) / m
+
+    m = max(1, int(np.ceil(5.0 / max(sample(1), 1e-3))))
+    times, total = [], 0.0
+    while (len(times) < max(reps, 30) or total < min_s * 1e3) and len(times) < 2000:
+        ms = sample(m)
+        times.append(ms)
+        total += ms * m
+    times.sort()
+    k = 1e3 / inner
+    return statistics.median(times) * k, times[0] * k, times[-1] * k
 
 
-def run_small(args):
-    """Config 2: 48 layers x {2048x512, 512x2048, 256x2048} NIBBLE, batch-1 GEMVs, one CUDA graph of 144 launches."""
+def expert_weights(e: int):
+    """(gate [512, 2048], up [512, 2048], down [2048, 512]) of routed expert e: N(0, 0.02) rounded to BF16, one seed per
+    expert, so that any rank (and the parity check) can regenerate any expert on its own."""
     import torch
-    from orin_qwen_lossless_b200 import ops
-    dev = torch.device("cuda", 0)
-    ops.init()
-    layers, nbytes = [], 0
-    for l in range(48):
-        ws = [_enc(ops, 2048, 512, 1, 0, False, 3 * l, dev), _enc(ops, 512, 2048, 1, 0, False, 3 * l + 1, dev),
-              _enc(ops, 256, 2048, 1, 0, False, 3 * l + 2, dev)]
-        nbytes += sum(w.nbytes for w in ws)
-        layers.append(ws)
-    x512 = torch.randn(1, 512, device=dev).to(torch.bfloat16)
-    x2048 = torch.randn(1, 2048, device=dev).to(torch.bfloat16)
-    outs = [[torch.empty(1, w.meta.rows, device=dev) for w in ws] for ws in layers]
-
-    def step():
-        for ws, ys in zip(layers, outs):
-            ops.mmv(x512, ws[0], out=ys[0]); ops.mmv(x2048, ws[1], out=ys[1]); ops.mmv(x2048, ws[2], out=ys[2])
-
-    us = _time_graph(torch, step, args.steps)
-    peak, _ = measured_peak()
-    print(json.dumps({"workload": "small matrices: 48 layers x {2048x512, 512x2048, 256x2048} NIBBLE, batch-1, one CUDA graph of 144 GEMVs",
-                      "us_per_graph": us, "us_per_gemv": us / 144, "compressed_bytes": nbytes, "GBps": nbytes / us / 1e3,
-                      "frac_of_measured_hbm": nbytes / us / 1e3 / peak, "l2": "191 MB of weights per replay > L2"}), flush=True)
+    g = torch.Generator().manual_seed(0xE0000 + e)
+    return tuple((torch.randn(shape, generator=g) * 0.02).to(torch.bfloat16) for shape in ((512, 2048), (512, 2048), (2048, 512)))
 
 
-def _moe_weights(ops, dev, n_experts, rank=0, fo=False):
-    """Routed expert weights of one rank (every rank draws its own experts: seeds differ per rank). fo: 16-row
-    fragment-order bands (the vLLM layout) instead of chunk-major R = 8 gate / up and row-major R = 16 down."""
-    gate = _enc(ops, n_experts * 512, 2048, 3, 16 if fo else 8, not fo, 101 + 10 * rank, dev, fo)
-    up = _enc(ops, n_experts * 512, 2048, 3, 16 if fo else 8, not fo, 102 + 10 * rank, dev, fo)
-    down = _enc(ops, n_experts * 2048, 512, 3, 16, False, 103 + 10 * rank, dev, fo)
-    return gate, up, down
+def _moe_weights(ops, dev, e_lo, n_local, fo=False):
+    """Routed experts [e_lo, e_lo + n_local) encoded as the policy lays them out. fo: 16-row fragment-order bands (the
+    vLLM layout) instead of chunk-major R = 8 gate / up and row-major R = 16 down (the llama.cpp layout)."""
+    import torch
+    parts = [expert_weights(e) for e in range(e_lo, e_lo + n_local)]
+    out = []
+    for i, (R_, cm) in enumerate(((16 if fo else 8, not fo), (16 if fo else 8, not fo), (16, False))):
+        w = torch.cat([p[i] for p in parts], dim=0)
+        plane, aux, meta = ops.encode(w, 3, R_, cm, fo)
+        out.append(ops.upload(plane, aux, meta, dev))
+    return out
+
+
+def _bits(t):
+    import torch
+    return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def _routed_oracle(x_bits, wts, ids, e_lo, n_local, bf16_act):
+    """FP64 output of the routed experts in [e_lo, e_lo + n_local) for the tokens given (x as BF16 bits [T, 2048];
+    wts FP32 / ids int32 [T, k]); slots routed elsewhere contribute nothing. Only the experts these tokens use are
+    generated."""
+    from oracle import cpu_oracle as o
+    used = sorted({int(e) for e in ids.reshape(-1) if e_lo <= int(e) < e_lo + n_local})
+    if not used:
+        return np.zeros((ids.shape[0], 2048))
+    pos = {e: i for i, e in enumerate(used)}
+    ws = [expert_weights(e) for e in used]
+    gb, ub, db = (np.concatenate([_bits(w[i]) for w in ws], axis=0) for i in range(3))
+    local = np.vectorize(lambda e: e_lo <= e < e_lo + n_local)(ids)
+    ids_c = np.vectorize(lambda e: pos.get(int(e), 0))(ids).astype(np.int32)
+    return o.moe_layer_f64(o.bf16_bits_to_f32(x_bits), gb, ub, db, np.where(local, wts, 0.0), ids_c, len(used), bf16_act=bf16_act)
 
 
 def _dist_setup(torch):
@@ -456,7 +600,7 @@ def _dist_setup(torch):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    if world > 1:
+    if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=dev)
     return rank, world, dev
 
@@ -470,21 +614,17 @@ def _max_over_ranks(torch, us, world, dev):
     return float(t.item())
 
 
-def run_moe_decode(args):
+def moe_decode_runs(args, torch, dist, ops, rank, world, dev, weights, shared):
     """Config 3: hidden 2048, 256 routed experts (gate|up 512x2048 each, down 2048x512) + shared expert (NIBBLE), softmax
     top-8 on the GPU, 1 / 2 / 4 tokens. A graph holds 16 steps with 16 different routings so that consecutive steps hit
     different experts (the 1.08 GB of expert weights do not fit L2; one step touches 34 MB per token)."""
-    import torch
-    import torch.distributed as dist
-    from orin_qwen_lossless_b200 import ops
-    rank, world, dev = _dist_setup(torch)
-    ops.init()
+    from oracle import cpu_oracle as o
     E, k = 256, 8
-    n_local = E // world                      # expert-parallel: rank r holds experts [r * n_local, (r + 1) * n_local)
-    gate, up, down = _moe_weights(ops, dev, n_local, rank)
-    sh_gu = _enc(ops, 1024, 2048, 1, 0, False, 104, dev)      # the shared expert is replicated; rank 0's result is used
-    sh_down = _enc(ops, 2048, 512, 1, 0, False, 105, dev)
+    n_local = E // world
+    gate, up, down = weights
+    sh_gu, sh_down = shared
     peak, _ = measured_peak()
+    out = []
     for T in (1, 2, 4):
         steps = 16
         g = torch.Generator(device=dev).manual_seed(1234 + T)   # the same tokens and routing on every rank
@@ -527,67 +667,178 @@ def run_moe_decode(args):
                 else:
                     y.add_(ysh)
 
-        us = _max_over_ranks(torch, _time_graph(torch, step, max(args.steps // 16, 5), inner=steps), world, dev)
+        med, lo, hi = _time_graph(torch, step, max(args.steps // 16, 5), inner=steps)
+        us = _max_over_ranks(torch, med, world, dev)
         distinct = sum(len(torch.unique(i)) for i in ids) / steps
         per_expert = (gate.nbytes + up.nbytes + down.nbytes) / n_local
         nbytes = distinct * per_expert + sh_gu.nbytes + sh_down.nbytes
+        # parity of the routed experts on step 0 (this rank's slice of them) against the FP64 oracle layer
+        part, w0, i0 = ops.moe_decode(xs[0], gate, up, down, E, k, router_logits=logits[0], expert_lo=rank * n_local,
+                                      n_experts_local=n_local)
+        parity = None
         if rank == 0:
-            print(json.dumps({"workload": f"MoE decode layer, {T} token(s), 256 experts top-8 + shared expert", "n_gpus": world,
-                              "parallelism": "1 GPU" if world == 1 else f"expert-parallel over {world} GPUs + NCCL all-reduce" if args.nccl
-                              else f"expert-parallel over {world} GPUs, partial outputs stored into every GPU by the combine kernel, no collective",
-                              "us_per_layer": us, "distinct_experts": distinct, "compressed_bytes": nbytes,
-                              "GBps": nbytes / us / 1e3, "frac_of_measured_hbm": nbytes / us / 1e3 / peak / world,
-                              "launches_per_layer": 7 + (world > 1)}), flush=True)
+            ids_ref, w_ref = o.softmax_topk(logits[0].cpu().numpy(), k)
+            ref = _routed_oracle(_bits(xs[0].cpu()), w0.cpu().numpy(), i0.cpu().numpy(), 0, n_local, False)
+            parity = {"router_ids_equal_oracle": bool(np.array_equal(i0.cpu().numpy(), ids_ref)),
+                      "router_weights_max_abs_diff": float(np.abs(w0.cpu().numpy() - w_ref).max()),
+                      "max_err_over_max_abs": float(np.abs(part.cpu().numpy() - ref).max() / max(np.abs(ref).max(), 1e-30)),
+                      "what": "routed experts held by rank 0, step 0, against the FP64 layer over the exact weights"}
+        if rank == 0:
+            out.append({"tokens": T, "n_gpus": world,
+                        "parallelism": "1 GPU" if world == 1 else f"expert-parallel over {world} GPUs + NCCL all-reduce" if args.nccl
+                        else f"expert-parallel over {world} GPUs, partial outputs stored into every GPU by the combine kernel, no collective",
+                        "us_per_layer": us, "us_min": lo, "us_max": hi, "distinct_experts": distinct, "compressed_bytes": nbytes,
+                        "GBps": nbytes / us / 1e3, "frac_of_measured_hbm": nbytes / us / 1e3 / peak / world,
+                        "launches_per_layer": 7 + (world > 1), "parity": parity})
         if fmd:
             fmd.close()
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    return out
 
 
-def run_moe_prefill(args):
+def moe_prefill_runs(args, torch, dist, ops, rank, world, dev, weights, fo=False):
     """Config 4: the same expert weights with 2048 and 8192 tokens: routing sort, batched gate/up + SwiGLU (BF16 out),
     batched down (FP32 out), combine."""
-    import torch
-    import torch.distributed as dist
-    from orin_qwen_lossless_b200 import ops, sharded
-    rank, world, dev = _dist_setup(torch)
-    ops.init()
+    from orin_qwen_lossless_b200 import sharded
     E, k = 256, 8
-    n_local = E // world
-    gate, up, down = _moe_weights(ops, dev, n_local, rank, args.fo)
+    gate, up, down = weights
+    hbm, _ = measured_peak()
+    burst, sustained, _ = measured_tensor_peaks()
+    out = []
     for T in (2048, 8192):
         flops = 6.0 * 512 * 2048 * k * T
         nbytes = (gate.nbytes + up.nbytes + down.nbytes) * world
+        g = torch.Generator(device=dev).manual_seed(4321 + T + rank)
         if world == 1:
-            x = torch.randn(T, 2048, device=dev).to(torch.bfloat16)
-            wts, ids = ops.moe_topk(torch.randn(T, E, device=dev), k)
-            us = _time_graph(torch, lambda: ops.moe_experts(x, gate, up, down, wts, ids, E), max(args.steps // 100, 5))
+            x = torch.randn(T, 2048, device=dev, generator=g).to(torch.bfloat16)
+            wts, ids = ops.moe_topk(torch.randn(T, E, device=dev, generator=g), k)
+            med, lo, hi = _time_graph(torch, lambda: ops.moe_experts(x, gate, up, down, wts, ids, E), max(args.steps // 100, 5))
+            us = med
+            y = ops.moe_experts(x, gate, up, down, wts, ids, E)
             par = "1 GPU"
         else:
             # tokens data-parallel (T / world per rank), experts sharded: all-to-all dispatch of the routed rows, batched
             # kernels on the owner, all-to-all back, combine. The exchange sizes come back to the host, so the layer is
             # timed as eager launches with CUDA events (max over ranks).
             Tl = T // world
-            x = torch.randn(Tl, 2048, device=dev).to(torch.bfloat16)
-            wts, ids = ops.moe_topk(torch.randn(Tl, E, device=dev), k)
+            x = torch.randn(Tl, 2048, device=dev, generator=g).to(torch.bfloat16)
+            wts, ids = ops.moe_topk(torch.randn(Tl, E, device=dev, generator=g), k)
             for _ in range(3):
-                sharded.moe_prefill_ep(x, wts, ids, gate, up, down, E)
-            reps = max(args.steps // 100, 5)
-            torch.cuda.synchronize(); dist.barrier()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
+                y = sharded.moe_prefill_ep(x, wts, ids, gate, up, down, E)
+            reps = max(args.steps // 100, 10)
+            times = []
             for _ in range(reps):
+                torch.cuda.synchronize(); dist.barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
                 sharded.moe_prefill_ep(x, wts, ids, gate, up, down, E)
-            e1.record()
-            torch.cuda.synchronize()
-            us = _max_over_ranks(torch, e0.elapsed_time(e1) * 1e3 / reps, world, dev)
+                e1.record()
+                torch.cuda.synchronize()
+                times.append(_max_over_ranks(torch, e0.elapsed_time(e1) * 1e3, world, dev))
+            times.sort()
+            us, lo, hi = statistics.median(times), times[0], times[-1]
             par = f"expert-parallel over {world} GPUs, NCCL all-to-all dispatch and return"
         if rank == 0:
-            print(json.dumps({"workload": f"MoE prefill layer, {T} tokens, 256 experts top-8" + (", fragment-order experts" if args.fo else ""),
-                              "n_gpus": world, "parallelism": par,
-                              "us_per_layer": us, "TFLOPs": flops / us / 1e6, "weight_GBps": nbytes / us / 1e3,
-                              "frac_of_bf16_peak_1679": flops / us / 1e6 / 1679.3 / world}), flush=True)
+            n = 4   # tokens checked against the FP64 layer (BF16 SwiGLU activations, as the batched path stores them)
+            ref = _routed_oracle(_bits(x[:n].cpu()), wts[:n].cpu().numpy(), ids[:n].cpu().numpy(), 0, E, True)
+            got = y[:n].float().cpu().numpy()
+            hbm_us, tensor_us = nbytes / world / hbm / 1e3, flops / world / burst / 1e6
+            out.append({"tokens": T, "n_gpus": world, "parallelism": par, "layout": "fragment order" if fo else "lane-major (chunk-major R=8 gate/up, R=16 down)",
+                        "us_per_layer": us, "us_min": lo, "us_max": hi, "TFLOPs": flops / us / 1e6, "weight_GBps": nbytes / us / 1e3,
+                        "roofline": {"hbm_bound_us": hbm_us, "tensor_bound_us": tensor_us, "tensor_bound_us_sustained": flops / world / sustained / 1e6,
+                                     "bound": "hbm" if hbm_us > tensor_us else "tensor", "frac": max(hbm_us, tensor_us) / us,
+                                     "flops": flops, "compressed_bytes": nbytes},
+                        "parity": {"tokens_checked": n, "max_err_over_max_abs": float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-30)),
+                                   "what": "BF16 layer output of the first tokens of rank 0 against the FP64 layer (BF16 SwiGLU activations)"}})
+    return out
+
+
+def moe_block(args, torch, dist, ops, rank, world, dev):
+    """The MoE half of the metric for the contract line: decode layer at 1 / 2 / 4 tokens, prefill layer at 2048 / 8192
+    tokens, expert-parallel over the ranks. Rank 0 returns the dict."""
+    E = 256
+    n_local = E // world
+    t0 = time.perf_counter()
+    weights = _moe_weights(ops, dev, rank * n_local, n_local)
+    shared = (_enc(ops, 1024, 2048, 1, 0, False, 104, dev), _enc(ops, 2048, 512, 1, 0, False, 105, dev))
+    t_w = time.perf_counter() - t0
+    decode = moe_decode_runs(args, torch, dist, ops, rank, world, dev, weights, shared)
+    prefill = moe_prefill_runs(args, torch, dist, ops, rank, world, dev, weights)
+    faults = ops.fault_status()
+    if world > 1:
+        dist.barrier()
+    if rank != 0:
+        return None
+    return {"experts": "256 routed experts (gate, up 512x2048; down 2048x512) + shared expert (NIBBLE 1024x2048, 2048x512), "
+                       "N(0, 0.02) weights, one seed per expert; top-8 of N(0,1) router logits",
+            "weights_gen_encode_s": t_w, "decode": decode, "prefill": prefill, "fault_status": faults}
+
+
+def small_block(args, torch, ops, dev):
+    """Config 2: 48 layers x {2048x512, 512x2048, 256x2048} NIBBLE, batch-1 GEMVs, one CUDA graph of 144 launches."""
+    from oracle import cpu_oracle as o
+    layers, nbytes, first = [], 0, None
+    for l in range(48):
+        made = [_enc(ops, 2048, 512, 1, 0, False, 3 * l, dev, keep=(l == 0)), _enc(ops, 512, 2048, 1, 0, False, 3 * l + 1, dev, keep=(l == 0)),
+                _enc(ops, 256, 2048, 1, 0, False, 3 * l + 2, dev, keep=(l == 0))]
+        if l == 0:
+            first = [m[1] for m in made]
+            made = [m[0] for m in made]
+        nbytes += sum(w.nbytes for w in made)
+        layers.append(made)
+    x512 = torch.randn(1, 512, device=dev).to(torch.bfloat16)
+    x2048 = torch.randn(1, 2048, device=dev).to(torch.bfloat16)
+    outs = [[torch.empty(1, w.meta.rows, device=dev) for w in ws] for ws in layers]
+
+    def step():
+        for ws, ys in zip(layers, outs):
+            ops.mmv(x512, ws[0], out=ys[0]); ops.mmv(x2048, ws[1], out=ys[1]); ops.mmv(x2048, ws[2], out=ys[2])
+
+    us, lo, hi = _time_graph(torch, step, args.steps // 10)
+    peak, _ = measured_peak()
+    worst = 0.0
+    for wsrc, xv, yv in zip(first, (x512, x2048, x2048), outs[0]):   # FP64 check of the first layer's three products
+        y64, sabs = o.gemv_f64(_bits(wsrc), o.bf16_bits_to_f32(_bits(xv.cpu())[0]))
+        worst = max(worst, float((np.abs(yv[0].cpu().numpy() - y64) / sabs).max()))
+    return {"workload": "small matrices: 48 layers x {2048x512, 512x2048, 256x2048} NIBBLE, batch-1, one CUDA graph of 144 GEMVs",
+            "us_per_graph": us, "us_min": lo, "us_max": hi, "us_per_gemv": us / 144, "compressed_bytes": nbytes, "GBps": nbytes / us / 1e3,
+            "frac_of_measured_hbm": nbytes / us / 1e3 / peak, "l2": "191 MB of weights per replay > L2",
+            "parity": {"max_err_over_sum_abs": worst, "what": "first layer's three GEMVs against FP64"}}
+
+
+def run_small(args):
+    import torch
+    from orin_qwen_lossless_b200 import ops
+    dev = torch.device("cuda", 0)
+    ops.init()
+    print(json.dumps(small_block(args, torch, ops, dev)), flush=True)
+
+
+def run_moe_decode(args):
+    import torch
+    import torch.distributed as dist
+    from orin_qwen_lossless_b200 import ops
+    rank, world, dev = _dist_setup(torch)
+    ops.init()
+    n_local = 256 // world
+    weights = _moe_weights(ops, dev, rank * n_local, n_local)
+    shared = (_enc(ops, 1024, 2048, 1, 0, False, 104, dev), _enc(ops, 2048, 512, 1, 0, False, 105, dev))
+    for rec in moe_decode_runs(args, torch, dist, ops, rank, world, dev, weights, shared):
+        print(json.dumps({"workload": f"MoE decode layer, {rec['tokens']} token(s), 256 experts top-8 + shared expert", **rec}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_moe_prefill(args):
+    import torch
+    import torch.distributed as dist
+    from orin_qwen_lossless_b200 import ops
+    rank, world, dev = _dist_setup(torch)
+    ops.init()
+    n_local = 256 // world
+    weights = _moe_weights(ops, dev, rank * n_local, n_local, args.fo)
+    for rec in moe_prefill_runs(args, torch, dist, ops, rank, world, dev, weights, args.fo):
+        print(json.dumps({"workload": f"MoE prefill layer, {rec['tokens']} tokens, 256 experts top-8", **rec}), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -614,7 +865,7 @@ def run_dense_mid(args):
                     for i in range(20):
                         ops.mmv(x, copies[i % 8], out=ys[i % 8])
 
-                line[f"us_{T}_tok"] = round(_time_graph(torch, step, max(10, args.steps // 20), inner=20), 2)
+                line[f"us_{T}_tok"] = round(_time_graph(torch, step, max(10, args.steps // 20), inner=20)[0], 2)
             print(json.dumps(line), flush=True)
 
 
@@ -626,7 +877,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=ROWS, help="rows of the matrix (default: the vocabulary projection)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--cublas", action="store_true", help="also time a stock BF16 GEMV of the uncompressed matrix")
+    ap.add_argument("--no-moe", action="store_true", help="skip the MoE layer and small-matrix blocks of the contract line")
     ap.add_argument("--fo", action="store_true", help="moe_prefill: experts in the fragment-order layout (mma.sync batched kernel)")
     ap.add_argument("--nccl", action="store_true", help="N > 1, moe_decode: all-reduce with NCCL instead of the fused peer stores")
     ap.add_argument("--workload", default="lm_head", choices=["lm_head", "small", "moe_decode", "moe_prefill", "dense_mid"],

@@ -95,6 +95,21 @@ def init() -> None:
     check(lib().bf16n_init())
 
 
+def fault_status() -> int:
+    """Synchronises the current stream and returns (and clears) the bit mask of the kernels' bounded waits that ran out
+    since the last call: 1 staged GEMV, 2 MoE decode units, 4 fragment-order kernels, 8 batched kernel. 0: all outputs
+    complete; otherwise the outputs of the affected work items are NaN."""
+    v = C.c_uint(0)
+    check(lib().bf16n_fault_status(C.byref(v), _stream()))
+    return int(v.value)
+
+
+def set_peer_wait_limit_ms(ms: int) -> None:
+    """How long a wait for the peers' announcements may take before it gives up and sets the exchange header's expired
+    word (default 2000 ms); applies to launches made or captured after the call."""
+    check(lib().bf16n_set_peer_wait_limit_ms(int(ms)))
+
+
 def sm_count() -> int:
     n = C.c_int(0)
     check(lib().bf16n_sm_count(C.byref(n)))
@@ -216,8 +231,8 @@ def _check_out(out: torch.Tensor, shape: tuple, dtype: torch.dtype, device: torc
     if tuple(out.shape) != tuple(shape) or out.dtype != dtype:
         raise RuntimeError(f"bf16n.{what}: out must have shape {tuple(shape)} and dtype {dtype}, got {tuple(out.shape)} {out.dtype}")
     if out.device.type == "cpu":
-        if not (out.is_pinned() and out.is_contiguous()):
-            raise RuntimeError(f"bf16n.{what}: a host output must be pinned and contiguous")
+        if not out.is_pinned():
+            raise RuntimeError(f"bf16n.{what}: a host output must be pinned (page-locked and mapped into the device)")
     elif out.device != device:
         raise RuntimeError(f"bf16n.{what}: out is on {out.device}, the weight on {device}")
     if out.numel() and out.stride(-1) != 1:

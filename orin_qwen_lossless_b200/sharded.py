@@ -238,15 +238,16 @@ class FusedShardedLinear:
         self.wait_in_kernel = wait_in_kernel
         self._outs = [self.xchg.peer_out(b * self.area + self.rank * max_tokens * self.width * 4, wait_in_kernel) for b in range(2)]
 
-    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, weight: ops.Weight | None = None) -> torch.Tensor:
         """x [T, K] (replicated, T == max_tokens) -> gathered [world, T, width]: rank r's logits in [r, :, :rows_r],
-        complete on this stream when the call returns."""
+        complete on this stream when the call returns. weight: another copy of the same shard (benchmarks rotate copies
+        so that a small shard is not served from L2)."""
         if x.shape[0] != self.T:
             raise RuntimeError("bf16n FusedShardedLinear: built for a fixed number of tokens")
         b = self.step & 1
         self.step += 1
         a0, a1 = self.ranges[self.rank]
-        mmv_peers(x, self.w, self._views[b][self.rank][:, : a1 - a0], self._outs[b])  # rows of the padded [T, width] slot
+        mmv_peers(x, weight or self.w, self._views[b][self.rank][:, : a1 - a0], self._outs[b])  # rows of the padded [T, width] slot
         if not self.wait_in_kernel:
             self.xchg.wait()
         return self._views[b]
@@ -256,6 +257,89 @@ class FusedShardedLinear:
 
     def close(self) -> None:
         self.xchg.close()
+
+
+class HostGatheredLinear:
+    """Row-sharded projection whose logits land in HOST memory: one pinned buffer shared by the ranks of a node (POSIX
+    shared memory, registered with CUDA in every process), into which every rank's GEMV kernel stores its shard
+    directly, so the logits cross as many PCIe links as there are GPUs and no copy follows the kernels. A decode step
+    that consumes its logits on the host (sampling) calls step(): activation in from pinned host memory, GEMV, stream
+    synchronise, then an epoch word per rank in the shared buffer tells every process when all shards are there. Two
+    logits buffers alternate: a rank cannot start step s + 2 before every rank has finished step s + 1, i.e. has
+    consumed the logits of step s. compute(x, out) replaces the GPU product in the CPU tests of the exchange."""
+
+    FLAG_STRIDE = 16  # int32 words between the ranks' epoch words (64 bytes: one cache line each)
+
+    def __init__(self, weight, rows_total: int, unit_rows: int, max_tokens: int, group=None, compute=None):
+        import mmap
+        import os
+        import uuid
+        self.w, self.group, self.compute = weight, group, compute
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.ranges = [unit_range(r, self.world, rows_total, unit_rows) for r in range(self.world)]
+        self.rows_total, self.T = rows_total, max_tokens
+        self.header = 4 * self.FLAG_STRIDE * 8
+        area = (max_tokens * rows_total * 4 + 255) // 256 * 256
+        nbytes = (self.header + 2 * area + 4095) // 4096 * 4096
+        name = [f"/dev/shm/bf16n_logits_{uuid.uuid4().hex}"] if self.rank == 0 else [None]
+        if self.rank == 0:
+            with open(name[0], "wb") as f:
+                f.truncate(nbytes)
+        if self.world > 1:
+            dist.broadcast_object_list(name, src=0, group=group)
+        self._fd = os.open(name[0], os.O_RDWR)
+        self._map = mmap.mmap(self._fd, nbytes)
+        if self.world > 1:
+            dist.barrier(group=group)  # every rank has the file open before its name goes away
+        if self.rank == 0:
+            os.unlink(name[0])
+        self._np = np.frombuffer(self._map, dtype=np.uint8)
+        self.flags = self._np[: self.header].view(np.int32)
+        self._registered = False
+        self._bufs = [torch.from_numpy(self._np[self.header + b * area: self.header + b * area + max_tokens * rows_total * 4]
+                                       .view(np.float32)).view(max_tokens, rows_total) for b in range(2)]
+        if compute is None:
+            rc = torch.cuda.cudart().cudaHostRegister(self._np.ctypes.data, nbytes, 1 | 2)  # portable | mapped
+            if int(rc) != 0:
+                raise RuntimeError(f"bf16n HostGatheredLinear: cudaHostRegister failed ({rc})")
+            self._registered = True
+        self.epoch = 0
+
+    def step(self, x_host: torch.Tensor, x_dev: torch.Tensor | None = None) -> torch.Tensor:
+        """x_host [T, K] pinned -> logits [T, rows_total] (host; valid until the step after the next one), complete in
+        every process when the call returns."""
+        a0, a1 = self.ranges[self.rank]
+        logits = self._bufs[self.epoch & 1]
+        mine = logits[:, a0:a1]
+        if self.compute is not None:
+            self.compute(x_host, mine)
+        else:
+            x_dev.copy_(x_host, non_blocking=True)
+            ops.mmv(x_dev, self.w, out=mine)
+            torch.cuda.current_stream().synchronize()
+        self.epoch += 1
+        self.flags[self.rank * self.FLAG_STRIDE] = self.epoch     # after the synchronise: this rank's shard is in host memory
+        for r in range(self.world):
+            spins = 0
+            while self.flags[r * self.FLAG_STRIDE] < self.epoch:
+                spins += 1
+                if spins > 50_000_000:
+                    raise RuntimeError(f"bf16n HostGatheredLinear: rank {r} never announced step {self.epoch}")
+        return logits
+
+    def close(self) -> None:
+        if self._registered:
+            torch.cuda.synchronize()
+            torch.cuda.cudart().cudaHostUnregister(self._np.ctypes.data)
+            self._registered = False
+        self._bufs = self.flags = self._np = None
+        try:
+            self._map.close()
+        except BufferError:
+            pass  # a view is still alive somewhere: the mapping goes with the process
+        import os
+        os.close(self._fd)
 
 
 # ------------------------------------------------------------------ MoE decode: expert-parallel + all-reduce

@@ -404,6 +404,13 @@ def test_mmv_large_matrix_path(ops, K, R, rows):
     x2, _ = act(2, K, seed=R + 1)
     y2 = ops.mmv(x2, enc, multi_col=False)
     assert torch.equal(y2[0:1], ops.mmv(x2[0:1], enc)) and torch.equal(y2[1:2], ops.mmv(x2[1:2], enc))
+    # 2..7 dense columns: groups of four and two share one decode (the ring kernel on the large shapes), same bits as
+    # one column at a time
+    x7, _ = act(7, K, seed=R + 2)
+    singles = torch.cat([ops.mmv(x7[i:i + 1], enc) for i in range(7)])
+    for T in (2, 3, 4, 7):
+        assert torch.equal(ops.mmv(x7[:T], enc), singles[:T])
+    assert ops.fault_status() == 0
 
 
 @pytest.mark.parametrize("rows", [20480, 40960])
