@@ -99,4 +99,21 @@ inline void swiglu(const float * g, const float * u, float * y, int64_t n, cudaS
     detail::raise(bf16n_swiglu(g, u, y, n, stream));
 }
 
+// draft-only k-bit output head (core/include/bf16n/draft_head.cuh:224-281; the reference declares these in
+// core/torch/torch_bindings.cpp:22-29 rather than in a header). sm_count is accepted for source compatibility.
+inline void int4_quantize(const void * w_bf16, int64_t rows, int K, uint8_t * q, float * s, cudaStream_t stream) {
+    detail::raise(bf16n_int4_quantize(w_bf16, rows, K, q, s, stream));
+}
+inline void int4_gemv(const void * x_bf16, int T, const uint8_t * q, const float * s, int64_t rows, int K, float * y, int /*sm_count*/,
+                      cudaStream_t stream) {
+    detail::raise(bf16n_int4_gemv(x_bf16, T, q, s, rows, K, y, stream));
+}
+inline void int2_quantize(const void * w_bf16, int64_t rows, int K, uint8_t * q, float * s, cudaStream_t stream) {
+    detail::raise(bf16n_int2_quantize(w_bf16, rows, K, q, s, stream));
+}
+inline void int2_gemv(const void * x_bf16, int T, const uint8_t * q, const float * s, int64_t rows, int K, float * y, int /*sm_count*/,
+                      cudaStream_t stream) {
+    detail::raise(bf16n_int2_gemv(x_bf16, T, q, s, rows, K, y, stream));
+}
+
 } // namespace bf16n

@@ -141,6 +141,18 @@ int bf16n_moe_combine(const float * ys, const void * w, int w_bf16, void * y, in
 /* y = silu(g) * u elementwise. Replaces bf16n::swiglu (launch.h:84, launch.cu:554-582). */
 int bf16n_swiglu(const float * g, const float * u, float * y, int64_t n, void * stream);
 
+/* Draft-only k-bit copies of an output head: q / s are a 4-bit (q [rows, K / 2], value + 8 per nibble, even column
+ * low) or 2-bit (q [rows, K / 4], level n of column c in bits 2 (c % 16) of 32-bit word c / 16, value (n - 1.5) s)
+ * copy of a BF16 matrix with one FP32 scale per 128 weights (s [rows, K / 128]); the GEMVs return approximate FP32
+ * scores y [T, rows] (T <= 4; int4: K 1024 / 2048 / 4096, int2: K = 2048) that only choose which rows the caller
+ * re-scores exactly. Same stored formats and argument rules as the reference. Replaces bf16n::int4_quantize /
+ * int4_gemv / int2_quantize / int2_gemv (core/include/bf16n/draft_head.cuh:224-281, declared at
+ * core/torch/torch_bindings.cpp:22-29; sm_count is taken from bf16n_init). */
+int bf16n_int4_quantize(const void * w_bf16, int64_t rows, int K, uint8_t * q, float * s, void * stream);
+int bf16n_int4_gemv(const void * x_bf16, int T, const uint8_t * q, const float * s, int64_t rows, int K, float * y, void * stream);
+int bf16n_int2_quantize(const void * w_bf16, int64_t rows, int K, uint8_t * q, float * s, void * stream);
+int bf16n_int2_gemv(const void * x_bf16, int T, const uint8_t * q, const float * s, int64_t rows, int K, float * y, void * stream);
+
 /* Router on the GPU: softmax over n_experts logits per token, the k largest (ties: lowest index), weights renormalised
  * to sum 1. The reference core takes ids and weights from its engines (tests/core/test_kernels.py:333-345 synthesise
  * them); this keeps the 1-4 token decode step on the device. logits FP32 [n_tok, n_experts]; ids int32 [n_tok, k];
@@ -186,6 +198,31 @@ int bf16n_moe_decode(const bf16n_weight * gate, const bf16n_weight * up, const b
 int bf16n_moe_decode_static(const bf16n_weight * gate, const bf16n_weight * up, const bf16n_weight * down, const void * x, int x_bf16,
                             int64_t x_tok, const float * router_logits, int n_experts, int32_t * topk_ids, float * topk_weights,
                             int n_tok, int n_used, int expert_lo, int n_experts_local, void * y, int y_bf16, void * stream);
+
+/* ---- loader side of the llama.cpp adapter -------------------------------------------------------------------------
+ * The engine-independent half of ggml-cuda/bf16n.cu (engines/llamacpp/patches/0002-ggml-cuda-thin-BF16N-adapter-over-
+ * the-shared-core.patch, patch lines 47-332): a registry keyed by the device address range of every converted tensor's
+ * plane, so that a tensor's data pointer, or a view that starts on a later row, finds its encoded matrix again.
+ * Load-time calls: they allocate and synchronise.
+ *
+ * choose   ggml's conversion ABI (patch lines 274-283, ggml_backend_cuda_bf16n_choose): 0 = stays BF16, 1 = NIBBLE,
+ *          2 = Huffman (pairs with single-symbol fallback), by the llama shape policy; mode "hybrid" | "huffman" | "nibble".
+ * convert  patch lines 285-332 (ggml_backend_cuda_bf16n_convert): encodes the host BF16 tensor [n_matrices,
+ *          rows_per_matrix, K] with the layout the llama policy picks for format_tag (1 or 2), copies the plane into
+ *          plane_dev (the tensor's own device storage, rows * K bytes), allocates the aux buffer, registers the range
+ *          for `owner` (the engine's buffer handle) and decodes every row on the device against the source in chunks
+ *          of at most 64 MiB; prints one line per tensor to stderr in the reference's format; *roundtrip_ok = 1 when
+ *          every weight came back bit-exact.
+ * lookup   patch lines 69-87: 1 and the matrix (by value) plus the first row of the view when `data` lies inside a
+ *          registered plane on a row boundary, else 0.
+ * release  patch lines 118-129 (ggml_cuda_bf16n_free): frees the aux buffers of everything `owner` registered; returns
+ *          how many. Call before the owning buffer is freed. */
+int bf16n_adapter_choose(int64_t rows, int64_t K, int64_t n_matrices, const char * mode, int64_t dense_min, int expert);
+int bf16n_adapter_convert(void * plane_dev, const void * bf16_host, int64_t K, int64_t rows_per_matrix, int64_t n_matrices,
+                          int format_tag, const void * owner, const char * name, int * roundtrip_ok);
+int bf16n_adapter_lookup(const void * data, bf16n_weight * out, int64_t * row0);
+int bf16n_adapter_release(const void * owner);
+int bf16n_adapter_count(void);
 
 /* ---- multi-GPU: outputs written straight into the other GPUs of the node ------------------------------------------
  * New: the reference is single-GPU and has nothing like this. A row-sharded projection normally ends with a collective

@@ -79,6 +79,16 @@ SIGNATURES = {
     "bf16n_peer_wait": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "bf16n_peer_expired": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
     "bf16n_set_peer_wait_limit_ms": (C.c_int, [C.c_uint]),
+    "bf16n_adapter_choose": (C.c_int, [C.c_int64, C.c_int64, C.c_int64, C.c_char_p, C.c_int64, C.c_int]),
+    "bf16n_adapter_convert": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_char_p,
+                                        C.POINTER(C.c_int)]),
+    "bf16n_adapter_lookup": (C.c_int, [C.c_void_p, C.POINTER(Weight), C.POINTER(C.c_int64)]),
+    "bf16n_adapter_release": (C.c_int, [C.c_void_p]),
+    "bf16n_adapter_count": (C.c_int, []),
+    "bf16n_int4_quantize": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "bf16n_int2_quantize": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "bf16n_int4_gemv": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]),
+    "bf16n_int2_gemv": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]),
     "bf16n_fault_status": (C.c_int, [C.POINTER(C.c_uint), C.c_void_p]),
 }
 

@@ -103,6 +103,7 @@ void check_x(const bf16n_weight & w, const bf16n_mmv_args & a) {
 } // namespace
 
 const DeviceInfo & device_info() { return g_info; }
+void set_last_error(const std::string & message) { g_error = message; }
 namespace dev { uint64_t peer_wait_limit_ns() { return g_peer_wait_ns.load(std::memory_order_relaxed); } }
 
 } // namespace b16
@@ -178,6 +179,19 @@ int bf16n_fault_status(unsigned int * flags, void * stream) {
         *flags = 0;
         for (int i = 0; i < 4; i++) { if (seen[i]) { *flags |= 1u << i; } }
     });
+}
+
+int bf16n_int4_quantize(const void * w_bf16, int64_t rows, int K, uint8_t * q, float * s, void * stream) {
+    return guarded([&] { ensure_init(); draft_quantize(4, w_bf16, rows, K, q, s, (cudaStream_t) stream); });
+}
+int bf16n_int2_quantize(const void * w_bf16, int64_t rows, int K, uint8_t * q, float * s, void * stream) {
+    return guarded([&] { ensure_init(); draft_quantize(2, w_bf16, rows, K, q, s, (cudaStream_t) stream); });
+}
+int bf16n_int4_gemv(const void * x_bf16, int T, const uint8_t * q, const float * s, int64_t rows, int K, float * y, void * stream) {
+    return guarded([&] { ensure_init(); draft_gemv(4, x_bf16, T, q, s, rows, K, y, (cudaStream_t) stream); });
+}
+int bf16n_int2_gemv(const void * x_bf16, int T, const uint8_t * q, const float * s, int64_t rows, int K, float * y, void * stream) {
+    return guarded([&] { ensure_init(); draft_gemv(2, x_bf16, T, q, s, rows, K, y, (cudaStream_t) stream); });
 }
 
 int bf16n_set_peer_wait_limit_ms(unsigned int ms) {

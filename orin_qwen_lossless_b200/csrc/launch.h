@@ -13,6 +13,8 @@
 
 namespace b16 {
 
+void set_last_error(const std::string & message); // what bf16n_last_error() returns on this thread (capi.cu)
+
 struct DeviceInfo { int sms = 0; int smem_optin = 0; };
 const DeviceInfo & device_info(); // filled by bf16n_init
 
@@ -112,6 +114,10 @@ size_t moe_decode_static_capacity_floats();
 void moe_decode_static(const bf16n_weight & gate, const bf16n_weight & up, const bf16n_weight & down, const void * x, bool x_bf16,
                        int64_t x_tok, const int32_t * ids, const float * weights, int n_tok, int n_used, int n_experts_local,
                        int e_lo, void * y, bool y_bf16, cudaStream_t st);
+
+// draft.cu: draft-only 2-bit / 4-bit copies of an output head
+void draft_quantize(int bits, const void * w_bf16, int64_t rows, int K, uint8_t * q, float * s, cudaStream_t st);
+void draft_gemv(int bits, const void * x_bf16, int T, const uint8_t * q, const float * s, int64_t rows, int K, float * y, cudaStream_t st);
 
 // prefill.cu
 void prefill_init();

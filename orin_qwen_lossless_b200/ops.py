@@ -406,6 +406,115 @@ def embedding(ids: torch.Tensor, w: Weight) -> torch.Tensor:
     return get_rows(ids.reshape(-1), w).view(*ids.shape, w.meta.K)
 
 
+# ------------------------------------------------------------------ device: draft-only k-bit output head
+# (engines/vllm/vllm_bf16n/ops.py:164-240 over core/torch/torch_bindings.cpp:241-295)
+
+def _kbit_quantize(w: torch.Tensor, bits: int) -> tuple[torch.Tensor, torch.Tensor]:
+    name = f"int{bits}_quantize"
+    if not (w.is_cuda and w.dtype == torch.bfloat16 and w.dim() == 2 and w.is_contiguous()):
+        raise RuntimeError(f"bf16n.{name}: w must be a contiguous 2-D CUDA bf16 tensor")
+    rows, K = w.shape
+    if K % 128:
+        raise ValueError(f"bf16n.{name}: K must be a multiple of 128")
+    q = torch.empty((rows, K * bits // 8), dtype=torch.uint8, device=w.device)
+    s = torch.empty((rows, K // 128), dtype=torch.float32, device=w.device)
+    with torch.cuda.device(w.device):
+        check(getattr(lib(), f"bf16n_{name}")(w.data_ptr(), rows, K, q.data_ptr(), s.data_ptr(), _stream()))
+    return q, s
+
+
+def _kbit_gemv(x: torch.Tensor, q: torch.Tensor, s: torch.Tensor, bits: int) -> torch.Tensor:
+    name = f"int{bits}_gemv"
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()):
+        raise RuntimeError(f"bf16n.{name}: x must be contiguous bf16 [T, K]")
+    T, K = x.shape
+    if not (q.is_cuda and q.dtype == torch.uint8 and q.dim() == 2 and q.is_contiguous() and q.shape[1] == K * bits // 8):
+        raise RuntimeError(f"bf16n.{name}: q must be uint8 [rows, K / {8 // bits}]")
+    if not (s.is_cuda and s.dtype == torch.float32 and s.is_contiguous() and tuple(s.shape) == (q.shape[0], K // 128)):
+        raise RuntimeError(f"bf16n.{name}: s must be f32 [rows, K / 128]")
+    y = torch.empty((T, q.shape[0]), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(getattr(lib(), f"bf16n_{name}")(x.data_ptr(), T, q.data_ptr(), s.data_ptr(), q.shape[0], K, y.data_ptr(), _stream()))
+    return y
+
+
+def int4_quantize(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Draft-only 4-bit copy of a BF16 matrix (symmetric, FP32 scale per 128 weights): (q uint8 [R, K/2], s f32 [R, K/128])."""
+    return _kbit_quantize(w, 4)
+
+
+def int4_gemv(x: torch.Tensor, q: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
+    """Approximate y = x W^T (FP32 [T, R]) from the 4-bit copy; T <= 4."""
+    return _kbit_gemv(x, q, s, 4)
+
+
+def int2_quantize(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Draft-only 2-bit copy of a BF16 matrix: per 128 weights s = amax / 1.5 and each weight the nearest of
+    -1.5 s, -0.5 s, 0.5 s, 1.5 s: (q uint8 [R, K/4], s f32 [R, K/128])."""
+    return _kbit_quantize(w, 2)
+
+
+def int2_gemv(x: torch.Tensor, q: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
+    """Approximate y = x W^T (FP32 [T, R]) from the 2-bit copy; T <= 4, K = 2048."""
+    return _kbit_gemv(x, q, s, 2)
+
+
+DRAFT_HEADS = {"int2": 2, "int4": 4}      # BF16N_DRAFT_HEAD values with a k-bit copy; "full" scores with the exact head
+DEFAULT_CANDIDATES = {2: 128, 4: 32}      # candidates re-scored exactly (the reference's measured defaults, ops.py:187-191)
+
+
+@dataclass(frozen=True)
+class DraftHead:
+    """Draft-only k-bit copy of an output head whose top `candidates` scores are re-scored exactly by draft_logits."""
+    bits: int
+    q: torch.Tensor
+    s: torch.Tensor
+    candidates: int
+
+    def __post_init__(self):
+        if self.bits not in DEFAULT_CANDIDATES:
+            raise ValueError(f"draft head: {self.bits} bits (2 or 4)")
+        if self.q.shape[1] * (8 // self.bits) != self.s.shape[1] * 128 or self.q.shape[0] != self.s.shape[0]:
+            raise ValueError(f"draft head: q {tuple(self.q.shape)} and s {tuple(self.s.shape)} disagree for {self.bits} bits")
+        if not 1 <= self.candidates <= self.q.shape[0]:
+            raise ValueError(f"draft head: {self.candidates} candidates for {self.q.shape[0]} rows")
+
+    def scores(self, h: torch.Tensor) -> torch.Tensor:
+        return (int2_gemv if self.bits == 2 else int4_gemv)(h, self.q, self.s)
+
+
+def draft_head_bits() -> int | None:
+    """Bits of the draft head chosen by BF16N_DRAFT_HEAD (int2 by default, int4; full = the exact head, None). Read by
+    the engine layer when it builds the head, never by a launch."""
+    import os
+    v = os.environ.get("BF16N_DRAFT_HEAD", "int2")
+    if v == "full":
+        return None
+    if v not in DRAFT_HEADS:
+        raise ValueError(f"BF16N_DRAFT_HEAD must be one of int2, int4, full; got {v!r}")
+    return DRAFT_HEADS[v]
+
+
+def make_draft_head(w: torch.Tensor, bits: int) -> DraftHead:
+    """The k-bit draft copy of BF16 w with BF16N_DRAFT_CANDIDATES candidates (default per bits)."""
+    import os
+    q, s = (int2_quantize if bits == 2 else int4_quantize)(w)
+    env = os.environ.get("BF16N_DRAFT_CANDIDATES")
+    return DraftHead(bits, q, s, int(env) if env is not None else DEFAULT_CANDIDATES[bits])
+
+
+def draft_logits(h: torch.Tensor, w: Weight, head: DraftHead, vocab: int) -> torch.Tensor:
+    """Draft-token logits: the k-bit head selects candidates, the gathered lossless rows are re-scored in FP32, every
+    other entry is -inf. A proposal path: candidate coverage does not guarantee the exact head's argmax."""
+    n, K = h.shape
+    h = h.contiguous()
+    cand = head.scores(h).topk(head.candidates, dim=-1).indices                   # [n, C]
+    rows = get_rows(cand.reshape(-1), w).view(n, head.candidates, K)              # exact BF16 rows
+    exact = torch.einsum("nck,nk->nc", rows.float(), h.float())
+    out = torch.full((n, vocab), float("-inf"), dtype=torch.float32, device=h.device)
+    return out.scatter_(1, cand, exact)
+
+
 # ------------------------------------------------------------------ device: MoE
 
 def mm_ids_supported(w: Weight, up: Weight | None = None) -> bool:

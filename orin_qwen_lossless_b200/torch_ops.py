@@ -2,10 +2,10 @@
 registered here with `torch.library` on top of the C ABI, so that code written against the reference's ops (its vLLM
 plugin, its tests) finds the same names, schemas, argument meaning and error types.
 
-Schemas are the reference's, character for character, for the ops of this path: init, encode, dequant, mmv, mmv_glu,
-linear, get_rows, moe_mm_ids, moe_combine, swiglu. `int[] meta` is [format, K, rows, R, flags, off_a, off_b, off_c,
-off_d] (torch_bindings.cpp:7). The lossy draft-head ops (int4_* / int2_*) are not part of this path and are not
-defined. Fake (meta) implementations follow vllm_bf16n/ops.py:292-369 so that the ops trace under torch.compile.
+Schemas are the reference's, character for character, for all fourteen ops: init, encode, dequant, mmv, mmv_glu,
+linear, get_rows, moe_mm_ids, moe_combine, swiglu and the draft-head ops int4_quantize, int4_gemv, int2_quantize,
+int2_gemv. `int[] meta` is [format, K, rows, R, flags, off_a, off_b, off_c, off_d] (torch_bindings.cpp:7). Fake (meta)
+implementations follow vllm_bf16n/ops.py:292-369 so that the ops trace under torch.compile.
 
 Importing this module registers the library once per process; it does not initialise CUDA.
 """
@@ -27,6 +27,10 @@ _SCHEMAS = (
     "int[] up_meta, int n_experts, bool out_bf16) -> Tensor",
     "moe_combine(Tensor ys, Tensor topk_weights, bool out_bf16) -> Tensor",
     "swiglu(Tensor g, Tensor u) -> Tensor",
+    "int4_quantize(Tensor w) -> (Tensor, Tensor)",
+    "int4_gemv(Tensor x, Tensor q, Tensor s) -> Tensor",
+    "int2_quantize(Tensor w) -> (Tensor, Tensor)",
+    "int2_gemv(Tensor x, Tensor q, Tensor s) -> Tensor",
 )
 
 _lib = torch.library.Library("bf16n", "DEF")
@@ -94,7 +98,9 @@ def _swiglu(g, u):
 _lib.impl("init", _init, "CompositeExplicitAutograd")
 _lib.impl("encode", _encode_cpu, "CPU")
 for _name, _fn in (("dequant", _dequant), ("mmv", _mmv), ("mmv_glu", _mmv_glu), ("linear", _linear), ("get_rows", _get_rows),
-                   ("moe_mm_ids", _moe_mm_ids), ("moe_combine", _moe_combine), ("swiglu", _swiglu)):
+                   ("moe_mm_ids", _moe_mm_ids), ("moe_combine", _moe_combine), ("swiglu", _swiglu),
+                   ("int4_quantize", ops.int4_quantize), ("int4_gemv", ops.int4_gemv), ("int2_quantize", ops.int2_quantize),
+                   ("int2_gemv", ops.int2_gemv)):
     _lib.impl(_name, _fn, "CUDA")
 
 
@@ -153,3 +159,23 @@ def _moe_combine_fake(ys, topk_weights, out_bf16):
 @torch.library.register_fake("bf16n::swiglu")
 def _swiglu_fake(g, u):
     return torch.empty_like(g)
+
+
+@torch.library.register_fake("bf16n::int4_quantize")
+def _int4_quantize_fake(w):
+    return w.new_empty((w.shape[0], w.shape[1] // 2), dtype=torch.uint8), w.new_empty((w.shape[0], w.shape[1] // 128), dtype=torch.float32)
+
+
+@torch.library.register_fake("bf16n::int2_quantize")
+def _int2_quantize_fake(w):
+    return w.new_empty((w.shape[0], w.shape[1] // 4), dtype=torch.uint8), w.new_empty((w.shape[0], w.shape[1] // 128), dtype=torch.float32)
+
+
+@torch.library.register_fake("bf16n::int4_gemv")
+def _int4_gemv_fake(x, q, s):
+    return x.new_empty((x.shape[0], q.shape[0]), dtype=torch.float32)
+
+
+@torch.library.register_fake("bf16n::int2_gemv")
+def _int2_gemv_fake(x, q, s):
+    return x.new_empty((x.shape[0], q.shape[0]), dtype=torch.float32)

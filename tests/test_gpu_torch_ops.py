@@ -1,7 +1,7 @@
 """`torch.ops.bf16n` on the GPU: torch.library.opcheck on every op (schema, fake kernels against the real ones,
 AOT dispatch with dynamic shapes), equality with the `ops` functions underneath, and CUDA-graph capture of a
 decode-like step replaying bitwise what eager execution computes after the inputs change in place. Mirrors the
-reference's tests/core/test_opcheck.py and tests/core/test_graphs.py (without the fragment-order and draft-head cases)."""
+reference's tests/core/test_opcheck.py and tests/core/test_graphs.py (without the fragment-order cases)."""
 import pytest
 import torch
 
@@ -39,6 +39,7 @@ def cases(m):
     a12 = torch.randn(12, TOPK, 512, generator=g).to(torch.bfloat16).cuda()
     ids = torch.stack([torch.randperm(E, generator=g)[:TOPK] for _ in range(12)]).to(torch.int32).cuda()
     hp, nib, gate, up, down = m["hp"], m["nib"], m["gate"], m["up"], m["down"]
+    w2 = to_bf16_tensor(o.weights_like(64, 2048, 9)).cuda()
     return {
         "dequant": (b.dequant, (hp.plane, hp.aux, hp.m, 16, 32)),
         "mmv_dense": (b.mmv, (x4, hp.plane, hp.aux, hp.m, None, 0, True)),
@@ -51,11 +52,15 @@ def cases(m):
         "moe_mm_ids_down": (b.moe_mm_ids, (a12, ids, down.plane, down.aux, down.m, None, None, [], E, False)),
         "moe_combine": (b.moe_combine, (torch.randn(12, TOPK, 2048, device="cuda"), torch.rand(12, TOPK, device="cuda"), True)),
         "swiglu": (b.swiglu, (torch.randn(12, TOPK, 512, device="cuda"), torch.randn(12, TOPK, 512, device="cuda"))),
+        "int2_quantize": (b.int2_quantize, (w2,)),
+        "int2_gemv": (b.int2_gemv, (x4[:1], *b.int2_quantize(w2))),
+        "int4_quantize": (b.int4_quantize, (w2,)),
+        "int4_gemv": (b.int4_gemv, (x4[:1], *b.int4_quantize(w2))),
     }
 
 
 NAMES = ["dequant", "mmv_dense", "mmv_ids", "mmv_glu", "linear_gemv", "linear_gemm", "get_rows", "moe_mm_ids_glu",
-         "moe_mm_ids_down", "moe_combine", "swiglu"]
+         "moe_mm_ids_down", "moe_combine", "swiglu", "int2_quantize", "int2_gemv", "int4_quantize", "int4_gemv"]
 
 
 @pytest.mark.parametrize("name", NAMES)

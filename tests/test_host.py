@@ -147,3 +147,18 @@ int main() {
                     lib, "-Wl,-rpath," + os.path.dirname(lib)], check=True)
     out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
     assert out == ["8192", "3", "16", "1"]
+
+
+def test_adapter_choose_follows_the_llama_policy(policy_table):
+    """ggml's conversion tags from the loader entry point of the llama.cpp adapter: 0 stays BF16, 1 NIBBLE, 2 Huffman
+    (pairs with single-symbol fallback), for every llama row of the reference's policy table."""
+    from orin_qwen_lossless_b200._lib import lib
+    n_checked = 0
+    for rows, K, n, engine, mode, expert, dfo, want in policy_table:
+        if engine != "llama" or dfo:
+            continue
+        tag = lib().bf16n_adapter_choose(rows, K, n, mode.encode(), 8 << 20, expert)
+        assert tag == (0 if want is None else 1 if want[0] == 1 else 2), (rows, K, n, mode, expert, want)
+        n_checked += 1
+    assert n_checked > 100
+    assert lib().bf16n_adapter_count() == 0

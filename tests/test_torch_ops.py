@@ -28,6 +28,10 @@ def test_schemas_match_the_reference(b):
                       "Tensor? up_aux, int[] up_meta, int n_experts, bool out_bf16) -> Tensor",
         "moe_combine": "bf16n::moe_combine(Tensor ys, Tensor topk_weights, bool out_bf16) -> Tensor",
         "swiglu": "bf16n::swiglu(Tensor g, Tensor u) -> Tensor",
+        "int4_quantize": "bf16n::int4_quantize(Tensor w) -> (Tensor, Tensor)",
+        "int4_gemv": "bf16n::int4_gemv(Tensor x, Tensor q, Tensor s) -> Tensor",
+        "int2_quantize": "bf16n::int2_quantize(Tensor w) -> (Tensor, Tensor)",
+        "int2_gemv": "bf16n::int2_gemv(Tensor x, Tensor q, Tensor s) -> Tensor",
     }
     for name, schema in want.items():
         assert str(getattr(b, name).default._schema) == schema
