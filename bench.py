@@ -216,8 +216,11 @@ def run_ours(args):
     t0 = time.perf_counter()
     w = gen_rows(r0, r1)
     t_gen = time.perf_counter() - t0
+    # rows per unit as the shape policy picks them for this rank's matrix on this machine (SMs x 24 warps must have a
+    # unit each): 16 for the whole projection and its halves and quarters, 8 for an eighth
+    shard_R = ops.choose(r1 - r0, K, engine="llama", mode="huffman", min_units=ops.sm_count() * 24)[1]
     t0 = time.perf_counter()
-    plane, aux, meta = ops.encode(w, ops.FMT_HUFPAIR, R, False)
+    plane, aux, meta = ops.encode(w, ops.FMT_HUFPAIR, shard_R, False)
     t_enc = time.perf_counter() - t0
     enc = ops.upload(plane, aux, meta, dev)
     ok = ops.roundtrip_equal(enc, w)  # verify at load: bit-exact decode of the whole shard on the GPU
@@ -414,6 +417,12 @@ def run_ours(args):
             parity["e2e_max_err_over_sum_abs"] = float((np.abs(got_h - y64) / s).max())
 
     expired = fused.xchg.expired() if fused else False
+    exchange_timing = None
+    if fused:
+        mine_t = fused.xchg.timing()
+        gathered_t = [None] * world
+        dist.all_gather_object(gathered_t, mine_t)
+        exchange_timing = gathered_t
     faults = ops.fault_status()
     fused_used, hosted_used = fused is not None, hosted is not None
     fused_width = fused.width if fused else width
@@ -450,7 +459,7 @@ def run_ours(args):
         "value": algo_bytes / (ms_step * 1e-3) / 1e9, "unit": "GB/s",
         "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"lm_head {rows}x{K} HUFPAIR R={R}, batch-1 decode GEMV, BF16 activation, FP32 logits"
+        "config": {"workload": f"lm_head {rows}x{K} HUFPAIR R={shard_R}, batch-1 decode GEMV, BF16 activation, FP32 logits"
                                + (f", rows sharded over {world} GPUs, logits stored into every GPU's buffer by the GEMV kernel "
                                   "(peer stores + epoch flags, no collective)" if fused_used else
                                   f", rows sharded over {world} GPUs + NCCL all-gather ({fused_note})" if world > 1 else ""),
@@ -474,6 +483,8 @@ def run_ours(args):
                         "activation copied in, gathered logits copied out behind the kernel") + ", stream synchronised every step"},
         "gpu_launches": steps,   # one kernel per step at every N
         "nccl_allgather_us_per_step": nccl_us,
+        "kernel_alone_us": kernel_ms * 1e3,
+        "exchange_timing_last_step_per_rank": exchange_timing,
         "cublas_bf16_gemv_us": cublas_us,
         "vs_cublas_bf16_gemv": cublas_us / (kernel_ms * 1e3),
         "multi_token": multi_tok,
@@ -789,18 +800,31 @@ def small_block(args, torch, ops, dev):
     x2048 = torch.randn(1, 2048, device=dev).to(torch.bfloat16)
     outs = [[torch.empty(1, w.meta.rows, device=dev) for w in ws] for ws in layers]
 
-    def step():
+    def step_one_by_one():
         for ws, ys in zip(layers, outs):
             ops.mmv(x512, ws[0], out=ys[0]); ops.mmv(x2048, ws[1], out=ys[1]); ops.mmv(x2048, ws[2], out=ys[2])
 
+    xs3 = [x512, x2048, x2048]
+
+    def step():   # the three products of a layer are independent: one grid serves them (48 launches per graph)
+        for ws, ys in zip(layers, outs):
+            ops.mmv_group(xs3, ws, ys)
+
+    us1, _, _ = _time_graph(torch, step_one_by_one, args.steps // 10)
+    torch.cuda.synchronize()
+    singles = [[y.clone() for y in ys] for ys in outs]
     us, lo, hi = _time_graph(torch, step, args.steps // 10)
+    torch.cuda.synchronize()
+    same = all(torch.equal(a, b) for ya, yb in zip(singles, outs) for a, b in zip(ya, yb))
     peak, _ = measured_peak()
     worst = 0.0
     for wsrc, xv, yv in zip(first, (x512, x2048, x2048), outs[0]):   # FP64 check of the first layer's three products
         y64, sabs = o.gemv_f64(_bits(wsrc), o.bf16_bits_to_f32(_bits(xv.cpu())[0]))
         worst = max(worst, float((np.abs(yv[0].cpu().numpy() - y64) / sabs).max()))
-    return {"workload": "small matrices: 48 layers x {2048x512, 512x2048, 256x2048} NIBBLE, batch-1, one CUDA graph of 144 GEMVs",
-            "us_per_graph": us, "us_min": lo, "us_max": hi, "us_per_gemv": us / 144, "compressed_bytes": nbytes, "GBps": nbytes / us / 1e3,
+    return {"workload": "small matrices: 48 layers x {2048x512, 512x2048, 256x2048} NIBBLE, batch-1, 144 GEMVs per CUDA graph, "
+                        "the three independent products of a layer in one launch (bf16n_mmv_group)",
+            "us_per_graph": us, "us_min": lo, "us_max": hi, "us_per_gemv": us / 144, "launches_per_graph": 48,
+            "us_per_graph_one_launch_per_gemv": us1, "grouped_bitwise_equal_to_single_launches": bool(same), "compressed_bytes": nbytes, "GBps": nbytes / us / 1e3,
             "frac_of_measured_hbm": nbytes / us / 1e3 / peak, "l2": "191 MB of weights per replay > L2",
             "parity": {"max_err_over_sum_abs": worst, "what": "first layer's three GEMVs against FP64"}}
 

@@ -82,6 +82,13 @@ int bf16n_parse_header(const uint8_t * aux_host, size_t nbytes, bf16n_weight * w
 int bf16n_choose(int64_t rows, int64_t K, int64_t n_matrices, int engine, int mode, int64_t dense_min, int expert,
                  int dense_frag_order, int out[4]);
 
+/* bf16n_choose with the machine size as an argument: a dense pair-Huffman matrix keeps at least min_units units (the
+ * reference hard-codes 512, the warps of the GPU it was written for; bf16n_choose keeps that constant and its tables).
+ * A loader that splits a matrix over several B200s asks with min_units of the order of SMs x warps per SM (e.g.
+ * 148 x 24), so that a small shard gets shorter units and still fills the machine. */
+int bf16n_choose_for_machine(int64_t rows, int64_t K, int64_t n_matrices, int engine, int mode, int64_t dense_min, int expert,
+                             int dense_frag_order, int64_t min_units, int out[4]);
+
 /* ---- device side ---------------------------------------------------------------------------------------------- */
 
 /* Once per process, with the process's GPU current, before the first launch and before any graph capture: device
@@ -106,6 +113,12 @@ int bf16n_fault_status(unsigned int * flags, void * stream);
 /* GEMV (<= a few columns), dense or routed by expert ids. multi_col != 0: dense batches of 2..4 columns decode the
  * matrix once per group of 4. Replaces bf16n::mmv (launch.h:50, launch.cu:313-325). */
 int bf16n_mmv(const bf16n_weight * w, const bf16n_mmv_args * a, void * stream, int multi_col);
+/* n independent products on one stream, w[i] with a[i]: the small dense NIBBLE products among them (K 512..4096, up to
+ * 8 columns; the per-layer projections and routers that are each too small to fill the GPU) share one grid, eight
+ * products per launch, instead of one launch each; everything else is launched as bf16n_mmv would launch it. Results
+ * are the bits bf16n_mmv gives for each product. The reference launches every product on its own
+ * (core/src/launch.cu:313-325); this is the B200 answer to its launch-bound small-matrix path. */
+int bf16n_mmv_group(const bf16n_weight * w, const bf16n_mmv_args * a, int n, void * stream);
 /* y = silu(gate x) * (up x) for a NIBBLE matrix whose rows_per_matrix rows are [gate (nrows); up (nrows)].
  * Replaces bf16n::mmv_glu(w, a, stream) (launch.h:53, launch.cu:327-339). */
 int bf16n_mmv_glu_merged(const bf16n_weight * w, const bf16n_mmv_args * a, void * stream);
@@ -232,7 +245,9 @@ int bf16n_adapter_count(void);
  * collective. No multicast, no library collective on this path.
  *
  * An exchange buffer is [256-byte header | payload]. Header words (uint32): 0..7 epoch announced by rank r (written by
- * rank r), 16 finished-block counter, 17 epochs sent, 18 epochs waited for, 19 set when a wait expired. The counters
+ * rank r), 16 finished-block counter, 17 epochs sent, 18 epochs waited for, 19 set when a wait expired; diagnostics of
+ * the last fan-out launch as 64-bit %globaltimer nanoseconds of this GPU: words 20-21 its first block began, 22-23 the
+ * last block saw every block's stores issued, 24-25 the epoch was published, 26-27 every awaited peer's epoch was seen. The counters
  * live on the device, so launches captured in a CUDA graph keep working when replayed; every rank must issue the same
  * sequence of fan-out launches and waits. Use two payload areas in turn when a step may start before every peer has
  * consumed the previous one. */

@@ -46,9 +46,12 @@ SIGNATURES = {
     "bf16n_encoded_free": (None, [C.c_void_p]),
     "bf16n_parse_header": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(Weight)]),
     "bf16n_choose": (C.c_int, [C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_int64, C.c_int, C.c_int, C.POINTER(C.c_int)]),
+    "bf16n_choose_for_machine": (C.c_int, [C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int64,
+                                           C.POINTER(C.c_int)]),
     "bf16n_init": (C.c_int, []),
     "bf16n_sm_count": (C.c_int, [C.POINTER(C.c_int)]),
     "bf16n_mmv": (C.c_int, [C.POINTER(Weight), C.POINTER(MmvArgs), C.c_void_p, C.c_int]),
+    "bf16n_mmv_group": (C.c_int, [C.POINTER(Weight), C.POINTER(MmvArgs), C.c_int, C.c_void_p]),
     "bf16n_mmv_glu_merged": (C.c_int, [C.POINTER(Weight), C.POINTER(MmvArgs), C.c_void_p]),
     "bf16n_mmv_glu": (C.c_int, [C.POINTER(Weight), C.POINTER(Weight), C.POINTER(MmvArgs), C.c_void_p]),
     "bf16n_dequant": (C.c_int, [C.POINTER(Weight), C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),

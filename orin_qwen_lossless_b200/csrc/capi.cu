@@ -163,6 +163,19 @@ int bf16n_choose(int64_t rows, int64_t K, int64_t n_matrices, int engine, int mo
     return 1;
 }
 
+int bf16n_choose_for_machine(int64_t rows, int64_t K, int64_t n_matrices, int engine, int mode, int64_t dense_min, int expert,
+                             int dense_frag_order, int64_t min_units, int out[4]) {
+    PolicyOptions o;
+    o.engine = engine ? Engine::vllm : Engine::llama;
+    o.mode = mode == 1 ? Mode::huffman : mode == 2 ? Mode::nibble : Mode::hybrid;
+    o.dense_min = dense_min; o.expert = expert != 0; o.dense_frag_order = dense_frag_order != 0;
+    o.min_units = min_units;
+    PolicyChoice c;
+    if (!choose(rows, K, n_matrices, o, &c)) { return 0; }
+    out[0] = c.format; out[1] = c.R; out[2] = c.chunk_major; out[3] = c.frag_order;
+    return 1;
+}
+
 int bf16n_init(void) { return guarded([] { ensure_init(); }); }
 
 int bf16n_fault_status(unsigned int * flags, void * stream) {
@@ -213,6 +226,31 @@ int bf16n_mmv(const bf16n_weight * w, const bf16n_mmv_args * a, void * stream, i
         if (frag_order(*w)) { fo_gemv(*w, *a, (cudaStream_t) stream); return; }
         if (expert_units_applies(*w, *a)) { expert_units_mmv(*w, *a, (cudaStream_t) stream); return; }
         gemv(*w, *a, (cudaStream_t) stream, multi_col != 0);
+    });
+}
+
+int bf16n_mmv_group(const bf16n_weight * w, const bf16n_mmv_args * a, int n, void * stream) {
+    return guarded([&] {
+        ensure_init();
+        require(n >= 0 && (n == 0 || (w && a)), "mmv_group: null argument");
+        for (int i = 0; i < n; i++) {
+            check_weight(w[i]);
+            require(a[i].ncols > 0 && a[i].ncols <= 65535, "ncols out of range");
+            whole_units(w[i], a[i]);
+            check_x(w[i], a[i]);
+        }
+        cudaStream_t st = (cudaStream_t) stream;
+        for (int i = 0; i < n;) {
+            int j = i;
+            while (j < n && gemv_groupable(w[j], a[j])) { j++; }
+            if (j > i) { gemv_group(w + i, a + i, j - i, st); i = j; continue; }
+            if (a[i].nrows != 0) { // not a small dense NIBBLE product: launched as bf16n_mmv launches it
+                if (frag_order(w[i])) { fo_gemv(w[i], a[i], st); }
+                else if (expert_units_applies(w[i], a[i])) { expert_units_mmv(w[i], a[i], st); }
+                else { gemv(w[i], a[i], st, true); }
+            }
+            i++;
+        }
     });
 }
 

@@ -96,6 +96,9 @@ struct PeerOut {
     uint64_t wait_ns;             // how long that wait may take before the header's expired word is set (bf16n_set_peer_wait_limit_ms)
 };
 constexpr int XH_DONE = 16, XH_SENT = 17, XH_WAITED = 18, XH_EXPIRED = 19; // header words (0..7: the peers' flags)
+// diagnostics of the last fan-out launch, %globaltimer nanoseconds of this GPU (64-bit, two words each): block 0 began,
+// the last block saw every block's stores issued, the epoch was published to the peers, every peer's epoch was seen
+constexpr int XH_T_BEGIN = 20, XH_T_STORED = 22, XH_T_PUBLISHED = 24, XH_T_SEEN = 26;
 
 struct Cols {
     const char * x; char * y;
@@ -121,45 +124,64 @@ __device__ __forceinline__ void peers_put(const Cols & c, int col, int64_t i, fl
 // End of a kernel that fans out: call with every thread of the block that is still running. Each block makes its
 // stores visible system-wide and counts itself; the last one advances this rank's epoch and publishes it to the peers
 // (release), whose bf16n_peer_wait acquires it.
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// start of a kernel that fans out: block 0 records when the launch began (header words 20, 21: diagnostics only)
+__device__ __forceinline__ void peers_begin(const PeerOut & o) {
+    if (o.n && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) { *(volatile uint64_t *) (o.hdr + XH_T_BEGIN) = global_ns(); }
+}
 __device__ __forceinline__ void peers_done(const PeerOut & o) {
     if (o.n == 0) { return; }
+    __shared__ uint32_t last_epoch; // 0: this block is not the last one
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence_system();
         const unsigned blocks = gridDim.x * gridDim.y * gridDim.z;
+        uint32_t epoch = 0;
         if (atomicAdd(o.hdr + XH_DONE, 1u) == blocks - 1u) {
             o.hdr[XH_DONE] = 0u;
-            const uint32_t epoch = o.hdr[XH_SENT] + 1u;
+            epoch = o.hdr[XH_SENT] + 1u;
             o.hdr[XH_SENT] = epoch;
+            *(volatile uint64_t *) (o.hdr + XH_T_STORED) = global_ns();
             __threadfence_system();
             for (int r = 0; r < o.n; r++) {
                 asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(o.flag[r]), "r"(epoch) : "memory");
             }
-            // Optionally the kernel also stands in for the consumer's wait: it ends only when the peers' outputs of the
-            // same epoch have arrived here. A peer publishes before it waits, so no rank waits for a rank that waits
-            // for it. Bounded: after wait_ns (two seconds by default) the header's expired word is set and the kernel ends anyway.
-            if (o.wait_mask) {
-                uint64_t t0 = 0;
-                bool all = false;
-                for (uint32_t i = 0; i < (1u << 26) && !all; i++) {
-                    all = true;
-                    for (int r = 0; r < 8; r++) {
-                        if (o.wait_mask >> r & 1) {
-                            uint32_t seen;
-                            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(o.hdr + r) : "memory");
-                            all = all && (int32_t) (seen - epoch) >= 0;
-                        }
-                    }
-                    if (!all && (i & 1023u) == 1023u) {
-                        uint64_t now;
-                        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-                        if (t0 == 0) { t0 = now; } else if (now - t0 > o.wait_ns) { break; }
-                    }
+            *(volatile uint64_t *) (o.hdr + XH_T_PUBLISHED) = global_ns();
+        }
+        last_epoch = o.wait_mask ? epoch : 0u;
+    }
+    __syncthreads();
+    // Optionally the kernel also stands in for the consumer's wait: it ends only when the peers' outputs of the same
+    // epoch have arrived here. A peer publishes before it waits, so no rank waits for a rank that waits for it. One
+    // thread per peer polls that peer's word (local memory); bounded: after wait_ns (two seconds by default) the
+    // header's expired word is set and the kernel ends anyway.
+    const uint32_t epoch = last_epoch;
+    if (epoch != 0u && threadIdx.x < 32) {
+        const int r = threadIdx.x;
+        bool ok = true;
+        if (r < 8 && (o.wait_mask >> r & 1)) {
+            ok = false;
+            uint64_t t0 = 0;
+            for (uint32_t i = 0; i < (1u << 26); i++) {
+                uint32_t seen;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(o.hdr + r) : "memory");
+                if ((int32_t) (seen - epoch) >= 0) { ok = true; break; }
+                if ((i & 255u) == 255u) {
+                    const uint64_t now = global_ns();
+                    if (t0 == 0) { t0 = now; } else if (now - t0 > o.wait_ns) { break; }
                 }
-                if (!all) { o.hdr[XH_EXPIRED] = 1u; }
-                o.hdr[XH_WAITED] = epoch;
-                __threadfence_system();
             }
+        }
+        const bool all = __all_sync(FULL, ok);
+        if (r == 0) {
+            if (!all) { o.hdr[XH_EXPIRED] = 1u; }
+            o.hdr[XH_WAITED] = epoch;
+            *(volatile uint64_t *) (o.hdr + XH_T_SEEN) = global_ns();
+            __threadfence_system();
         }
     }
 }

@@ -683,6 +683,92 @@ void gemv(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st, boo
     if (a.x_bf16) { launch_gemv<bf16>(w, a, st, multi_col, peers); } else { launch_gemv<float>(w, a, st, multi_col, peers); }
 }
 
+// ---------------------------------------------------------------- several independent small products in one launch
+
+namespace {
+
+constexpr int GROUP_MAX = 8;
+struct NibItem { // one dense NIBBLE product of a group
+    NibView v;
+    const char * x; char * y;
+    int64_t x_tok, y_tok, row0, nrows;
+    int ncols, chunks, first_block, blocks; // blocks [first_block, first_block + blocks) of the grid serve this item
+    bool x_bf16, y_bf16;
+};
+struct NibGroup { int n; NibItem item[GROUP_MAX]; };
+
+template <int C, typename TX>
+__device__ __forceinline__ void nib_item_rows(const NibItem & it, int block, int col) {
+    const TX * xg = (const TX *) (it.x + col * it.x_tok);
+    const OutVec out = {it.y + col * it.y_tok, it.y_bf16};
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    bool waited = false;
+    for (int64_t r = (int64_t) block * 8 + warp; r < it.nrows; r += (int64_t) it.blocks * 8) {
+        NibRow<C> d;
+        nib_load<C>(d, it.v, it.row0 + r, lane);
+        if (!waited) { grid_dependency_wait(); waited = true; } // weights first, then the activations an earlier kernel may have written
+        const float s = nib_dot<C, TX>(d, it.v, xg, lane);
+        if (lane == 0) { out.put(r, s); }
+    }
+    if (!waited) { grid_dependency_wait(); }
+}
+
+// Every block belongs to one item of the group (a prefix table of block ranges); within its item it is a block of the
+// single-product kernel: same loads, same order of operations, so the results are the same bits.
+__global__ void __launch_bounds__(256) k_nib_gemv_group(const NibGroup g) {
+    int m = 0;
+    while (m + 1 < g.n && (int) blockIdx.x >= g.item[m + 1].first_block) { m++; }
+    const NibItem & it = g.item[m];
+    const int local = (int) blockIdx.x - it.first_block;
+    const int col = local / (it.blocks / it.ncols), block = local % (it.blocks / it.ncols);
+    NibItem one = it;
+    one.blocks = it.blocks / it.ncols;
+    const int key = it.chunks * 2 + (it.x_bf16 ? 1 : 0);
+    switch (key) {
+        case 2: nib_item_rows<1, float>(one, block, col); break;
+        case 3: nib_item_rows<1, bf16>(one, block, col); break;
+        case 4: nib_item_rows<2, float>(one, block, col); break;
+        case 5: nib_item_rows<2, bf16>(one, block, col); break;
+        case 8: nib_item_rows<4, float>(one, block, col); break;
+        case 9: nib_item_rows<4, bf16>(one, block, col); break;
+        case 16: nib_item_rows<8, float>(one, block, col); break;
+        case 17: nib_item_rows<8, bf16>(one, block, col); break;
+        default: grid_dependency_wait(); break;
+    }
+}
+
+} // namespace
+
+// dense NIBBLE products of up to 8 columns can share a grid
+bool gemv_groupable(const bf16n_weight & w, const bf16n_mmv_args & a) {
+    const int C = (int) (w.K / CHUNK);
+    return w.format == FMT_NIBBLE && !a.ids && a.nrows > 0 && a.ncols >= 1 && a.ncols <= 8 && (C == 1 || C == 2 || C == 4 || C == 8);
+}
+
+// n independent groupable products (different matrices, activations and outputs) on one stream: one grid per eight.
+void gemv_group(const bf16n_weight * w, const bf16n_mmv_args * a, int n, cudaStream_t st) {
+    int i = 0;
+    while (i < n) {
+        NibGroup g = {};
+        int blocks = 0;
+        while (i < n && g.n < GROUP_MAX) {
+            NibItem & it = g.item[g.n++];
+            it.v = nib_view(w[i]);
+            it.x = (const char *) a[i].x; it.y = (char *) a[i].y;
+            it.x_tok = a[i].x_tok; it.y_tok = a[i].y_tok; it.row0 = a[i].row0; it.nrows = a[i].nrows;
+            it.ncols = a[i].ncols; it.chunks = (int) (w[i].K / CHUNK);
+            it.x_bf16 = a[i].x_bf16 != 0; it.y_bf16 = a[i].y_bf16 != 0;
+            const dim3 geo = row_geometry(a[i].nrows, a[i].ncols);
+            it.first_block = blocks;
+            it.blocks = (int) geo.x * a[i].ncols;
+            blocks += it.blocks;
+            i++;
+        }
+        launch_chained(k_nib_gemv_group, dim3((unsigned) blocks), dim3(256), 0, st, g);
+        check_launch();
+    }
+}
+
 void gemv_glu_merged(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st) {
     const NibView up = nib_view(w, a.nrows);
     if (a.x_bf16) { launch_glu<bf16>(w, &up, nullptr, a, st); } else { launch_glu<float>(w, &up, nullptr, a, st); }

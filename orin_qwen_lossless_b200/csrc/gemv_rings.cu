@@ -199,6 +199,7 @@ __global__ void __launch_bounds__(NT, 1) k_pair_gemv_rings(const PairView w, int
 
     const bf16 * xg; OutVec out; int64_t rbase;
     column<bf16>(p, NC == 1 ? blockIdx.y : 0, xg, out, rbase);
+    if (PEERS) { peers_begin(p.peers); }
     if (warp == 0) { tmem_alloc(smem_u32(&tmem_slot), TCOLS); }
     for (int i = threadIdx.x; i < HP_MAX_PAIRS; i += blockDim.x) { const uint32_t e = __ldg(w.lut + i); ((uint4 *) lut)[i] = make_uint4(e, e, e, e); }
     // 16 bytes per (column n, chunk c, half h, lane l): the lane's activations of column quads 2h and 2h+1 of the chunk

@@ -50,6 +50,8 @@ __device__ __forceinline__ void grid_dependency_wait() {
 // gemv.cu
 void gemv_init();
 void gemv(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st, bool multi_col, const bf16n_peer_out * peers = nullptr);
+bool gemv_groupable(const bf16n_weight & w, const bf16n_mmv_args & a);
+void gemv_group(const bf16n_weight * w, const bf16n_mmv_args * a, int n, cudaStream_t st);
 void gemv_glu_merged(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st);
 void gemv_glu(const bf16n_weight & g, const bf16n_weight & u, const bf16n_mmv_args & a, cudaStream_t st);
 void expand_store(const bf16n_weight & w, int64_t row0, int64_t nrows, uint16_t * out, cudaStream_t st);

@@ -3,17 +3,17 @@
 namespace b16 {
 namespace {
 
-// Rows per unit of a dense HUFPAIR matrix. Candidates keep at least 512 units (one per warp of a full machine in the
+// Rows per unit of a dense HUFPAIR matrix. Candidates keep at least min_units units (512 in the reference: one per warp of a full machine in the
 // decode GEMV's first wave). llama takes the largest such R; vLLM prefers a smaller R when its wave model says the
 // last, partly empty wave of 512 units costs at least 5 % less (cost = waves * R rows per warp).
-int dense_unit_rows(int64_t rows, Engine engine) noexcept {
+int dense_unit_rows(int64_t rows, Engine engine, int64_t min_units) noexcept {
     int pick = 1;
     int64_t pick_cost = 0;
     const int cand[4] = {16, 8, 4, 2};
     for (int r : cand) {
         const int64_t units = rows / r;
-        if (rows % r != 0 || units < 512) { continue; }
-        const int64_t waves = (units + 511) / 512;
+        if (rows % r != 0 || units < min_units) { continue; }
+        const int64_t waves = (units + min_units - 1) / min_units;
         const int64_t cost = waves * r;
         if (pick == 1) {
             pick = r;
@@ -49,7 +49,7 @@ bool choose(int64_t rows, int64_t K, int64_t n_matrices, const PolicyOptions & o
     if (stack) {
         R = (fo_gate_up || (bands && rows >= 2048)) ? 16 : rows % 8 == 0 ? 8 : rows % 4 == 0 ? 4 : 1;
     } else {
-        R = fo_dense ? 16 : dense_unit_rows(rows, o.engine);
+        R = fo_dense ? 16 : dense_unit_rows(rows, o.engine, o.min_units > 0 ? o.min_units : 512);
     }
     const bool fo_down = vllm && stack && K == CHUNK && R == 16;             // K = 512 expert stacks
     const bool fo = fo_gate_up || fo_down || fo_dense;

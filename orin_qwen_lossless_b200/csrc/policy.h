@@ -18,6 +18,10 @@ struct PolicyOptions {
     int64_t dense_min = 8ll << 20;  // dense tensors with fewer weights take NIBBLE
     bool expert = false;            // llama: the loader says whether the tensor is a routed-expert stack
     bool dense_frag_order = false;  // vLLM linear layers opt in to fragment-order bands
+    int64_t min_units = 512;        // a dense pair-Huffman matrix keeps at least this many units (one per warp of a full
+                                    // machine in the decode GEMV's first wave). 512 is the reference's constant, sized
+                                    // for the GPU it was written on; a B200 runs about 148 x 27 such warps, so a loader
+                                    // that shards a matrix over several B200s passes its own machine size here.
 };
 
 struct PolicyChoice {

@@ -147,11 +147,13 @@ def encode(w: torch.Tensor, fmt: int, R: int, chunk_major: bool, frag_order: boo
 
 
 def choose(rows: int, K: int, n_matrices: int = 1, *, engine: str = "vllm", mode: str = "hybrid", dense_min: int = 8 << 20,
-           expert: bool = False, dense_frag_order: bool = False):
-    """Shape policy: None (stays BF16) or (format, R, chunk_major, frag_order)."""
+           expert: bool = False, dense_frag_order: bool = False, min_units: int = 512):
+    """Shape policy: None (stays BF16) or (format, R, chunk_major, frag_order). min_units: the fewest units a dense
+    pair-Huffman matrix may have (512 = the reference's constant; a loader that shards over several B200s passes about
+    SMs x 24 so that small shards get shorter units)."""
     out = (C.c_int * 4)()
-    ok = lib().bf16n_choose(rows, K, n_matrices, int(engine == "vllm"), {"hybrid": 0, "huffman": 1, "nibble": 2}[mode],
-                            dense_min, int(expert), int(dense_frag_order), out)
+    ok = lib().bf16n_choose_for_machine(rows, K, n_matrices, int(engine == "vllm"), {"hybrid": 0, "huffman": 1, "nibble": 2}[mode],
+                                        dense_min, int(expert), int(dense_frag_order), min_units, out)
     return (out[0], out[1], bool(out[2]), bool(out[3])) if ok else None
 
 
@@ -310,6 +312,41 @@ def _mmv_common(x, w: Weight, ids, rows_per_matrix: int, out_bf16: bool, glu: bo
 def mmv(x: torch.Tensor, w: Weight, ids: torch.Tensor | None = None, rows_per_matrix: int = 0,
         out_dtype: torch.dtype = torch.float32, multi_col: bool = True, out: torch.Tensor | None = None) -> torch.Tensor:
     return _mmv_common(x, w, ids, rows_per_matrix, out_dtype == torch.bfloat16, False, multi_col, out)
+
+
+def mmv_group(xs, ws, outs=None, out_dtype: torch.dtype = torch.float32):
+    """Independent dense products ys[i] = ws[i] xs[i] in as few launches as possible: small NIBBLE matrices share one
+    grid (eight products per launch), other formats are launched as mmv launches them. Same bits as mmv per product."""
+    n = len(ws)
+    if len(xs) != n or (outs is not None and len(outs) != n):
+        raise RuntimeError("bf16n.mmv_group: one activation (and output) per matrix")
+    if n == 0:
+        return []
+    out_bf16 = out_dtype == torch.bfloat16
+    cws = (CWeight * n)()
+    args = (MmvArgs * n)()
+    ys = []
+    dev = ws[0].plane.device
+    for i, (x, w) in enumerate(zip(xs, ws)):
+        cws[i] = w.c()
+        m = w.meta
+        _check_x(x, m.K)
+        if x.dim() != 2 or w.plane.device != dev:
+            raise RuntimeError("bf16n.mmv_group: dense x [tokens, K], all matrices on one device")
+        T = x.shape[0]
+        y = torch.empty((T, m.rows), dtype=out_dtype, device=dev) if outs is None else outs[i]
+        y_row = m.rows * y.element_size() if outs is None else _check_out(y, (T, m.rows), out_dtype, dev, "mmv_group")
+        a = args[i]
+        a.x, a.x_bf16, a.y, a.y_bf16 = x.data_ptr(), int(x.dtype == torch.bfloat16), y.data_ptr(), int(out_bf16)
+        a.ncols, a.n_used, a.x_per_slot = T, 1, 1
+        a.x_tok, a.y_tok = x.stride(0) * x.element_size(), y_row
+        a.rows_per_matrix, a.nrows = m.rows, m.rows if T else 0
+        if T == 0:
+            a.ncols = 1
+        ys.append(y)
+    with torch.cuda.device(dev):
+        check(lib().bf16n_mmv_group(cws, args, n, _stream()))
+    return ys
 
 
 def mmv_glu(x: torch.Tensor, w: Weight, ids: torch.Tensor | None = None, rows_per_matrix: int = 0,

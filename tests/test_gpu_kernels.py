@@ -429,3 +429,31 @@ def test_mmv_large_matrix_long_codes(ops, rows):
     idx = np.r_[0:512, rows - 512:rows]
     assert np.array_equal(y.cpu().numpy()[0, idx].view(np.uint32), o.gemv_f32_order(w[idx], xf[0]).view(np.uint32))
     assert np.array_equal(bits_of(ops.dequant(enc, 0, 512)), w[:512])
+
+
+def test_mmv_group_equals_single_launches(ops):
+    """Independent products in one call: the small NIBBLE matrices share a grid, a pair-Huffman matrix in the middle of
+    the list is launched on its own; every result is bitwise what mmv gives, eagerly and replayed from a CUDA graph."""
+    shapes = [(2048, 512, NIB, 0), (512, 2048, NIB, 0), (256, 2048, NIB, 0), (1024, 2048, HP, 16), (96, 4096, NIB, 0),
+              (40, 1024, NIB, 0)] + [(64, 512, NIB, 0)] * 8          # more than eight groupable items: two grids
+    ws = [up(ops, o.weights_like(r, K, 300 + i, outliers=True), fmt, R) for i, (r, K, fmt, R) in enumerate(shapes)]
+    for T, xdt in ((1, torch.bfloat16), (3, torch.float32), (8, torch.bfloat16)):
+        xs = [act(T, K, seed=50 + i)[0].to(xdt) for i, (r, K, fmt, R) in enumerate(shapes)]
+        want = [ops.mmv(x, w) for x, w in zip(xs, ws)]
+        got = ops.mmv_group(xs, ws)
+        assert all(torch.equal(a, b) for a, b in zip(got, want))
+    xs = [act(1, K, seed=70 + i)[0] for i, (r, K, fmt, R) in enumerate(shapes)]
+    outs = [torch.empty(1, r, device="cuda") for (r, K, fmt, R) in shapes]
+    ops.mmv_group(xs, ws, outs)
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            ops.mmv_group(xs, ws, outs)
+    for x in xs:
+        x.copy_(act(1, x.shape[1], seed=int(x.shape[1]) + 5)[0])
+    g.replay()
+    torch.cuda.synchronize()
+    assert all(torch.equal(y, ops.mmv(x, w)) for x, w, y in zip(xs, ws, outs))
+    assert ops.mmv_group([], []) == []
