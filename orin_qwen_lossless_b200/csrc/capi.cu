@@ -398,8 +398,11 @@ static void moe_decode_checked(const bf16n_weight * gate, const bf16n_weight * u
     require(gate && up && down, "moe_decode: null weight");
     require(n_tok <= 0 || (x && y && topk_ids && topk_weights && scratch), "moe_decode: null argument");
     check_weight(*gate); check_weight(*up); check_weight(*down);
-    require(moe_decode_supported(*gate, *up, *down),
-            "moe_decode: gate/up must be chunk-major HUFPAIR R = 8 K = 2048 and down row-major HUFPAIR R = 16 K = 512");
+    const bool frag = gate->fo && up->fo && down->fo && fo_supported(*gate) && fo_supported(*up) && fo_supported(*down) &&
+                      gate->rows == up->rows && gate->K == up->K;
+    require(frag || moe_decode_supported(*gate, *up, *down),
+            "moe_decode: gate/up must be chunk-major HUFPAIR R = 8 K = 2048 and down row-major HUFPAIR R = 16 K = 512, or all three "
+            "in fragment order");
     require(n_tok >= 0 && n_tok <= 64 && n_used > 0 && n_used <= 32, "moe_decode: 0..64 tokens, 1..32 slots");
     require(n_experts_local > 0 && expert_lo >= 0 && expert_lo + n_experts_local <= n_experts, "moe_decode: expert slice out of range");
     require(gate->rows % n_experts_local == 0 && down->rows % n_experts_local == 0, "rows must split evenly into experts");
@@ -414,8 +417,17 @@ static void moe_decode_checked(const bf16n_weight * gate, const bf16n_weight * u
         require(peers->n_peers == 0 || peers->local_header, "moe_decode_peers: the local exchange header is missing");
         for (int r = 0; r < peers->n_peers; r++) { require(peers->y[r] && peers->flag[r], "moe_decode_peers: null peer pointer"); }
     }
+    if (frag) {
+        require(!peers && expert_lo == 0 && n_experts_local == n_experts,
+                "moe_decode: fragment-order experts run with all experts on one GPU (no expert slice, no peers)");
+    }
     if (n_tok == 0) { return; }
     if (router_logits) { moe_topk(router_logits, n_tok, n_experts, n_used, topk_ids, topk_weights, (cudaStream_t) stream); }
+    if (frag) {
+        moe_decode_frag_order(*gate, *up, *down, x, x_bf16 != 0, x_tok, topk_ids, topk_weights, n_tok, n_used, n_experts, scratch, y,
+                              y_bf16 != 0, (cudaStream_t) stream);
+        return;
+    }
     moe_decode(*gate, *up, *down, x, x_bf16 != 0, x_tok, topk_ids, topk_weights, n_tok, n_used, n_experts_local, expert_lo,
                scratch, y, y_bf16 != 0, (cudaStream_t) stream, peers);
 }

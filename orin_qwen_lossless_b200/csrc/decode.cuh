@@ -146,9 +146,11 @@ __device__ __forceinline__ void peers_done(const PeerOut & o) {
             epoch = o.hdr[XH_SENT] + 1u;
             o.hdr[XH_SENT] = epoch;
             *(volatile uint64_t *) (o.hdr + XH_T_STORED) = global_ns();
+            // every block fenced before it counted itself; this fence (after the count was read) completes the
+            // release of all of their stores, so the announcements themselves can be plain system-scope stores
             __threadfence_system();
             for (int r = 0; r < o.n; r++) {
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(o.flag[r]), "r"(epoch) : "memory");
+                asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(o.flag[r]), "r"(epoch) : "memory");
             }
             *(volatile uint64_t *) (o.hdr + XH_T_PUBLISHED) = global_ns();
         }

@@ -663,7 +663,7 @@ void launch_expand(const bf16n_weight & w, int64_t row0, int64_t nrows, const Si
 
 void gemv_init() {
     const int optin = device_info().smem_optin;
-#define ATTR(KERNEL, BYTES) cuda_ok(cudaFuncSetAttribute(KERNEL, cudaFuncAttributeMaxDynamicSharedMemorySize, std::min<int>(optin, (int) (BYTES))), #KERNEL)
+#define ATTR(KERNEL, BYTES) allow_dynamic_smem((const void *) KERNEL, (int) (BYTES), optin, #KERNEL)
 #define MC_ATTR(TX, CC) \
     ATTR((k_pair_gemv<CC, 1, TX, false>), 4 * HP_MAX_PAIRS + 1 * CC * CHUNK * 4); ATTR((k_pair_gemv<CC, 2, TX, false>), 4 * HP_MAX_PAIRS + 2 * CC * CHUNK * 4); \
     ATTR((k_pair_gemv<CC, 3, TX, false>), 4 * HP_MAX_PAIRS + 3 * CC * CHUNK * 4); ATTR((k_pair_gemv<CC, 4, TX, false>), 4 * HP_MAX_PAIRS + 4 * CC * CHUNK * 4);

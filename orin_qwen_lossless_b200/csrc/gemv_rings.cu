@@ -323,12 +323,8 @@ constexpr int g_warps = 28; // most warps per block (72 registers per thread)
 
 void gemv_rings_init() {
     const int optin = device_info().smem_optin;
-    auto allow = [optin](const void * kernel) { // the opt-in limit covers static and dynamic shared memory together
-        cudaFuncAttributes fa;
-        cuda_ok(cudaFuncGetAttributes(&fa, kernel), "rings attributes");
-        cuda_ok(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, optin - (int) fa.sharedSizeBytes), "rings shared memory");
-    };
-#define ATTR(CC, NT, NC) allow((const void *) k_pair_gemv_rings<CC, NT, NC>); allow((const void *) k_pair_gemv_rings<CC, NT, NC, true>);
+#define ATTR(CC, NT, NC) allow_dynamic_smem((const void *) k_pair_gemv_rings<CC, NT, NC>, optin, optin, "rings"); \
+                         allow_dynamic_smem((const void *) k_pair_gemv_rings<CC, NT, NC, true>, optin, optin, "rings");
     RINGS_FOR_EACH(ATTR)
 #undef ATTR
 }

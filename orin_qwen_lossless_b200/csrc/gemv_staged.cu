@@ -157,7 +157,7 @@ BF16N_DEFINE_FAULT_WORD(gemv_staged_fault_word)
 
 void gemv_staged_init() {
     const int optin = device_info().smem_optin;
-#define ATTR(KERNEL) cuda_ok(cudaFuncSetAttribute(KERNEL, cudaFuncAttributeMaxDynamicSharedMemorySize, optin), #KERNEL)
+#define ATTR(KERNEL) allow_dynamic_smem((const void *) KERNEL, optin, optin, #KERNEL)
     ATTR((k_pair_gemv_staged<1, float>)); ATTR((k_pair_gemv_staged<2, float>)); ATTR((k_pair_gemv_staged<4, float>));
     ATTR((k_pair_gemv_staged<1, bf16>)); ATTR((k_pair_gemv_staged<2, bf16>)); ATTR((k_pair_gemv_staged<4, bf16>));
     ATTR((k_pair_gemv_staged<1, float, true>)); ATTR((k_pair_gemv_staged<2, float, true>)); ATTR((k_pair_gemv_staged<4, float, true>));

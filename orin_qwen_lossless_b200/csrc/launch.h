@@ -24,6 +24,13 @@ inline void cuda_ok(cudaError_t e, const char * what) {
     if (e != cudaSuccess) { throw std::runtime_error(std::string("bf16n: CUDA error ") + cudaGetErrorString(e) + " at " + what); }
 }
 inline void check_launch() { cuda_ok(cudaGetLastError(), "kernel launch"); }
+// Lets `kernel` use up to `bytes` of dynamic shared memory, capped at the device's opt-in limit less whatever the
+// kernel declares statically (the limit covers both together).
+inline void allow_dynamic_smem(const void * kernel, int bytes, int optin, const char * what) {
+    cudaFuncAttributes fa;
+    cuda_ok(cudaFuncGetAttributes(&fa, kernel), what);
+    cuda_ok(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, std::min(bytes, optin - (int) fa.sharedSizeBytes)), what);
+}
 
 #ifdef __CUDACC__
 // Launch of a kernel that may start while the kernel before it on the stream is still draining (programmatic dependent
@@ -110,6 +117,9 @@ bool moe_decode_supported(const bf16n_weight & gate, const bf16n_weight & up, co
 void moe_decode(const bf16n_weight & gate, const bf16n_weight & up, const bf16n_weight & down, const void * x, bool x_bf16,
                 int64_t x_tok, const int32_t * ids, const float * weights, int n_tok, int n_used, int n_experts_local, int e_lo,
                 float * scratch, void * y, bool y_bf16, cudaStream_t st, const bf16n_peer_out * peers = nullptr);
+void moe_decode_frag_order(const bf16n_weight & gate, const bf16n_weight & up, const bf16n_weight & down, const void * x, bool x_bf16,
+                           int64_t x_tok, const int32_t * ids, const float * weights, int n_tok, int n_used, int n_experts,
+                           float * scratch, void * y, bool y_bf16, cudaStream_t st);
 void peer_sum(const float * parts, int n_parts, int64_t n, const float * extra, void * y, bool y_bf16, cudaStream_t st);
 
 size_t moe_decode_static_capacity_floats();

@@ -37,7 +37,26 @@ struct ExpertCols {
     int64_t rows_per_expert;
     int e_lo, e_n;                             // experts held by this weight: global ids [e_lo, e_lo + e_n)
     uint32_t cap_bytes;
+    bool early_ids;                            // the expert ids were complete before the PREVIOUS kernel on the stream
+                                               // began its dependent work (they come from a kernel before that one):
+                                               // ids, unit geometry and the bulk copies need not wait for it; only the
+                                               // activations do
 };
+
+// Loads of data the kernel before this one on the stream may still be writing when this kernel starts (programmatic
+// dependent launch): issued after the grid dependency wait and kept there. They are volatile asm with a memory clobber
+// and use the coherent path; the read-only (__ldg) path may be hoisted above the wait by the compiler and may serve
+// lines fetched before the producer's stores.
+__device__ __forceinline__ float4 ld_dep_x4(const float * p) {
+    float4 v;
+    asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 ld_dep_x4(const __nv_bfloat16 * p) {
+    uint2 v;
+    asm volatile("ld.global.cg.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return make_float4(bf16lo_f32(v.x), bf16hi_f32(v.x), bf16lo_f32(v.y), bf16hi_f32(v.y));
+}
 
 template <int C, int R, bool CM, typename TX, bool GLU_IN, bool PLANE_STAGED>
 __global__ void __launch_bounds__(256) k_expert_units(const ExpertMat m0, const ExpertMat m1, const ExpertCols p, const Opaque k) {
@@ -57,7 +76,11 @@ __global__ void __launch_bounds__(256) k_expert_units(const ExpertMat m0, const 
     if (lane == 0) { mbar_init(bar, 1); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     __syncthreads();
-    grid_dependency_wait(); // expert ids, activations and the output buffers belong to earlier kernels up to here
+    // Expert ids, activations and the output buffers belong to earlier kernels. Normally everything below waits for
+    // them. With early_ids only the activations come from the kernel right before this one: that kernel's blocks let
+    // this one start only after their own wait, i.e. after everything older (ids, the last reader of the outputs) was
+    // complete and visible, so the ids, the unit geometry and the bulk copies of streams and plane run ahead of it.
+    if (!p.early_ids) { grid_dependency_wait(); }
 
     const int col = blockIdx.y, t = col / p.n_used, s = col - t * p.n_used;
     const int e = *(const int32_t *) (p.ids + t * p.ids_s1 + s * p.ids_s0) - p.e_lo;
@@ -84,6 +107,7 @@ __global__ void __launch_bounds__(256) k_expert_units(const ExpertMat m0, const 
     if (!plane_staged && lane == 0) { bulk_prefetch_l2(m.v.plane + gu * R * K, (uint32_t) (R * K)); } // later chunks then hit L2
     const uint32_t my = w0 - start + __ldg(m.v.lrel + gu * 32 + lane);
 
+    if (p.early_ids) { grid_dependency_wait(); }
     // this lane's activations, in registers (FP32 values; BF16 inputs are widened exactly)
     float4 xr[C * 4];
     {
@@ -92,9 +116,9 @@ __global__ void __launch_bounds__(256) k_expert_units(const ExpertMat m0, const 
 #pragma unroll
         for (int i = 0; i < C * 4; i++) {
             const int at = (i >> 2) * CHUNK + 128 * (i & 3) + 4 * lane;
-            float4 v = ldg_x4((const TX *) xp, at);
+            float4 v = ld_dep_x4((const TX *) xp + at);
             if (GLU_IN) {
-                const float4 g = v, w2 = __ldg((const float4 *) (x2 + at));
+                const float4 g = v, w2 = ld_dep_x4(x2 + at);
                 v = make_float4(silu_f(g.x) * w2.x, silu_f(g.y) * w2.y, silu_f(g.z) * w2.z, silu_f(g.w) * w2.w);
             }
             xr[i] = v;
@@ -329,9 +353,37 @@ void moe_decode(const bf16n_weight & gate, const bf16n_weight & up, const bf16n_
     ExpertCols q = p;
     q.x = (const char *) g; q.x2 = u; q.x_tok = 4ll * n_used * N; q.x_slot = 4ll * N;
     q.rows_per_expert = H; q.cap_bytes = unit_cap(down);
+    q.early_ids = true; // the ids precede the gate / up launch, whose outputs are the only thing this launch waits for
     launch_units<1, 16, false, float, true>(expert_mat(down, ys), expert_mat(down, ys), 1, q, ncols, st);
     const dim3 grid((unsigned) std::min<int64_t>((H + 255) / 256, 64), (unsigned) n_tok);
     launch_chained(k_combine_f32, grid, dim3(256), 0, st, ys, weights, (char *) y, y_bf16, n_used, H, make_peer_out(peers));
+}
+
+// The same step over fragment-order experts (the layout the vLLM policy gives expert stacks): routed products through the
+// fragment-order GEMV (one decode per (token, slot) column, a band's slabs on separate warps), SwiGLU in place, the
+// slot-order combine. All experts on this GPU (no expert slice). Same scratch layout as moe_decode.
+void moe_decode_frag_order(const bf16n_weight & gate, const bf16n_weight & up, const bf16n_weight & down, const void * x, bool x_bf16,
+                           int64_t x_tok, const int32_t * ids, const float * weights, int n_tok, int n_used, int n_experts,
+                           float * scratch, void * y, bool y_bf16, cudaStream_t st) {
+    const int64_t N = gate.rows / n_experts, H = down.rows / n_experts;
+    const int ncols = n_tok * n_used;
+    float * g = scratch, * u = g + (int64_t) ncols * N, * ys = u + (int64_t) ncols * N;
+    bf16n_mmv_args a = {};
+    a.x = x; a.x_bf16 = x_bf16; a.y_bf16 = 0; a.ncols = ncols; a.n_used = n_used; a.x_per_slot = 1;
+    a.x_tok = x_tok; a.x_slot = 0;
+    a.ids = ids; a.ids_s0 = 4; a.ids_s1 = 4ll * n_used;
+    a.rows_per_matrix = N; a.row0 = 0; a.nrows = N;
+    a.y_tok = 4ll * n_used * N; a.y_slot = 4ll * N;
+    a.y = g; fo_gemv(gate, a, st);
+    a.y = u; fo_gemv(up, a, st);
+    moe_swiglu(g, u, g, (int64_t) ncols * N, st);            // g := silu(g) * u
+    bf16n_mmv_args d = a;
+    d.x = g; d.x_bf16 = 0; d.x_per_slot = n_used; d.x_tok = 4ll * n_used * N; d.x_slot = 4ll * N;
+    d.rows_per_matrix = H; d.nrows = H; d.y = ys; d.y_tok = 4ll * n_used * H; d.y_slot = 4ll * H;
+    fo_gemv(down, d, st);
+    const dim3 grid((unsigned) std::min<int64_t>((H + 255) / 256, 64), (unsigned) n_tok);
+    launch_chained(k_combine_f32, grid, dim3(256), 0, st, ys, weights, (char *) y, y_bf16, n_used, H, PeerOut{});
+    check_launch();
 }
 
 void peer_sum(const float * parts, int n_parts, int64_t n, const float * extra, void * y, bool y_bf16, cudaStream_t st) {

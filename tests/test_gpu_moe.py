@@ -77,6 +77,28 @@ def test_expert_parallel_partials_add_up(ops, layer, ranks):
     assert torch.allclose(total, full.double(), rtol=0, atol=2.0 ** -18 * float(full.abs().max()) * K_TOP)
 
 
+@pytest.mark.parametrize("T", [1, 2, 4])
+def test_step_over_fragment_order_experts(ops, layer, T):
+    """The vLLM layout (16-row fragment-order bands for gate, up and down) through the same entry point: equal to the
+    operator chain over the same weights (bitwise) and within the bound of the FP64 layer; an expert slice is refused."""
+    bits, _ = layer
+
+    def enc_fo(w):
+        plane, aux, meta = ops.encode(to_bf16_tensor(w), 3, 16, False, True)
+        return ops.upload(plane, aux, meta, "cuda")
+
+    g, u, d = enc_fo(bits["gate"]), enc_fo(bits["up"]), enc_fo(bits["down"])
+    x, xf, logits, _ = inputs(T, 40 + T)
+    y, wts, ids = ops.moe_decode(x, g, u, d, E, K_TOP, router_logits=logits)
+    gg, uu = ops.mmv(x, g, ids, N), ops.mmv(x, u, ids, N)
+    chain = ops.moe_combine(ops.mmv(ops.swiglu(gg, uu), d, ids, H), wts, torch.float32)
+    assert torch.equal(y, chain)
+    ref = o.moe_layer_f64(xf, bits["gate"], bits["up"], bits["down"], wts.cpu().numpy(), ids.cpu().numpy(), E)
+    assert np.abs(y.cpu().numpy() - ref).max() <= 2.0 ** -10 * np.abs(ref).max()
+    with pytest.raises(ValueError, match="no expert slice"):
+        ops.moe_decode(x, g, u, d, 2 * E, K_TOP, topk_weights=wts, topk_ids=ids, expert_lo=0, n_experts_local=E)
+
+
 def test_fused_step_in_a_cuda_graph(ops, layer):
     bits, enc = layer
     g, u, d = enc(bits["gate"], 8, True), enc(bits["up"], 8, True), enc(bits["down"], 16, False)
