@@ -46,9 +46,9 @@ sys.path.insert(0, ROOT)
 
 ROWS, K, R = 248320, 2048, 16
 # DRAM bytes moved per algorithmic byte by the GEMV kernel: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture
-# on a 65536-row case of the same matrix family (182.99 MB moved for 179.01 MB algorithmic, profiles/lm_head_gemv_ncu.md);
+# on a 65536-row case of the same matrix family (181.97 MB moved for 179.01 MB algorithmic, profiles/lm_head_gemv_ncu.md);
 # traffic grows in proportion to the rows, so a full launch is this ratio times its algorithmic bytes.
-DRAM_TRAFFIC_RATIO = 1.022
+DRAM_TRAFFIC_RATIO = 1.017
 BLOCK_ROWS = 4096  # weights are generated in seeded blocks of rows so that every shard is reproducible on its own
 
 
@@ -526,10 +526,20 @@ def _enc(ops, rows, K, fmt, R, cm, seed, dev, fo=False, keep=False):
     return (enc, w) if keep else enc
 
 
+def _agree_max(torch, n: int) -> int:
+    """The largest n over the ranks (ranks whose kernels wait for each other must replay the same number of times)."""
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1):
+        return n
+    t = torch.tensor([n], dtype=torch.int64, device=torch.device("cuda", torch.cuda.current_device()))
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return int(t.item())
+
+
 def _time_graph(torch, fn, reps, inner=1, min_s=0.3):
     """A CUDA graph of `fn`, replayed back to back: every sample times enough replays to last about 5 ms (so that the
-    launch of a replay overlaps the one before it, as in a decode loop), at least max(reps, 30) samples and min_s seconds
-    of them. Returns (median, min, max) microseconds per inner step."""
+    launch of a replay overlaps the one before it, as in a decode loop), at least max(reps, 30) samples and about min_s
+    seconds of them; the counts are agreed between the ranks. Returns (median, min, max) microseconds per inner step."""
     s = torch.cuda.Stream()
     fn()
     torch.cuda.synchronize()
@@ -550,13 +560,10 @@ def _time_graph(torch, fn, reps, inner=1, min_s=0.3):
         e1.synchronize()
         return e0.elapsed_time(e1) / m
 
-    m = max(1, int(np.ceil(5.0 / max(sample(1), 1e-3))))
-    times, total = [], 0.0
-    while (len(times) < max(reps, 30) or total < min_s * 1e3) and len(times) < 2000:
-        ms = sample(m)
-        times.append(ms)
-        total += ms * m
-    times.sort()
+    one = sample(1)
+    m = _agree_max(torch, max(1, int(np.ceil(5.0 / max(one, 1e-3)))))
+    n = _agree_max(torch, min(2000, max(reps, 30, int(np.ceil(min_s * 1e3 / max(one * m, 1e-3))))))
+    times = sorted(sample(m) for _ in range(n))
     k = 1e3 / inner
     return statistics.median(times) * k, times[0] * k, times[-1] * k
 
@@ -726,10 +733,29 @@ def moe_prefill_runs(args, torch, dist, ops, rank, world, dev, weights, fo=False
             us = med
             y = ops.moe_experts(x, gate, up, down, wts, ids, E)
             par = "1 GPU"
+        elif not args.nccl:
+            # tokens data-parallel (T / world per rank), experts sharded: every routed row is stored into the exchange
+            # buffer of its expert's rank by a kernel (peer stores over NVLink), multiplied there by the batched kernels
+            # and stored back; no host round trip, no collective: the layer is one CUDA graph per rank
+            Tl = T // world
+            x = torch.randn(Tl, 2048, device=dev, generator=g).to(torch.bfloat16)
+            wts, ids = ops.moe_topk(torch.randn(Tl, E, device=dev, generator=g), k)
+            fmp = sharded.FusedMoePrefill(gate, up, down, E, k, Tl)
+            y = fmp(x, wts, ids)
+            torch.cuda.synchronize(); dist.barrier()
+            med, lo, hi = _time_graph(torch, lambda: fmp(x, wts, ids), max(args.steps // 100, 5))
+            us = _max_over_ranks(torch, med, world, dev)
+            lo, hi = _max_over_ranks(torch, lo, world, dev), _max_over_ranks(torch, hi, world, dev)
+            y = fmp(x, wts, ids).clone()
+            expired = fmp.xchg.expired()
+            fmp.close()
+            if expired:
+                raise SystemExit("bench.py: a wait for a peer's rows expired")
+            par = f"expert-parallel over {world} GPUs, routed rows exchanged by peer stores on the device (no host round trip, no collective)"
         else:
-            # tokens data-parallel (T / world per rank), experts sharded: all-to-all dispatch of the routed rows, batched
-            # kernels on the owner, all-to-all back, combine. The exchange sizes come back to the host, so the layer is
-            # timed as eager launches with CUDA events (max over ranks).
+            # the NCCL form for comparison: all-to-all dispatch of the routed rows, batched kernels on the owner,
+            # all-to-all back, combine. The exchange sizes come back to the host, so the layer is timed as eager launches
+            # with CUDA events (max over ranks).
             Tl = T // world
             x = torch.randn(Tl, 2048, device=dev, generator=g).to(torch.bfloat16)
             wts, ids = ops.moe_topk(torch.randn(Tl, E, device=dev, generator=g), k)
@@ -903,7 +929,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-moe", action="store_true", help="skip the MoE layer and small-matrix blocks of the contract line")
     ap.add_argument("--fo", action="store_true", help="moe_prefill: experts in the fragment-order layout (mma.sync batched kernel)")
-    ap.add_argument("--nccl", action="store_true", help="N > 1, moe_decode: all-reduce with NCCL instead of the fused peer stores")
+    ap.add_argument("--nccl", action="store_true", help="N > 1, MoE workloads: NCCL collectives instead of the fused peer stores")
     ap.add_argument("--workload", default="lm_head", choices=["lm_head", "small", "moe_decode", "moe_prefill", "dense_mid"],
                     help="lm_head is the headline contract line; the others print extra lines for the other baseline configs "
                          "(small: 1 GPU; the MoE workloads run expert-parallel under torchrun)")

@@ -291,6 +291,32 @@ int bf16n_peer_sum(const float * parts, int n_parts, int64_t n, const float * ex
 /* Synchronises the stream and returns header word 19 (non-zero: a wait expired since the buffer was created). */
 int bf16n_peer_expired(const uint32_t * local_header, void * stream, int * expired);
 
+/* Expert-parallel prefill on the device: tokens split over the ranks of a node, experts sharded; every routed
+ * (token, slot) row is stored into the exchange buffer of the rank that owns its expert, multiplied there by the batched
+ * kernels and its result stored back into the source's buffer. No host round trip and no collective: the three calls
+ * enqueue kernels on the caller's stream and a layer can be captured in a CUDA graph. Every rank issues the same
+ * sequence of calls per layer:
+ *     bf16n_ep_dispatch    plan + row copies into the owners' inboxes; ends when every peer's rows have arrived here
+ *     bf16n_ep_inbox_ids   expert id of every inbox slot ([n_ranks * cap], 0x7fffffff = empty) for bf16n_mm_ids_route /
+ *                          bf16n_mm_ids over the inbox rows (n_tok = n_ranks * cap, n_used = 1)
+ *     bf16n_ep_give_back   results [n_ranks * cap, H] FP32 of the inbox rows into their sources' `back` areas (row = pair
+ *                          index, i.e. [n_tok, n_used, H] for bf16n_moe_combine); ends when every owner's results are here
+ * The buffers are bf16n_exchange_create buffers of bf16n_ep_layout_bytes(l) payload bytes with one layout on all ranks. */
+typedef struct bf16n_ep_layout {
+    int n_ranks, rank;
+    int cap;             /* rows one source can send to one owner: at least the largest n_tok * n_used of any rank */
+    int K, H;            /* activation columns (BF16) and result columns (FP32) */
+    int n_pairs_max;     /* the most (token, slot) pairs this rank itself routes in a layer */
+    void * base[8];      /* the exchange buffers of all ranks as mapped into this process ([rank] = the own one) */
+    size_t off_counts, off_expert, off_pair, off_rows, off_back;   /* payload areas, set by bf16n_ep_layout_bytes */
+} bf16n_ep_layout;
+size_t bf16n_ep_layout_bytes(bf16n_ep_layout * l);
+/* plan: device scratch of n_tok * n_used + 8 int32 */
+int bf16n_ep_dispatch(const bf16n_ep_layout * l, const void * x_bf16, int64_t x_row_bytes, const int32_t * topk_ids, int n_tok, int n_used,
+                      int n_experts, int32_t * plan, void * stream);
+int bf16n_ep_inbox_ids(const bf16n_ep_layout * l, int32_t * ids_out, void * stream);
+int bf16n_ep_give_back(const bf16n_ep_layout * l, const float * ys, void * stream);
+
 #ifdef __cplusplus
 }
 #endif

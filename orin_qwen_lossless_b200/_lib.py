@@ -30,6 +30,13 @@ class MmvArgs(C.Structure):
                 ("y_slot", C.c_int64), ("rows_per_matrix", C.c_int64), ("row0", C.c_int64), ("nrows", C.c_int64)]
 
 
+class EpLayout(C.Structure):
+    """struct bf16n_ep_layout"""
+    _fields_ = [("n_ranks", C.c_int), ("rank", C.c_int), ("cap", C.c_int), ("K", C.c_int), ("H", C.c_int), ("n_pairs_max", C.c_int),
+                ("base", C.c_void_p * 8), ("off_counts", C.c_size_t), ("off_expert", C.c_size_t), ("off_pair", C.c_size_t),
+                ("off_rows", C.c_size_t), ("off_back", C.c_size_t)]
+
+
 class PeerOut(C.Structure):
     """struct bf16n_peer_out"""
     _fields_ = [("n_peers", C.c_int), ("y", C.c_void_p * 7), ("flag", C.c_void_p * 7), ("local_header", C.c_void_p), ("wait_mask", C.c_int)]
@@ -82,6 +89,10 @@ SIGNATURES = {
     "bf16n_peer_wait": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "bf16n_peer_expired": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
     "bf16n_set_peer_wait_limit_ms": (C.c_int, [C.c_uint]),
+    "bf16n_ep_layout_bytes": (C.c_size_t, [C.POINTER(EpLayout)]),
+    "bf16n_ep_dispatch": (C.c_int, [C.POINTER(EpLayout), C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "bf16n_ep_inbox_ids": (C.c_int, [C.POINTER(EpLayout), C.c_void_p, C.c_void_p]),
+    "bf16n_ep_give_back": (C.c_int, [C.POINTER(EpLayout), C.c_void_p, C.c_void_p]),
     "bf16n_adapter_choose": (C.c_int, [C.c_int64, C.c_int64, C.c_int64, C.c_char_p, C.c_int64, C.c_int]),
     "bf16n_adapter_convert": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_char_p,
                                         C.POINTER(C.c_int)]),

@@ -549,6 +549,30 @@ int bf16n_peer_wait(uint32_t * local_header, int rank_mask, void * stream) {
     });
 }
 
+size_t bf16n_ep_layout_bytes(bf16n_ep_layout * l) { return l ? ep_layout_fill(*l) : 0; }
+int bf16n_ep_dispatch(const bf16n_ep_layout * l, const void * x_bf16, int64_t x_row_bytes, const int32_t * topk_ids, int n_tok, int n_used,
+                      int n_experts, int32_t * plan, void * stream) {
+    return guarded([&] {
+        ensure_init();
+        require(l && x_bf16 && topk_ids && plan, "ep_dispatch: null argument");
+        ep_dispatch(*l, x_bf16, x_row_bytes, topk_ids, n_tok, n_used, n_experts, plan, (cudaStream_t) stream);
+    });
+}
+int bf16n_ep_inbox_ids(const bf16n_ep_layout * l, int32_t * ids_out, void * stream) {
+    return guarded([&] {
+        ensure_init();
+        require(l && ids_out, "ep_inbox_ids: null argument");
+        ep_inbox_ids(*l, ids_out, (cudaStream_t) stream);
+    });
+}
+int bf16n_ep_give_back(const bf16n_ep_layout * l, const float * ys, void * stream) {
+    return guarded([&] {
+        ensure_init();
+        require(l && ys, "ep_give_back: null argument");
+        ep_give_back(*l, ys, (cudaStream_t) stream);
+    });
+}
+
 int bf16n_peer_expired(const uint32_t * local_header, void * stream, int * expired) {
     return guarded([&] {
         require(local_header && expired, "peer_expired: null argument");

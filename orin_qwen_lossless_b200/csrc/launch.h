@@ -101,6 +101,13 @@ void fo_gather_rows(const bf16n_weight & w, const void * ids, int64_t ids_s0, in
 // peer.cu: exchange buffers shared between the GPUs of a node and the wait for the peers' announcements
 void peer_wait(uint32_t * local_header, int n_peers_mask, cudaStream_t st);
 
+// ep_prefill.cu: expert-parallel prefill, rows exchanged with peer stores
+size_t ep_layout_fill(bf16n_ep_layout & l);
+void ep_dispatch(const bf16n_ep_layout & l, const void * x_bf16, int64_t x_row, const int32_t * ids, int n_tok, int n_used, int n_experts,
+                 int32_t * plan, cudaStream_t st);
+void ep_inbox_ids(const bf16n_ep_layout & l, int32_t * ids_out, cudaStream_t st);
+void ep_give_back(const bf16n_ep_layout & l, const float * ys, cudaStream_t st);
+
 // moe.cu
 void moe_init();
 void moe_topk(const float * logits, int n_tok, int n_experts, int k, int32_t * ids, float * weights, cudaStream_t st);

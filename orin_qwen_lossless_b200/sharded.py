@@ -18,7 +18,7 @@ import torch
 import torch.distributed as dist
 
 from . import ops
-from ._lib import MmvArgs, PeerOut, check, lib
+from ._lib import EpLayout, MmvArgs, PeerOut, check, lib
 from .ops import FLAG_CHUNK_MAJOR, FLAG_FRAG_ORDER, FMT_HUFFMAN, FMT_HUFPAIR, FMT_NIBBLE, HEADER, MAGIC, Meta
 
 HP_TAIL_WORDS, HUF_TAIL_WORDS = 32, 16
@@ -469,3 +469,73 @@ def moe_prefill_ep(x, topk_weights, topk_ids, gate, up, down, n_experts, group=N
     for s in range(k):
         acc = acc + topk_weights[:, s:s + 1].to(ys.dtype) * ys[:, s]
     return acc
+
+
+class FusedMoePrefill:
+    """Expert-parallel prefill layer without the host in the loop: this rank's tokens are routed on the device, every
+    routed row is stored into the exchange buffer of the rank that owns its expert (peer stores over NVLink), multiplied
+    there by the batched kernels and its result stored back; the slot-order combine finishes the layer. Only kernels on
+    the current stream: no exchange of sizes through the host, no collective, capturable in a CUDA graph. Every rank
+    calls it once per layer with at most `max_local_tokens` tokens (any rank's count may differ from call to call).
+    Results equal moe_prefill_ep's bit for bit."""
+
+    def __init__(self, gate, up, down, n_experts: int, top_k: int, max_local_tokens: int, group=None):
+        self.gate, self.up, self.down, self.E, self.k = gate, up, down, n_experts, top_k
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.n_local = n_experts // self.world
+        self.K, self.H = gate.meta.K, down.meta.rows // self.n_local
+        self.dev = gate.plane.device
+        self.P = max_local_tokens * top_k
+        lay = EpLayout()
+        lay.n_ranks, lay.rank, lay.cap, lay.K, lay.H, lay.n_pairs_max = self.world, self.rank, self.P, self.K, self.H, self.P
+        nbytes = lib().bf16n_ep_layout_bytes(C.byref(lay))
+        if self.world > 1:
+            self.xchg = PeerExchange(nbytes, group)
+            bases = self.xchg.bases
+        else:
+            self.xchg = None
+            self._own = torch.zeros(HEADER_BYTES + nbytes, dtype=torch.uint8, device=self.dev)
+            bases = [self._own.data_ptr()]
+        for r, b in enumerate(bases):
+            lay.base[r] = b
+        self.lay = lay
+        n_slots = self.world * self.P
+        base = bases[self.rank] + HEADER_BYTES
+        self.rows = _device_view(base + lay.off_rows, (n_slots, self.K), torch.bfloat16, self.dev)
+        self.back = _device_view(base + lay.off_back, (self.P, self.H), torch.float32, self.dev)
+        self.inbox_ids = torch.empty((n_slots, 1), dtype=torch.int32, device=self.dev)
+        self.plan = torch.empty(self.P + 8, dtype=torch.int32, device=self.dev)
+
+    def __call__(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
+        """x [T, K] BF16 (this rank's tokens), topk_weights / topk_ids [T, k] -> [T, H] BF16."""
+        T, k = topk_ids.shape
+        if not (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[0] == T and x.stride(1) == 1):
+            raise RuntimeError("bf16n FusedMoePrefill: x must be bf16 [tokens, K] on the GPU")
+        if not (topk_ids.dtype == torch.int32 and topk_ids.is_contiguous() and k == self.k and 0 < T * k <= self.P):
+            raise RuntimeError("bf16n FusedMoePrefill: topk_ids int32 [tokens, k] within the token limit it was built for")
+        st = ops._stream()
+        with torch.cuda.device(self.dev):
+            check(lib().bf16n_ep_dispatch(C.byref(self.lay), x.data_ptr(), x.stride(0) * 2, topk_ids.data_ptr(), T, k, self.E,
+                                          self.plan.data_ptr(), st))
+            check(lib().bf16n_ep_inbox_ids(C.byref(self.lay), self.inbox_ids.data_ptr(), st))
+        route = ops.moe_route(self.inbox_ids, self.n_local, False)
+        a = ops.moe_mm_ids(self.rows, self.inbox_ids, self.gate, self.n_local, up=self.up, out_dtype=torch.bfloat16, route=route)
+        ys = ops.moe_mm_ids(a, self.inbox_ids, self.down, self.n_local, out_dtype=torch.float32, route=(route[1], route[1], route[2]))
+        with torch.cuda.device(self.dev):
+            check(lib().bf16n_ep_give_back(C.byref(self.lay), ys.data_ptr(), st))
+        return ops.moe_combine(self.back[: T * k].view(T, k, self.H), topk_weights.contiguous(), torch.bfloat16)
+
+    def close(self) -> None:
+        self.rows = self.back = None
+        if self.xchg is not None:
+            self.xchg.close()
+
+
+def _device_view(ptr: int, shape, dtype, device) -> torch.Tensor:
+    """A tensor over device memory the library owns (the caller keeps the owner alive)."""
+    iface = {"shape": tuple(int(s) for s in shape), "typestr": {torch.float32: "<f4", torch.bfloat16: "<u2", torch.int32: "<i4"}[dtype],
+             "data": (ptr, False), "version": 3}
+    holder = type("_Span", (), {"__cuda_array_interface__": iface})()
+    t = torch.as_tensor(holder, device=device)
+    return t.view(dtype) if dtype == torch.bfloat16 else t

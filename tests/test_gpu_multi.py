@@ -124,6 +124,24 @@ def _worker(rank, world, port, ret):
         y_loc = ops.moe_experts(xp, g, u, d, w_p, i_p, E)
         err = float((y_a2a.float() - y_loc.float()).abs().max())
         ok3 = err <= 2.0 ** -7 * float(y_loc.float().abs().max())
+        # 3b. the same layer with the rows exchanged by peer stores on the device (no host round trip, no collective):
+        # bit-equal to the all-to-all form, over several layers with different token counts and from a CUDA graph
+        fmp = sharded.FusedMoePrefill(gl, ul, dl, E, TOPK, 64)
+        ok3 = ok3 and bool(torch.equal(fmp(xp, w_p, i_p), y_a2a))
+        for t2 in (9 + 3 * rank, 64):
+            x2 = to_bf16_tensor(o.f32_to_bf16_bits(np.random.default_rng(50 + t2 + rank).standard_normal((t2, H)).astype(np.float32))).to(dev)
+            w2, i2 = ops.moe_topk(torch.from_numpy(np.random.default_rng(60 + t2 + rank).standard_normal((t2, E)).astype(np.float32)).to(dev), TOPK)
+            ok3 = ok3 and bool(torch.equal(fmp(x2, w2, i2), sharded.moe_prefill_ep(x2, w2, i2, gl, ul, dl, E)))
+        want_g = fmp(xp, w_p, i_p).clone()
+        torch.cuda.synchronize()
+        gr3 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr3):
+            y_g = fmp(xp, w_p, i_p)
+        gr3.replay()
+        gr3.replay()
+        torch.cuda.synchronize()
+        ok3 = ok3 and bool(torch.equal(y_g, want_g)) and not fmp.xchg.expired() and ops.fault_status() == 0
+        fmp.close()
         ret[rank] = (ok1, ok1b, ok2, ok3)
     finally:
         dist.destroy_process_group()

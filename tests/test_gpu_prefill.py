@@ -128,3 +128,19 @@ def test_unsupported_shapes_are_rejected(ops, layer):
     assert not ops.mm_ids_supported(rm) and ops.mm_ids_supported(w["gate"], w["up"]) and ops.mm_ids_supported(w["down"])
     with pytest.raises(ValueError, match="no batched kernel"):
         ops.moe_mm_ids(x, ids, rm, E)
+
+
+def test_device_side_dispatch_on_one_rank(ops, layer):
+    """The expert-parallel layer with its device-side exchange, degenerate on one rank (every row is sent to this rank's
+    own inbox): bit-equal to the single-GPU layer, which pins the plan, inbox, routing-over-inbox and give-back kernels."""
+    from orin_qwen_lossless_b200 import sharded
+    bits, enc_w, _ = layer
+    if enc_w["gate"].meta.frag_order:
+        pytest.skip("lane-major experts only")
+    fmp = sharded.FusedMoePrefill(enc_w["gate"], enc_w["up"], enc_w["down"], E, TOPK, 300)
+    for T in (9, 130, 300):
+        x, _ = act((T, H), 70 + T)
+        ids = torch.from_numpy(routing(T, "uniform", T).astype(np.int32)).cuda()
+        wts = torch.rand(T, TOPK, device="cuda")
+        assert torch.equal(fmp(x, wts, ids), ops.moe_experts(x, enc_w["gate"], enc_w["up"], enc_w["down"], wts, ids, E))
+    fmp.close()
