@@ -258,9 +258,11 @@ def run_ours(args):
             dist.all_gather_into_tensor(gathered.view(-1), gathered[rank])
 
     # N > 1, the product: the GEMV kernel stores its logits into every GPU's gathered buffer itself (peer stores over
-    # NVLink, epoch flags; the kernel ends when the peers' logits have arrived); no collective. One CUDA graph holds an
-    # even number of steps (the two exchange buffers in turn) that also walks through the rotating copies.
-    fused = graph = None
+    # NVLink, epoch flags; the kernel ends when the peers' logits have arrived); no collective. A CUDA graph holds exactly
+    # --steps steps (the two exchange buffers in turn, walking through the rotating copies); with an odd step count a second
+    # graph that starts on the other buffer takes every other block, so that the buffers keep alternating across replays.
+    fused = None
+    graphs = []
     fused_note = None
     per_call = 1
     if world > 1:
@@ -274,17 +276,23 @@ def run_ours(args):
         if int(agree.item()) and fused:
             fused.close()
             fused, fused_note = None, "exchange buffers unavailable on another rank"
-    if fused:
-        per_call = 2 * n_copies if n_copies > 1 else 2
-        last = [fused(x, next_copy()) for _ in range(per_call)]
+    if fused and args.steps <= 4096:
+        per_call = args.steps
+        last = [fused(x, next_copy()) for _ in range(2)]
         torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            last = [fused(x, next_copy()) for _ in range(per_call)]
+        for _ in range(1 if per_call % 2 == 0 else 2):
+            g_ = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_):
+                last = [fused(x, next_copy()) for _ in range(per_call)]
+            graphs.append(g_)
+    which = [0]
 
     def step():
-        if fused:
-            graph.replay()     # per_call steps
+        if graphs:
+            graphs[which[0] % len(graphs)].replay()     # per_call steps
+            which[0] += 1
+        elif fused:
+            fused(x, next_copy())
         else:
             step_nccl()
 
@@ -359,7 +367,7 @@ def run_ours(args):
         return sorted((ms / (calls * steps_per_call)).tolist())
 
     calls = max(1, args.steps // per_call)
-    steps = calls * per_call                      # exactly what a block times (equal to --steps when it divides)
+    steps = calls * per_call                      # = --steps: a block is one graph of that many steps, or that many eager steps
     for _ in range(max(args.warmup, 3)):
         step()
     sampler = ClockSampler(local) if rank == 0 else None

@@ -61,15 +61,39 @@ __device__ __forceinline__ float silu_f(float v) { return __fdividef(v, 1.0f + _
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __uint_as_float((uint32_t) __bfloat16_as_ushort(v) << 16); }
 
+// Activations may have been written by the kernel right before this one on the stream, which can still be running when
+// this kernel starts (programmatic dependent launch). They are therefore read with ordinary coherent loads written as
+// volatile asm: such a load stays behind the grid dependency wait (the read-only ld.global.nc path may be moved above it
+// and may serve lines fetched before the producer's stores), and it still caches in L1 for the other rows of the block.
+__device__ __forceinline__ uint4 ld_act16(const void * p) {
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint2 ld_act8(const void * p) {
+    uint2 v;
+    asm volatile("ld.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float ld_act_f32(const float * p) {
+    float v;
+    asm volatile("ld.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
 // x[i..i+3] as FP32 from global memory (i a multiple of 4; the caller guarantees 16-/8-byte alignment)
-__device__ __forceinline__ float4 ldg_x4(const float * x, int i) { return __ldg((const float4 *) (x + i)); }
+__device__ __forceinline__ float4 ldg_x4(const float * x, int i) {
+    const uint4 v = ld_act16(x + i);
+    return make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
+}
 __device__ __forceinline__ float4 ldg_x4(const __nv_bfloat16 * x, int i) {
-    const uint2 v = __ldg((const uint2 *) (x + i));
+    const uint2 v = ld_act8(x + i);
     return make_float4(bf16lo_f32(v.x), bf16hi_f32(v.x), bf16lo_f32(v.y), bf16hi_f32(v.y));
 }
-__device__ __forceinline__ float ldg_x1(const float * x, int i) { return __ldg(x + i); }
+__device__ __forceinline__ float ldg_x1(const float * x, int i) { return ld_act_f32(x + i); }
 __device__ __forceinline__ float ldg_x1(const __nv_bfloat16 * x, int i) {
-    return __uint_as_float((uint32_t) __ldg((const unsigned short *) x + i) << 16);
+    unsigned short v;
+    asm volatile("ld.global.u16 %0, [%1];" : "=h"(v) : "l"(x + i) : "memory");
+    return __uint_as_float((uint32_t) v << 16);
 }
 
 // ---------------------------------------------------------------- output

@@ -671,7 +671,7 @@ __global__ void __launch_bounds__(1024) k_fo_gemv_staged(const PairView w, const
     grid_dependency_wait();
     for (int i = threadIdx.x; i < 8 * (K / 8); i += blockDim.x) { // 16-byte pieces; columns beyond ncols are zero
         const int n = i / (K / 8), c = i - n * (K / 8);
-        const uint4 v = n < ncols ? __ldg((const uint4 *) (p.x + n * p.x_tok) + c) : make_uint4(0, 0, 0, 0);
+        const uint4 v = n < ncols ? ld_act16((const uint4 *) (p.x + n * p.x_tok) + c) : make_uint4(0, 0, 0, 0);
         *(uint4 *) (xs + n * XS + c * 8) = v;
     }
     const uint32_t n_units = (uint32_t) hdr->n_a, n_words = (uint32_t) hdr->n_b;

@@ -43,21 +43,6 @@ struct ExpertCols {
                                                // activations do
 };
 
-// Loads of data the kernel before this one on the stream may still be writing when this kernel starts (programmatic
-// dependent launch): issued after the grid dependency wait and kept there. They are volatile asm with a memory clobber
-// and use the coherent path; the read-only (__ldg) path may be hoisted above the wait by the compiler and may serve
-// lines fetched before the producer's stores.
-__device__ __forceinline__ float4 ld_dep_x4(const float * p) {
-    float4 v;
-    asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ float4 ld_dep_x4(const __nv_bfloat16 * p) {
-    uint2 v;
-    asm volatile("ld.global.cg.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-    return make_float4(bf16lo_f32(v.x), bf16hi_f32(v.x), bf16lo_f32(v.y), bf16hi_f32(v.y));
-}
-
 template <int C, int R, bool CM, typename TX, bool GLU_IN, bool PLANE_STAGED>
 __global__ void __launch_bounds__(256) k_expert_units(const ExpertMat m0, const ExpertMat m1, const ExpertCols p, const Opaque k) {
     constexpr int K = C * CHUNK;
@@ -116,9 +101,9 @@ __global__ void __launch_bounds__(256) k_expert_units(const ExpertMat m0, const 
 #pragma unroll
         for (int i = 0; i < C * 4; i++) {
             const int at = (i >> 2) * CHUNK + 128 * (i & 3) + 4 * lane;
-            float4 v = ld_dep_x4((const TX *) xp + at);
+            float4 v = ldg_x4((const TX *) xp, at); // an ordered load: stays behind the dependency wait
             if (GLU_IN) {
-                const float4 g = v, w2 = ld_dep_x4(x2 + at);
+                const float4 g = v, w2 = ldg_x4(x2, at);
                 v = make_float4(silu_f(g.x) * w2.x, silu_f(g.y) * w2.y, silu_f(g.z) * w2.z, silu_f(g.w) * w2.w);
             }
             xr[i] = v;
@@ -217,9 +202,9 @@ __global__ void k_combine_f32(const float * __restrict__ ys, const float * __res
     const OutVec out = {y + (int64_t) t * n * (y_bf16 ? 2 : 4), y_bf16};
     for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) {
         float acc = 0.f;
-        for (int kx = 0; kx < n_used; kx++) {
+        for (int kx = 0; kx < n_used; kx++) { // the slot outputs come from the launch right before this one: ordered loads
             const int64_t s = (int64_t) t * n_used + kx;
-            acc = fmaf(w[s], ys[s * n + i], acc);
+            acc = fmaf(w[s], ld_act_f32(ys + s * n + i), acc);
         }
         out.put(i, acc);
         peers_put(peers, (int64_t) t * n * (y_bf16 ? 2 : 4), y_bf16, i, acc);
@@ -233,9 +218,9 @@ __global__ void k_peer_sum(const float * __restrict__ parts, int n_parts, int64_
     grid_dependency_wait();
     const OutVec out = {y, y_bf16};
     for (int64_t i = blockIdx.x * (int64_t) blockDim.x + threadIdx.x; i < n; i += (int64_t) gridDim.x * blockDim.x) {
-        float acc = parts[i];
-        for (int r = 1; r < n_parts; r++) { acc += parts[(int64_t) r * n + i]; }
-        if (extra) { acc += extra[i]; }
+        float acc = ld_act_f32(parts + i); // stored by the launch before this one and by the peers' kernels: ordered loads
+        for (int r = 1; r < n_parts; r++) { acc += ld_act_f32(parts + (int64_t) r * n + i); }
+        if (extra) { acc += ld_act_f32(extra + i); }
         out.put(i, acc);
     }
 }

@@ -143,7 +143,7 @@ template <int C> struct LaneX<C, bf16> {
     uint2 q[C * 4]; // two BF16 pairs per column quad
     __device__ __forceinline__ void load(const bf16 * x, int lane) {
 #pragma unroll
-        for (int i = 0; i < C * 4; i++) { q[i] = __ldg((const uint2 *) (x + (i >> 2) * CHUNK + 128 * (i & 3) + 4 * lane)); }
+        for (int i = 0; i < C * 4; i++) { q[i] = ld_act8(x + (i >> 2) * CHUNK + 128 * (i & 3) + 4 * lane); }
     }
     // acc += w.lo * x.lo ; acc2 += w.hi * x.hi with BF16 operands and FP32 accumulate
     static __device__ __forceinline__ void fma2(uint32_t w, uint32_t x, float & lo, float & hi) {
