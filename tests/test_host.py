@@ -162,3 +162,27 @@ def test_adapter_choose_follows_the_llama_policy(policy_table):
         n_checked += 1
     assert n_checked > 100
     assert lib().bf16n_adapter_count() == 0
+
+
+def test_choose_for_machine_keeps_the_reference_table_at_512_units(policy_table):
+    """The machine-size argument of the shape policy: 512 reproduces every row of the reference's table; a B200-sized
+    machine (148 SMs x 24 warps) shortens the units of small dense shards only."""
+    from orin_qwen_lossless_b200 import ops
+    for rows, K, n, engine, mode, expert, dfo, want in policy_table:
+        got = ops.choose(rows, K, n, engine=engine, mode=mode, expert=bool(expert), dense_frag_order=bool(dfo), min_units=512)
+        assert (None if got is None else [got[0], got[1], int(got[2]), int(got[3])]) == want
+    big = 148 * 24
+    assert [ops.choose(r, 2048, engine="llama", mode="huffman", min_units=big)[1] for r in (248320, 124160, 62080, 31040)] == [16, 16, 16, 8]
+    assert ops.choose(31040, 2048, engine="llama", mode="huffman")[1] == 16
+
+
+def test_ep_layout_is_aligned_and_large_enough():
+    import ctypes as C
+    from orin_qwen_lossless_b200._lib import EpLayout, lib
+    lay = EpLayout()
+    lay.n_ranks, lay.rank, lay.cap, lay.K, lay.H, lay.n_pairs_max = 8, 3, 8192, 2048, 2048, 8192
+    n = lib().bf16n_ep_layout_bytes(C.byref(lay))
+    offs = [lay.off_counts, lay.off_expert, lay.off_pair, lay.off_rows, lay.off_back]
+    assert offs == sorted(offs) and all(o % 256 == 0 for o in offs)
+    assert lay.off_pair - lay.off_expert >= 4 * 8 * 8192 and lay.off_back - lay.off_rows >= 2 * 8 * 8192 * 2048
+    assert n >= lay.off_back + 4 * 8192 * 2048
