@@ -15,8 +15,8 @@ serve it (config.l2 says what was done).
 
 One JSON line on stdout (rank 0):
   value    GB/s of compressed bytes (plane + aux + x + y) per second with everything resident in HBM
-  e2e      the same with the activation in pinned host memory and the logits back in host memory every step (one GPU:
-           ops.linear_host; several: sharded.HostGatheredLinear, one host buffer shared by the ranks)
+  e2e      the same with the activation in pinned host memory and the logits back in host memory every step
+           (sharded.HostGatheredLinear: one host buffer shared by the ranks, written by the GEMV kernels)
   roofline achieved / measured copy bandwidth for the GEMV kernel (one launch per step)
   cublas_bf16_gemv_us   the stock BF16 GEMV of the same (uncompressed) shard on the same GPU
   multi_token           the same matrix with 2 and 4 activation columns (one decode for all of them)
@@ -299,32 +299,32 @@ def run_ours(args):
     # end to end: activation from pinned host memory, logits back in host memory, every step
     hosted = None
     y_host = None
-    if world == 1:
-        y_host = torch.empty((1, rows), dtype=torch.float32).pin_memory()
-    else:
-        from orin_qwen_lossless_b200 import sharded
-        try:   # every rank's kernel stores its shard into one pinned host buffer shared by the processes of the node
-            hosted = sharded.HostGatheredLinear(enc, rows, R, 1)
-        except (RuntimeError, OSError) as e:
-            fused_note = (fused_note + "; " if fused_note else "") + f"shared host buffer unavailable: {e}"
+    from orin_qwen_lossless_b200 import sharded
+    try:   # every rank's kernel stores its shard into one pinned host buffer shared by the processes of the node
+        hosted = sharded.HostGatheredLinear(enc, rows, R, 1)
+    except (RuntimeError, OSError) as e:
+        fused_note = (fused_note + "; " if fused_note else "") + f"shared host buffer unavailable: {e}"
+    if world > 1:
         agree = torch.tensor([0 if hosted else 1], dtype=torch.int32, device=dev)
         dist.all_reduce(agree)
         if int(agree.item()) and hosted:
             hosted.close()
             hosted = None
-        if hosted is None:
-            y_host = torch.empty((1, world * (fused.width if fused else width)), dtype=torch.float32).pin_memory()
+    if hosted is None:
+        y_host = torch.empty((1, rows if world == 1 else world * (fused.width if fused else width)), dtype=torch.float32).pin_memory()
 
     def step_e2e():
+        if hosted is not None:
+            # one graph launch (activation copy from pinned memory + GEMV whose kernel stores the logits into the shared
+            # host buffer and then this rank's epoch word), then a spin on every rank's epoch word
+            hosted.w = next_copy()
+            hosted.step(x_host)
+            return
         if world == 1:
-            # one GPU: ops.linear_host without a device buffer for the logits: x is copied in (4 KB), the kernel stores
-            # the logits into the pinned host buffer itself, so the D2H traffic is the kernel's own stores
+            # ops.linear_host without a device buffer for the logits: x is copied in (4 KB), the kernel stores the
+            # logits into the pinned host buffer itself, so the D2H traffic is the kernel's own stores
             ops.linear_host(x_host, next_copy(), y_host, x)
             torch.cuda.current_stream().synchronize()  # a decode step consumes its logits on the host
-            return
-        if hosted is not None:
-            hosted.w = next_copy()
-            hosted.step(x_host, x)   # copy in, GEMV straight into the shared host buffer, synchronise, wait for every rank's epoch word
             return
         x.copy_(x_host, non_blocking=True)
         if fused:
@@ -380,7 +380,7 @@ def run_ours(args):
         nccl_us = statistics.median(blocks(step_nccl, args.steps)) * 1e3
     # the GEMV launch alone (no collective), per launch, on the launching stream: the roofline figure
     kernel_ms = ms_step if world == 1 else statistics.median(blocks(lambda: ops.mmv(x, next_copy(), out=mine), args.steps))
-    for _ in range(3):
+    for _ in range(6 * n_copies + 3):   # every (weight copy, logits buffer) pair reaches its captured graph
         step_e2e()
     e2e_steps = blocks(step_e2e, args.steps)
     ms_e2e = statistics.median(e2e_steps)
@@ -485,10 +485,12 @@ def run_ours(args):
         "e2e": {"value": algo_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": K * 2, "d2h_bytes_per_step": int(rows * 4 if (hosted_used or world == 1) else world * fused_width * 4),
                 "us_per_step": ms_e2e * 1e3, "us_per_step_min": e2e_steps[0] * 1e3, "us_per_step_max": e2e_steps[-1] * 1e3,
-                "how": ("activation copied in from pinned host memory, logits stored by the GEMV kernel straight into pinned host memory"
-                        + (" shared by the ranks of the node (every rank writes its shard; epoch words in the buffer tell every process when all shards are there)"
-                           if hosted_used else "") if (hosted_used or world == 1) else
-                        "activation copied in, gathered logits copied out behind the kernel") + ", stream synchronised every step"},
+                "how": ("one graph launch per step: activation copied in from pinned host memory, logits stored by the GEMV kernel straight "
+                        "into a pinned host buffer shared by the ranks of the node (every rank's kernel writes its shard and then its epoch "
+                        "word); the step ends when the host has seen every rank's epoch word (no stream synchronise)" if hosted_used else
+                        "activation copied in from pinned host memory, logits stored by the GEMV kernel straight into pinned host memory, "
+                        "stream synchronised every step" if world == 1 else
+                        "activation copied in, gathered logits copied out behind the kernel, stream synchronised every step")},
         "gpu_launches": steps,   # one kernel per step at every N
         "nccl_allgather_us_per_step": nccl_us,
         "kernel_alone_us": kernel_ms * 1e3,

@@ -273,10 +273,11 @@ class FusedShardedLinear:
 class HostGatheredLinear:
     """Row-sharded projection whose logits land in HOST memory: one pinned buffer shared by the ranks of a node (POSIX
     shared memory, registered with CUDA in every process), into which every rank's GEMV kernel stores its shard
-    directly, so the logits cross as many PCIe links as there are GPUs and no copy follows the kernels. A decode step
-    that consumes its logits on the host (sampling) calls step(): activation in from pinned host memory, GEMV, stream
-    synchronise, then an epoch word per rank in the shared buffer tells every process when all shards are there. Two
-    logits buffers alternate: a rank cannot start step s + 2 before every rank has finished step s + 1, i.e. has
+    directly, so the logits cross as many PCIe links as there are GPUs and no copy follows the kernels. The kernel treats
+    the host buffer as its one "peer" (bf16n_mmv_peers): after its last block's stores it writes the step number into
+    this rank's epoch word in the shared buffer, so a step is one graph launch (activation copy from pinned memory +
+    GEMV) and a spin on the ranks' epoch words: no stream synchronise, and every process sees when all shards are there.
+    Two logits buffers alternate: a rank cannot start step s + 2 before every rank has finished step s + 1, i.e. has
     consumed the logits of step s. compute(x, out) replaces the GPU product in the CPU tests of the exchange."""
 
     FLAG_STRIDE = 16  # int32 words between the ranks' epoch words (64 bytes: one cache line each)
@@ -315,22 +316,56 @@ class HostGatheredLinear:
             if int(rc) != 0:
                 raise RuntimeError(f"bf16n HostGatheredLinear: cudaHostRegister failed ({rc})")
             self._registered = True
+            dev = weight.plane.device
+            self._hdr = torch.zeros(HEADER_BYTES // 4, dtype=torch.int32, device=dev)   # block counter and step number of the kernel
+            self._y_dev = torch.empty(max_tokens, rows_total, dtype=torch.float32, device=dev)
+            self._x_dev = torch.empty(max_tokens, weight.meta.K, dtype=torch.bfloat16, device=dev)
+            a0 = self.ranges[self.rank][0]
+            self._outs = []
+            for b in range(2):
+                o = PeerOut()
+                o.n_peers, o.wait_mask = 1, 0
+                o.y[0] = self._np.ctypes.data + self.header + b * area + 4 * a0
+                o.flag[0] = self._np.ctypes.data + 4 * self.rank * self.FLAG_STRIDE
+                o.local_header = self._hdr.data_ptr()
+                self._outs.append(o)
+            self._graphs = {}   # (activation address, tokens, buffer, weight address) -> None after the first eager step, then its graph
         self.epoch = 0
 
-    def step(self, x_host: torch.Tensor, x_dev: torch.Tensor | None = None) -> torch.Tensor:
-        """x_host [T, K] pinned -> logits [T, rows_total] (host; valid until the step after the next one), complete in
-        every process when the call returns."""
+    def _launch(self, x_host: torch.Tensor, b: int) -> None:
+        T = x_host.shape[0]
         a0, a1 = self.ranges[self.rank]
-        logits = self._bufs[self.epoch & 1]
-        mine = logits[:, a0:a1]
+        x = self._x_dev[:T]
+        x.copy_(x_host, non_blocking=True)
+        mmv_peers(x, self.w, self._y_dev[:T, a0:a1], self._outs[b])
+
+    def step(self, x_host: torch.Tensor, x_dev: torch.Tensor | None = None) -> torch.Tensor:
+        """x_host [T, K] BF16 pinned -> logits [T, rows_total] (host; valid until the step after the next one), complete
+        in every process when the call returns. The first step from a given activation buffer launches eagerly, the
+        second captures a graph, later ones replay it."""
+        b = self.epoch & 1
+        logits = self._bufs[b][: x_host.shape[0]]
         if self.compute is not None:
-            self.compute(x_host, mine)
+            a0, a1 = self.ranges[self.rank]
+            self.compute(x_host, logits[:, a0:a1])
+            self.epoch += 1
+            self.flags[self.rank * self.FLAG_STRIDE] = self.epoch
         else:
-            x_dev.copy_(x_host, non_blocking=True)
-            ops.mmv(x_dev, self.w, out=mine)
-            torch.cuda.current_stream().synchronize()
-        self.epoch += 1
-        self.flags[self.rank * self.FLAG_STRIDE] = self.epoch     # after the synchronise: this rank's shard is in host memory
+            if x_host.dtype != torch.bfloat16 or not x_host.is_pinned() or x_host.dim() != 2 or x_host.shape[0] > self.T:
+                raise ValueError("bf16n HostGatheredLinear: x_host is a pinned BF16 [T <= max_tokens, K] tensor")
+            key = (x_host.data_ptr(), x_host.shape[0], b, self.w.plane.data_ptr())
+            g = self._graphs.get(key, False)
+            if g is False:
+                self._launch(x_host, b)
+                self._graphs[key] = None
+            else:
+                if g is None:
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g):
+                        self._launch(x_host, b)
+                    self._graphs[key] = g
+                g.replay()
+            self.epoch += 1   # the kernel's last block writes the same number into this rank's epoch word
         for r in range(self.world):
             spins = 0
             while self.flags[r * self.FLAG_STRIDE] < self.epoch:
@@ -342,6 +377,7 @@ class HostGatheredLinear:
     def close(self) -> None:
         if self._registered:
             torch.cuda.synchronize()
+            self._graphs = {}
             torch.cuda.cudart().cudaHostUnregister(self._np.ctypes.data)
             self._registered = False
         self._bufs = self.flags = self._np = None

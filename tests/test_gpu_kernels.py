@@ -457,3 +457,25 @@ def test_mmv_group_equals_single_launches(ops):
     torch.cuda.synchronize()
     assert all(torch.equal(y, ops.mmv(x, w)) for x, w, y in zip(xs, ws, outs))
     assert ops.mmv_group([], []) == []
+
+
+def test_host_gathered_projection_on_one_gpu(ops):
+    """The end-to-end projection (activation from pinned host memory, logits stored into host memory by the kernel, which
+    then writes the step number the host waits for): eager, captured and replayed steps equal ops.mmv bitwise."""
+    from orin_qwen_lossless_b200 import sharded
+    rows, K, R = 16 * 148 * 16, 2048, 16
+    w = up(ops, o.weights_like(rows, K, 21), HP, R, False)
+    hg = sharded.HostGatheredLinear(w, rows, R, 2)
+    try:
+        for T in (1, 2):
+            xh = torch.empty((T, K), dtype=torch.bfloat16).pin_memory()
+            for i in range(5):
+                xi = to_bf16_tensor(o.f32_to_bf16_bits(np.random.default_rng(90 + i).standard_normal((T, K)).astype(np.float32)))
+                xh.copy_(xi)
+                got = hg.step(xh).clone()
+                assert torch.equal(got, ops.mmv(xi.cuda(), w).cpu())
+        assert ops.fault_status() == 0
+        with pytest.raises(ValueError):
+            hg.step(torch.empty((1, K), dtype=torch.bfloat16))   # not pinned
+    finally:
+        hg.close()

@@ -74,6 +74,20 @@ def _worker(rank, world, port, ret):
             ok1b = ok1b and not fused.xchg.expired()
             fused.close()
 
+        # 1c. the end-to-end form: every rank's kernel stores its shard into one pinned host buffer shared by the processes
+        # and then its epoch word; eager, captured and replayed steps, one and two tokens
+        hg = sharded.HostGatheredLinear(ops.upload(sp, sa, sm, dev), rows, R, 2)
+        ok1c = True
+        for T1 in (1, 2):
+            xh = torch.empty((T1, K), dtype=torch.bfloat16).pin_memory()
+            for i in range(6):
+                xi = to_bf16_tensor(o.f32_to_bf16_bits(np.random.default_rng(70 + i).standard_normal((T1, K)).astype(np.float32)))
+                xh.copy_(xi)
+                got = hg.step(xh).clone()
+                ok1c = ok1c and bool(torch.equal(got, ops.mmv(xi.to(dev), ops.upload(p, a, m, dev)).cpu()))
+        hg.close()
+        ok1b = ok1b and ok1c
+
         # 2. MoE decode, experts split over the ranks
         bits = {"gate": o.weights_like(E * N, H, 11), "up": o.weights_like(E * N, H, 12), "down": o.weights_like(E * H, N, 13)}
         n_local = E // world
