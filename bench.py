@@ -732,7 +732,14 @@ def moe_prefill_runs(args, torch, dist, ops, rank, world, dev, weights, fo=False
     hbm, _ = measured_peak()
     burst, sustained, _ = measured_tensor_peaks()
     out = []
+    # two-pass form (decode into BF16 operand tiles in a workspace, then the tensor-core pass over the tiles) unless
+    # --fused-prefill asks for the fused decode-and-multiply kernel; fragment-order experts have their own kernel
+    two_pass = not fo and not args.fused_prefill
+    ws_bytes = ops.ensure_workspace((gate, up), (down, None)) if two_pass else 0
+    form = ("fragment-order kernel" if fo else "two-pass: decode into BF16 operand tiles (%.0f MB workspace), tcgen05 pass over the tiles" % (ws_bytes / 1e6)
+            if two_pass else "fused decode-and-multiply kernel")
     for T in (2048, 8192):
+        fused_us = None
         flops = 6.0 * 512 * 2048 * k * T
         nbytes = (gate.nbytes + up.nbytes + down.nbytes) * world
         g = torch.Generator(device=dev).manual_seed(4321 + T + rank)
@@ -743,6 +750,10 @@ def moe_prefill_runs(args, torch, dist, ops, rank, world, dev, weights, fo=False
             us = med
             y = ops.moe_experts(x, gate, up, down, wts, ids, E)
             par = "1 GPU"
+            if two_pass:   # the fused kernel on the same inputs, for comparison
+                ops.set_workspace(None)
+                fused_us = _time_graph(torch, lambda: ops.moe_experts(x, gate, up, down, wts, ids, E), max(args.steps // 100, 5))[0]
+                ops.ensure_workspace((gate, up), (down, None))
         elif not args.nccl:
             # tokens data-parallel (T / world per rank), experts sharded: every routed row is stored into the exchange
             # buffer of its expert's rank by a kernel (peer stores over NVLink), multiplied there by the batched kernels
@@ -790,12 +801,16 @@ def moe_prefill_runs(args, torch, dist, ops, rank, world, dev, weights, fo=False
             got = y[:n].float().cpu().numpy()
             hbm_us, tensor_us = nbytes / world / hbm / 1e3, flops / world / burst / 1e6
             out.append({"tokens": T, "n_gpus": world, "parallelism": par, "layout": "fragment order" if fo else "lane-major (chunk-major R=8 gate/up, R=16 down)",
-                        "us_per_layer": us, "us_min": lo, "us_max": hi, "TFLOPs": flops / us / 1e6, "weight_GBps": nbytes / us / 1e3,
+                        "form": form, "us_per_layer": us, "us_min": lo, "us_max": hi, "us_per_layer_fused_kernel": fused_us,
+                        "TFLOPs": flops / us / 1e6, "weight_GBps": nbytes / us / 1e3,
                         "roofline": {"hbm_bound_us": hbm_us, "tensor_bound_us": tensor_us, "tensor_bound_us_sustained": flops / world / sustained / 1e6,
                                      "bound": "hbm" if hbm_us > tensor_us else "tensor", "frac": max(hbm_us, tensor_us) / us,
                                      "flops": flops, "compressed_bytes": nbytes},
                         "parity": {"tokens_checked": n, "max_err_over_max_abs": float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-30)),
                                    "what": "BF16 layer output of the first tokens of rank 0 against the FP64 layer (BF16 SwiGLU activations)"}})
+    if two_pass:
+        torch.cuda.synchronize()
+        ops.set_workspace(None)
     return out
 
 
@@ -938,6 +953,7 @@ def main():
     ap.add_argument("--rows", type=int, default=ROWS, help="rows of the matrix (default: the vocabulary projection)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-moe", action="store_true", help="skip the MoE layer and small-matrix blocks of the contract line")
+    ap.add_argument("--fused-prefill", action="store_true", help="MoE prefill: the fused decode-and-multiply kernel instead of the two-pass form")
     ap.add_argument("--fo", action="store_true", help="moe_prefill: experts in the fragment-order layout (mma.sync batched kernel)")
     ap.add_argument("--nccl", action="store_true", help="N > 1, MoE workloads: NCCL collectives instead of the fused peer stores")
     ap.add_argument("--workload", default="lm_head", choices=["lm_head", "small", "moe_decode", "moe_prefill", "dense_mid"],

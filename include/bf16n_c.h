@@ -147,6 +147,18 @@ int bf16n_mm_ids(const bf16n_weight * w, const bf16n_weight * up, const void * x
                  const int32_t * ids_src1, const int32_t * ids_dst, const int32_t * bounds, void * dst, int dst_bf16,
                  int64_t dst_col, int n_experts, int n_tok, int n_used, void * stream);
 
+
+/* No reference counterpart: a caller-owned device buffer for the two-pass form of bf16n_mm_ids. With a workspace of at
+ * least bf16n_mm_ids_workspace_bytes(w, up) bytes registered, bf16n_mm_ids on lane-major HUFPAIR experts first decodes the
+ * experts that have routed pairs into BF16 operand tiles in the workspace (every SM's warps decoding, no tensor core)
+ * and then multiplies from those tiles on the tensor cores (bulk copies into shared memory, tcgen05.mma with N = 256);
+ * without one (the default), or when it is too small, the fused decode-and-multiply kernel runs. Results of the two
+ * forms agree to FP32 accumulation order, not bitwise. The library never allocates or frees the buffer; it is used by
+ * the launches of one stream at a time and must stay valid while they (or CUDA graphs captured from them) can run.
+ * workspace = NULL withdraws it. bf16n_mm_ids_workspace_bytes returns 0 for matrices the two-pass form does not take
+ * (fragment order, NIBBLE, other unit shapes): rows * K * 2 bytes for one matrix, twice that for a gate/up pair. */
+size_t bf16n_mm_ids_workspace_bytes(const bf16n_weight * w, const bf16n_weight * up);
+int bf16n_set_workspace(void * workspace, size_t bytes);
 /* y[t, i] = sum_k w[t, k] * ys[t, k, i] in slot order (FP32). Replaces bf16n::moe_combine (launch.h:81-82,
  * launch.cu:539-572). */
 int bf16n_moe_combine(const float * ys, const void * w, int w_bf16, void * y, int y_bf16, int n_tok, int n_used, int64_t n,

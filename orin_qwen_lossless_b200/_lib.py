@@ -65,6 +65,8 @@ SIGNATURES = {
     "bf16n_verify": (C.c_int, [C.POINTER(Weight), C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "bf16n_get_rows": (C.c_int, [C.POINTER(Weight), C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_int64]),
     "bf16n_mm_ids_supported": (C.c_int, [C.POINTER(Weight), C.POINTER(Weight)]),
+    "bf16n_mm_ids_workspace_bytes": (C.c_size_t, [C.POINTER(Weight), C.POINTER(Weight)]),
+    "bf16n_set_workspace": (C.c_int, [C.c_void_p, C.c_size_t]),
     "bf16n_mm_ids_route": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "bf16n_mm_ids": (C.c_int, [C.POINTER(Weight), C.POINTER(Weight), C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "bf16n_moe_combine": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_void_p]),

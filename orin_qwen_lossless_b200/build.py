@@ -17,7 +17,7 @@ OBJ = os.path.join(PKG, "build")
 LIB = os.path.join(PKG, "libbf16n_b200.so")
 INC = os.path.join(os.path.dirname(PKG), "include")
 
-CUDA_SOURCES = ["gemv.cu", "gemv_staged.cu", "gemv_rings.cu", "moe.cu", "moe_decode.cu", "prefill.cu", "peer.cu", "fo.cu", "draft.cu", "adapter.cu", "ep_prefill.cu", "capi.cu"]
+CUDA_SOURCES = ["gemv.cu", "gemv_staged.cu", "gemv_rings.cu", "moe.cu", "moe_decode.cu", "prefill.cu", "expand_tiles.cu", "peer.cu", "fo.cu", "draft.cu", "adapter.cu", "ep_prefill.cu", "capi.cu"]
 HOST_SOURCES = ["encode.cpp", "policy.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC,-pthread",
               "-I", INC]

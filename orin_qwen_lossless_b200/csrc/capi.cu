@@ -364,6 +364,17 @@ int bf16n_mm_ids(const bf16n_weight * w, const bf16n_weight * up, const void * x
     });
 }
 
+size_t bf16n_mm_ids_workspace_bytes(const bf16n_weight * w, const bf16n_weight * up) {
+    return w ? prefill_workspace_bytes(*w, up) : 0;
+}
+
+int bf16n_set_workspace(void * workspace, size_t bytes) {
+    return guarded([&] {
+        require(!workspace || ((uintptr_t) workspace % 1024) == 0, "set_workspace: the buffer must be 1024-byte aligned");
+        prefill_set_workspace(workspace, bytes);
+    });
+}
+
 int bf16n_moe_combine(const float * ys, const void * w, int w_bf16, void * y, int y_bf16, int n_tok, int n_used, int64_t n,
                       void * stream) {
     return guarded([&] {

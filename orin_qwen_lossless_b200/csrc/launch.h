@@ -140,6 +140,11 @@ void draft_gemv(int bits, const void * x_bf16, int T, const uint8_t * q, const f
 
 // prefill.cu
 void prefill_init();
+void expand_tiles_init();
+bool expand_tiles_supported(const bf16n_weight & w);
+void expand_tiles(const bf16n_weight & w, const bf16n_weight * up, int n_experts, const int32_t * bounds, void * images, cudaStream_t st);
+void prefill_set_workspace(void * p, size_t bytes);
+size_t prefill_workspace_bytes(const bf16n_weight & w, const bf16n_weight * up);
 bool prefill_supported(const bf16n_weight & w, const bf16n_weight * up);
 void prefill_mm_ids(const bf16n_weight & w, const bf16n_weight * up, const void * x_bf16, int64_t x_row, const int32_t * ids_src1,
                     const int32_t * ids_dst, const int32_t * bounds, void * dst, bool dst_bf16, int64_t dst_col, int n_experts,

@@ -144,20 +144,23 @@ struct PrefillArgs {
 };
 
 // four consecutive output elements of one (token, slot) row
-__device__ __forceinline__ void store4(const PrefillArgs & p, int64_t at, float a, float b, float c, float d) {
-    if (p.dst_bf16) {
-        bf16 * o = (bf16 *) p.dst + at;
-        if (p.vec_ok) {
+__device__ __forceinline__ void store4(char * dst, bool dst_bf16, bool vec_ok, int64_t at, float a, float b, float c, float d) {
+    if (dst_bf16) {
+        bf16 * o = (bf16 *) dst + at;
+        if (vec_ok) {
             const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
             *(uint2 *) o = make_uint2(*(const uint32_t *) &lo, *(const uint32_t *) &hi);
         } else {
             o[0] = __float2bfloat16_rn(a); o[1] = __float2bfloat16_rn(b); o[2] = __float2bfloat16_rn(c); o[3] = __float2bfloat16_rn(d);
         }
     } else {
-        float * o = (float *) p.dst + at;
-        if (p.vec_ok) { *(float4 *) o = make_float4(a, b, c, d); }
+        float * o = (float *) dst + at;
+        if (vec_ok) { *(float4 *) o = make_float4(a, b, c, d); }
         else { o[0] = a; o[1] = b; o[2] = c; o[3] = d; }
     }
+}
+__device__ __forceinline__ void store4(const PrefillArgs & p, int64_t at, float a, float b, float c, float d) {
+    store4(p.dst, p.dst_bf16, p.vec_ok, at, a, b, c, d);
 }
 
 // C chunks per row, R rows per unit, CM chunk-major units, GLU fused gate/up + SwiGLU, G token groups of 128 per pass,
@@ -421,6 +424,295 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const PrefillArgs p) {
     if (warp == 0) { tmem_free(tmem, TMEM_COLS); }
 }
 
+// ---------------------------------------------------------------- second pass of the two-pass product
+//
+// k_tile_mm multiplies routed activation rows with weights that expand_tiles.cu has already decoded into operand-tile
+// images ([k-tile][256 rows][128 bytes], 128-byte swizzled, 32 KB per k-tile). Without decoders the block is six warps:
+//   * warps 0..3 gather the routed activation rows (cp.async into a ring of 128-token x 64-column slots, each slot's
+//     mbarrier completed by cp.async.mbarrier.arrive) and afterwards read the accumulators (tcgen05.ld: warp w reads TMEM
+//     lanes 32 w .. 32 w + 31 = tokens) and store them, SwiGLU applied in registers;
+//   * warp 4, one thread: tcgen05.mma with M = 128 tokens, N = 256 weight rows, K = 16; per (k-tile, token group) four of
+//     them; tcgen05.commit hands activation slots and weight stages back and announces the finished accumulators;
+//   * warp 5, one thread: one 32 KB bulk copy per k-tile of the item's image into a ring of four weight stages
+//     (mbarrier expect_tx / complete_tx).
+// A work item is (expert, row block of 256 image rows); a pass covers up to TM_G x 128 of the expert's tokens, whose
+// accumulators (TM_G x 256 columns) fill tensor memory. The activations of a pass cross L2 -> shared memory once per
+// 256 weight rows, and a weight k-tile is copied once per pass.
+constexpr int TM_N = 256, TM_G = 2, TM_WST = 4, TM_XSL = 6;
+constexpr int TM_GATHERERS = 128, TM_THREADS = 192, TM_MMA_WARP = 4, TM_W_WARP = 5;
+constexpr int TM_W_STAGE = TM_N * 128;       // one k-tile of a row block
+constexpr int TM_STAGE_ROW = 256 + 16;       // epilogue staging: 256 output bytes per thread, padded so that 16-byte stores of a quarter warp miss each other's banks
+constexpr int TM_STAGE_BYTES = TM_GATHERERS * TM_STAGE_ROW;
+static_assert(2 * TM_STAGE_BYTES <= TM_XSL * X_SLOT_BYTES, "the epilogue stages its output rows in the activation ring");
+__host__ __device__ constexpr uint32_t tm_instr_desc() { return 1u << 4 | 1u << 7 | 1u << 10 | (uint32_t) (TM_N >> 3) << 17 | (uint32_t) (M_TOK >> 4) << 24; }
+static_assert(TM_G * TM_N <= TMEM_COLS, "accumulators of a pass must fit TMEM");
+
+struct TileMmArgs {
+    const unsigned char * images;       // [expert][row block][k-tile][256][128 bytes]
+    const bf16 * x; int64_t x_row;
+    const int32_t * ids_src1; const int32_t * ids_dst; const int32_t * bounds;
+    char * dst; int64_t dst_col; bool dst_bf16;
+    bool vec_ok;                        // dst rows allow 4-element vector stores
+    bool bulk_ok;                       // dst rows are 16-byte aligned: BF16 rows may leave as 256-byte bulk stores
+    int n_experts, blocks_per_expert, ktiles;
+};
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void * src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// shared -> global bulk store (16-byte aligned addresses, size a multiple of 16), tracked by the thread's bulk groups
+__device__ __forceinline__ void bulk_s2g(void * dst, uint32_t src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void tm_helper_bar() { asm volatile("bar.sync 1, %0;" ::"n"(TM_GATHERERS) : "memory"); }
+
+template <bool GLU>
+__global__ void __launch_bounds__(TM_THREADS, 1) k_tile_mm(const TileMmArgs p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char * smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u); // operand tiles need 1024-byte alignment
+    unsigned char * wbuf = smem;                                   // TM_WST weight stages
+    unsigned char * xbuf = wbuf + TM_WST * TM_W_STAGE;             // TM_XSL activation slots
+    uint64_t * bars = (uint64_t *) (xbuf + TM_XSL * X_SLOT_BYTES);
+    uint64_t * w_full = bars, * w_empty = bars + TM_WST, * x_full = w_empty + TM_WST, * x_free = x_full + TM_XSL;
+    uint64_t * acc_done = x_free + TM_XSL, * drained = acc_done + 1, * fin = drained + 1;
+    uint32_t * tmem_slot = (uint32_t *) (fin + 1);
+    volatile int * failed = (volatile int *) (tmem_slot + 1);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        for (int i = 0; i < TM_WST; i++) { mbar_init(smem_u32(w_full + i), 1); mbar_init(smem_u32(w_empty + i), 1); }
+        for (int i = 0; i < TM_XSL; i++) { mbar_init(smem_u32(x_full + i), TM_GATHERERS); mbar_init(smem_u32(x_free + i), 1); }
+        mbar_init(smem_u32(acc_done), 1);
+        mbar_init(smem_u32(drained), 1);
+        mbar_init(smem_u32(fin), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        *failed = 0;
+    }
+    if (warp == 0) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const int n_items = p.n_experts * p.blocks_per_expert, KT = p.ktiles;
+
+    if (warp == TM_W_WARP) {
+        // ------------------------------------------------------------------ weight stages: one bulk copy per k-tile
+        if (lane == 0) {
+            uint32_t n = 0, issued = 0; // stages of the walk, copies actually started (equal until a wait fails)
+            for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+                const int e = item / p.blocks_per_expert;
+                const int j0 = p.bounds[e], j1 = p.bounds[e + 1];
+                const unsigned char * img = p.images + (int64_t) item * KT * TM_W_STAGE;
+                for (int jp = j0; jp < j1; jp += TM_G * M_TOK) {
+                    for (int kt = 0; kt < KT; kt++, n++) {
+                        const uint32_t s = n % TM_WST, use = n / TM_WST;
+                        if (use >= 1) { wait_on(w_empty + s, (use - 1) & 1, failed); }
+                        if (*failed) { continue; }
+                        mbar_expect_tx(smem_u32(w_full + s), TM_W_STAGE);
+                        bulk_g2s(smem_u32(wbuf + s * TM_W_STAGE), img + (int64_t) kt * TM_W_STAGE, TM_W_STAGE, smem_u32(w_full + s));
+                        issued++;
+                    }
+                }
+            }
+            if (*failed) { // copies may still be in flight: wait (bounded) for every stage's last one before the block ends
+                for (uint32_t back = 1; back <= (uint32_t) TM_WST && back <= issued; back++) {
+                    const uint32_t m = issued - back;
+                    mbar_poll(smem_u32(w_full + m % TM_WST), (m / TM_WST) & 1);
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ gather warps + epilogue, MMA warp
+        const int ht = tid, hw = warp;          // gather thread index / TMEM lane quarter (warps 0..3)
+        const bool mma_warp = warp == TM_MMA_WARP;
+        uint32_t n = 0;        // weight stages consumed
+        uint32_t vv = 0;       // activation slots used
+        uint32_t passes = 0;
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+            const int e = item / p.blocks_per_expert, nb = item - e * p.blocks_per_expert;
+            const int j0 = p.bounds[e], j1 = p.bounds[e + 1];
+            for (int jp = j0; jp < j1; jp += TM_G * M_TOK) {
+                const int ntok = min(TM_G * M_TOK, j1 - jp), ng = (ntok + M_TOK - 1) / M_TOK;
+                const int total = KT * ng;   // slots of the pass: for each k-tile, each token group
+                if (!mma_warp) {
+                    int64_t my_dst[TM_G];    // output row of the token whose accumulators this thread reads
+#pragma unroll
+                    for (int tg = 0; tg < TM_G; tg++) {
+                        const int ti = tg * M_TOK + ht;
+                        my_dst[tg] = ti < ntok ? (int64_t) p.ids_dst[jp + ti] : -1;
+                    }
+                    // ---- gather: this thread copies 16-byte piece pc of rows r0, r0 + 16, ... of every slot
+                    const int pc = ht & 7, r0 = ht >> 3;
+                    constexpr int RSTEP = TM_GATHERERS / 8, RMAX = M_TOK / RSTEP;
+                    const bf16 * src[TM_G][RMAX]; // the rows' activations at piece pc (nullptr: no such token)
+#pragma unroll
+                    for (int tg = 0; tg < TM_G; tg++) {
+#pragma unroll
+                        for (int i = 0; i < RMAX; i++) {
+                            const int ti = tg * M_TOK + r0 + i * RSTEP;
+                            src[tg][i] = ti < ntok ? p.x + (int64_t) p.ids_src1[jp + ti] * p.x_row + pc * 8 : nullptr;
+                        }
+                    }
+                    for (int si = 0; si < total; si++) {
+                        const int kt = si / ng, tg = si - kt * ng;
+                        const uint32_t vs = vv + (uint32_t) si, slot = vs % TM_XSL, use = vs / TM_XSL;
+                        if (use >= 1) { wait_on(x_free + slot, (use - 1) & 1, failed); }
+                        const uint32_t dst0 = smem_u32(xbuf + slot * X_SLOT_BYTES) + (uint32_t) r0 * 128;
+#pragma unroll
+                        for (int g2 = 0; g2 < TM_G; g2++) {
+                            if (g2 == tg) {
+#pragma unroll
+                                for (int i = 0; i < RMAX; i++) {
+                                    const int row = r0 + i * RSTEP;
+                                    if (src[g2][i]) { cp_async16(dst0 + i * RSTEP * 128 + ((pc ^ (row & 7)) << 4), src[g2][i] + kt * 64); }
+                                }
+                            }
+                        }
+                        cp_async_arrive(x_full + slot); // arrives once this thread's copies so far have landed
+                    }
+                    vv += (uint32_t) total;
+                    // ---- epilogue: TMEM -> registers -> dst
+                    wait_on(acc_done, passes & 1, failed);
+                    passes++;
+                    tc_fence_after();
+                    // A thread holds one token's accumulators; written row by row from there, a store instruction would touch
+                    // 32 different lines. Both output forms go through shared memory instead (the activation ring is idle
+                    // now: every MMA of the pass is complete).
+                    // A thread stages 256 bytes of its token's output row (128 BF16 SwiGLU outputs, or 64 FP32 outputs: four
+                    // pieces per token) and sends them with one bulk store; two staging rows per thread alternate, so a
+                    // store is read out while the next piece is staged. (Measured at 8192 tokens per layer: direct stores
+                    // 1.91 ms, bulk stores 1.64 ms, a warp-level transposition through shared memory with four whole
+                    // lines per store instruction 1.68 ms.)
+                    uint32_t piece_no = 0;
+                    const bool bulk_out = GLU && p.dst_bf16 && p.bulk_ok;
+                    for (int tg = 0; tg < ng; tg++) {
+                        const int64_t drow = my_dst[tg];
+                        const uint32_t taddr = tmem + ((uint32_t) (32 * hw) << 16) + (uint32_t) (tg * TM_N);
+                        const bool live = drow >= 0 && !*failed;
+                        if (GLU) { // image rows 0..127: gate, 128..255: the same rows of up
+                            const int64_t at0 = drow * p.dst_col + (int64_t) nb * (TM_N / 2);
+                            unsigned char * row = xbuf + (piece_no & 1) * TM_STAGE_BYTES + ht * TM_STAGE_ROW;
+                            if (bulk_out) { bulk_wait_read<1>(); } // the store that used this staging row two pieces ago has read it
+#pragma unroll 1
+                            for (int cc = 0; cc < TM_N / 2; cc += 32) {
+                                __syncwarp(); // the TMEM loads are warp-wide
+                                uint32_t v0[32], v1[32];
+                                tmem_ld32(taddr + cc, v0);
+                                tmem_ld32(taddr + TM_N / 2 + cc, v1);
+                                if (!live) { continue; }
+                                float r[32];
+#pragma unroll
+                                for (int u = 0; u < 32; u++) { r[u] = silu_f(__uint_as_float(v0[u])) * __uint_as_float(v1[u]); }
+                                if (bulk_out) {
+#pragma unroll
+                                    for (int u = 0; u < 32; u += 8) {
+                                        uint32_t o[4];
+#pragma unroll
+                                        for (int j = 0; j < 4; j++) {
+                                            const __nv_bfloat162 h = __floats2bfloat162_rn(r[u + 2 * j], r[u + 2 * j + 1]);
+                                            o[j] = *(const uint32_t *) &h;
+                                        }
+                                        *(uint4 *) (row + (cc + u) * 2) = make_uint4(o[0], o[1], o[2], o[3]);
+                                    }
+                                } else {
+#pragma unroll
+                                    for (int u = 0; u < 32; u += 4) { store4(p.dst, p.dst_bf16, p.vec_ok, at0 + cc + u, r[u], r[u + 1], r[u + 2], r[u + 3]); }
+                                }
+                            }
+                            if (bulk_out) {
+                                if (live) { proxy_fence(); bulk_s2g((bf16 *) p.dst + at0, smem_u32(row), 256); }
+                                bulk_commit();
+                                piece_no++;
+                            }
+                        } else if (!p.dst_bf16 && p.bulk_ok) {   // 256 FP32 outputs = four pieces of 64
+                            const int64_t at0 = drow * p.dst_col + (int64_t) nb * TM_N;
+#pragma unroll 1
+                            for (int c0 = 0; c0 < TM_N; c0 += 64) {
+                                unsigned char * row = xbuf + (piece_no & 1) * TM_STAGE_BYTES + ht * TM_STAGE_ROW;
+                                bulk_wait_read<1>();
+#pragma unroll 1
+                                for (int cc = c0; cc < c0 + 64; cc += 32) {
+                                    __syncwarp();
+                                    uint32_t v0[32];
+                                    tmem_ld32(taddr + cc, v0);
+                                    if (!live) { continue; }
+#pragma unroll
+                                    for (int u = 0; u < 32; u += 4) { *(uint4 *) (row + (cc - c0 + u) * 4) = make_uint4(v0[u], v0[u + 1], v0[u + 2], v0[u + 3]); }
+                                }
+                                if (live) { proxy_fence(); bulk_s2g((float *) p.dst + at0 + c0, smem_u32(row), 256); }
+                                bulk_commit();
+                                piece_no++;
+                            }
+                        } else {
+                            const int64_t at0 = drow * p.dst_col + (int64_t) nb * TM_N;
+#pragma unroll 1
+                            for (int cc = 0; cc < TM_N; cc += 32) {
+                                __syncwarp();
+                                uint32_t v0[32];
+                                tmem_ld32(taddr + cc, v0);
+                                if (!live) { continue; }
+#pragma unroll
+                                for (int u = 0; u < 32; u += 4) {
+                                    store4(p.dst, p.dst_bf16, p.vec_ok, at0 + cc + u, __uint_as_float(v0[u]), __uint_as_float(v0[u + 1]),
+                                           __uint_as_float(v0[u + 2]), __uint_as_float(v0[u + 3]));
+                                }
+                            }
+                        }
+                    }
+                    bulk_wait_read<0>(); // the staging rows are activation slots again from the next pass on
+                    __syncwarp();
+                    tc_fence_before();
+                    tm_helper_bar(); // all four quarters are read
+                    if (tid == 0) { mbar_arrive(smem_u32(drained)); } // the next pass may overwrite the accumulators
+                } else if (lane == 0) {
+                    // ---- MMA issue
+                    if (passes >= 1) { wait_on(drained, (passes - 1) & 1, failed); tc_fence_after(); }
+                    passes++;
+                    for (int si = 0; si < total; si++) {
+                        const int kt = si / ng, tg = si - kt * ng;
+                        const uint32_t s = n % TM_WST;
+                        const uint32_t vs = vv + (uint32_t) si, slot = vs % TM_XSL, use = vs / TM_XSL;
+                        if (tg == 0) { wait_on(w_full + s, (n / TM_WST) & 1, failed); }
+                        wait_on(x_full + slot, use & 1, failed);
+                        if (!*failed) {
+                            proxy_fence(); // the gather's copies (generic proxy) before the tensor core's reads (async proxy)
+                            tc_fence_after();
+                            const uint32_t d = tmem + (uint32_t) (tg * TM_N);
+                            const uint32_t a0 = smem_u32(xbuf + slot * X_SLOT_BYTES), b0 = smem_u32(wbuf + s * TM_W_STAGE);
+#pragma unroll
+                            for (int s2 = 0; s2 < 4; s2++) {
+                                umma_bf16(d, tile_desc(a0 + s2 * 32), tile_desc(b0 + s2 * 32), tm_instr_desc(), (kt | s2) != 0);
+                            }
+                        }
+                        umma_commit(x_free + slot);
+                        if (tg == ng - 1) { umma_commit(w_empty + s); n++; }
+                        if (si == total - 1) { umma_commit(acc_done); }
+                    }
+                    vv += (uint32_t) total;
+                }
+            }
+        }
+        if (!mma_warp) { cp_async_wait_all(); }
+        if (mma_warp && lane == 0 && *failed) {
+            // MMAs may still be in flight: wait (bounded) until the tensor core has drained before TMEM is freed
+            umma_commit(fin);
+            mbar_poll(smem_u32(fin), 0);
+            atomicOr(&g_prefill_fault, 1u);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) { tmem_free(tmem, TMEM_COLS); }
+}
+
+constexpr size_t TM_SMEM = (size_t) TM_WST * TM_W_STAGE + (size_t) TM_XSL * X_SLOT_BYTES + 256 + 1024;
+
 PairView view_of(const bf16n_weight & w) {
     return {w.plane, (const uint32_t *) (w.aux + w.off_a), (const uint32_t *) (w.aux + w.off_b),
             (const uint16_t *) (w.aux + w.off_c), (const uint32_t *) (w.aux + w.off_d)};
@@ -448,6 +740,9 @@ void prefill_init() {
                                  (int) smem_bytes<false, SLOTS_ONE>()), "k_prefill gate");
     cuda_ok(cudaFuncSetAttribute(k_prefill<1, 16, false, false, G_TOK, SLOTS_ONE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int) smem_bytes<false, SLOTS_ONE>()), "k_prefill down");
+    cuda_ok(cudaFuncSetAttribute(k_tile_mm<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) TM_SMEM), "k_tile_mm glu");
+    cuda_ok(cudaFuncSetAttribute(k_tile_mm<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) TM_SMEM), "k_tile_mm");
+    expand_tiles_init();
 }
 
 bool prefill_supported(const bf16n_weight & w, const bf16n_weight * up) {
@@ -457,6 +752,48 @@ bool prefill_supported(const bf16n_weight & w, const bf16n_weight * up) {
     const bool same = up->format == w.format && up->K == w.K && up->R == w.R && up->cm == w.cm && up->fo == w.fo && up->rows == w.rows;
     return same && w.format == FMT_HUFPAIR && w.K == 2048 && w.cm && w.R == 8;
 }
+
+// The caller's buffer for the decoded operand tiles of the two-pass product (bf16n_set_workspace): one per process, used
+// by one stream at a time.
+static void * g_workspace = nullptr;
+static size_t g_workspace_bytes = 0;
+
+void prefill_set_workspace(void * p, size_t bytes) {
+    g_workspace = p;
+    g_workspace_bytes = p ? bytes : 0;
+}
+
+size_t prefill_workspace_bytes(const bf16n_weight & w, const bf16n_weight * up) {
+    if (!expand_tiles_supported(w) || (up && !expand_tiles_supported(*up))) { return 0; }
+    return (size_t) w.rows * (size_t) w.K * 2 * (up ? 2 : 1);
+}
+
+namespace {
+
+// decode pass (expand_tiles.cu) + tensor-core pass over the decoded tiles
+bool two_pass(const bf16n_weight & w, const bf16n_weight * up, const PrefillArgs & a, int n_experts, cudaStream_t st) {
+    const size_t need = prefill_workspace_bytes(w, up);
+    const int rows_per_block = up ? TM_N / 2 : TM_N;
+    if (need == 0 || need > g_workspace_bytes || a.rows_per_expert % rows_per_block || ((uintptr_t) g_workspace % 1024)) { return false; }
+    expand_tiles(w, up, n_experts, a.bounds, g_workspace, st);
+    TileMmArgs t = {};
+    t.images = (const unsigned char *) g_workspace;
+    t.x = a.x; t.x_row = a.x_row;
+    t.ids_src1 = a.ids_src1; t.ids_dst = a.ids_dst; t.bounds = a.bounds;
+    t.dst = a.dst; t.dst_col = a.dst_col; t.dst_bf16 = a.dst_bf16;
+    t.vec_ok = a.vec_ok;
+    t.bulk_ok = ((uintptr_t) a.dst % 16) == 0 && (a.dst_col * (a.dst_bf16 ? 2 : 4)) % 16 == 0;
+    t.n_experts = n_experts;
+    t.blocks_per_expert = (int) (a.rows_per_expert / rows_per_block);
+    t.ktiles = (int) (w.K / 64);
+    const unsigned grid = (unsigned) std::min<int64_t>(device_info().sms, (int64_t) n_experts * t.blocks_per_expert);
+    if (up) { k_tile_mm<true><<<grid, TM_THREADS, TM_SMEM, st>>>(t); }
+    else { k_tile_mm<false><<<grid, TM_THREADS, TM_SMEM, st>>>(t); }
+    check_launch();
+    return true;
+}
+
+} // namespace
 
 void prefill_mm_ids(const bf16n_weight & w, const bf16n_weight * up, const void * x_bf16, int64_t x_row, const int32_t * ids_src1,
                     const int32_t * ids_dst, const int32_t * bounds, void * dst, bool dst_bf16, int64_t dst_col, int n_experts,
@@ -474,6 +811,7 @@ void prefill_mm_ids(const bf16n_weight & w, const bf16n_weight * up, const void 
     require(((uintptr_t) x_bf16 % 16) == 0 && (x_row * 2) % 16 == 0, "batched activations must be 16-byte aligned rows");
     const int rows_out = (up ? DEC_WARPS / 2 : DEC_WARPS) * w.R;
     require(a.rows_per_expert % rows_out == 0, "rows per expert must be a multiple of the batched kernel's row block");
+    if (g_workspace && two_pass(w, up, a, n_experts, st)) { return; }
     const unsigned grid = (unsigned) std::min<int64_t>(device_info().sms, (int64_t) n_experts * (a.rows_per_expert / rows_out));
     if (up) {
         k_prefill<4, 8, true, true, G_TOK, SLOTS_GLU><<<grid, NTHREADS, smem_bytes<true, SLOTS_GLU>(), st>>>(a);

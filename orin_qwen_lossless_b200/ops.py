@@ -560,6 +560,46 @@ def mm_ids_supported(w: Weight, up: Weight | None = None) -> bool:
     return bool(lib().bf16n_mm_ids_supported(C.byref(cw), C.byref(cu) if cu is not None else None))
 
 
+def mm_ids_workspace_bytes(w: Weight, up: Weight | None = None) -> int:
+    """Bytes of workspace the two-pass batched product needs for this matrix (or gate/up pair); 0: not taken."""
+    cw = w.c()
+    cu = up.c() if up is not None else None
+    return int(lib().bf16n_mm_ids_workspace_bytes(C.byref(cw), C.byref(cu) if cu is not None else None))
+
+
+_workspace: torch.Tensor | None = None
+
+
+def set_workspace(buf: torch.Tensor | None) -> None:
+    """Registers a device buffer (uint8, kept alive here) for the two-pass form of the batched product: with it,
+    moe_mm_ids / moe_experts on lane-major pair-Huffman experts decode into BF16 operand tiles first and multiply from
+    them on the tensor cores. None withdraws it (the fused decode-and-multiply kernel runs again)."""
+    global _workspace
+    if buf is None:
+        check(lib().bf16n_set_workspace(None, 0))
+        _workspace = None
+        return
+    if not buf.is_cuda or buf.dtype != torch.uint8 or not buf.is_contiguous():
+        raise RuntimeError("bf16n.set_workspace: a contiguous uint8 CUDA tensor")
+    off = (-buf.data_ptr()) % 1024
+    if buf.numel() <= off:
+        raise RuntimeError("bf16n.set_workspace: buffer too small")
+    check(lib().bf16n_set_workspace(buf.data_ptr() + off, buf.numel() - off))
+    _workspace = buf
+
+
+def ensure_workspace(*pairs) -> int:
+    """Grows the registered workspace to what the given (w, up) pairs need; returns its size in bytes."""
+    need = max((mm_ids_workspace_bytes(w, up) for w, up in pairs), default=0)
+    have = 0 if _workspace is None else _workspace.numel() - (-_workspace.data_ptr()) % 1024
+    if need > have:
+        dev = pairs[0][0].plane.device
+        set_workspace(None)
+        set_workspace(torch.empty(need + 1024, dtype=torch.uint8, device=dev))
+        have = need
+    return have
+
+
 def moe_route(topk_ids: torch.Tensor, n_experts: int, per_slot: bool):
     """Routing sort on the GPU: (ids_src1, ids_dst, bounds) int32 device tensors."""
     _check_ids(topk_ids)

@@ -22,10 +22,12 @@ def ops():
     return m
 
 
-@pytest.fixture(scope="module", params=["lane_major", "fragment_order"])
+@pytest.fixture(scope="module", params=["lane_major", "lane_major_two_pass", "fragment_order"])
 def layer(ops, request):
-    """The expert weights in the llama.cpp layout (chunk-major R = 8 gate / up, row-major R = 16 down: tcgen05 kernels) and
-    in the vLLM layout (16-row fragment-order bands everywhere: the mma.m16n8k16 batched kernel)."""
+    """The expert weights in the llama.cpp layout (chunk-major R = 8 gate / up, row-major R = 16 down: tcgen05 kernels;
+    once with the fused decode-and-multiply kernel, once with a workspace registered, i.e. the decode pass into operand
+    tiles followed by the tensor-core pass) and in the vLLM layout (16-row fragment-order bands everywhere: the
+    mma.m16n8k16 batched kernel)."""
     bits = {"gate": o.weights_like(E * N, H, 21), "up": o.weights_like(E * N, H, 22), "down": o.weights_like(E * H, N, 23)}
     fo = request.param == "fragment_order"
 
@@ -35,7 +37,16 @@ def layer(ops, request):
 
     enc_w = {"gate": enc(bits["gate"], 8, True), "up": enc(bits["up"], 8, True), "down": enc(bits["down"], 16, False)}
     f64 = {k: o.bf16_bits_to_f32(v).astype(np.float64) for k, v in bits.items()}
-    return bits, enc_w, f64
+    if request.param == "lane_major_two_pass":
+        assert ops.mm_ids_workspace_bytes(enc_w["gate"], enc_w["up"]) == 2 * E * N * H * 2
+        assert ops.mm_ids_workspace_bytes(enc_w["down"]) == E * H * N * 2
+        assert ops.ensure_workspace((enc_w["gate"], enc_w["up"]), (enc_w["down"], None)) >= 2 * E * N * H * 2
+    elif fo:
+        assert ops.mm_ids_workspace_bytes(enc_w["gate"], enc_w["up"]) == 0
+    yield bits, enc_w, f64
+    torch.cuda.synchronize()
+    ops.set_workspace(None)
+    assert ops.fault_status() == 0
 
 
 def routing(T, kind, seed):
