@@ -738,7 +738,7 @@ def moe_prefill_runs(args, torch, dist, ops, rank, world, dev, weights, fo=False
     ws_bytes = ops.ensure_workspace((gate, up), (down, None)) if two_pass else 0
     form = ("fragment-order kernel" if fo else "two-pass: decode into BF16 operand tiles (%.0f MB workspace), tcgen05 pass over the tiles" % (ws_bytes / 1e6)
             if two_pass else "fused decode-and-multiply kernel")
-    for T in (2048, 8192):
+    for T in ((2048, 8192) if not args.tokens else (args.tokens,)):
         fused_us = None
         flops = 6.0 * 512 * 2048 * k * T
         nbytes = (gate.nbytes + up.nbytes + down.nbytes) * world
@@ -953,6 +953,7 @@ def main():
     ap.add_argument("--rows", type=int, default=ROWS, help="rows of the matrix (default: the vocabulary projection)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-moe", action="store_true", help="skip the MoE layer and small-matrix blocks of the contract line")
+    ap.add_argument("--tokens", type=int, default=0, help="--workload moe_prefill: this token count only (default: 2048 and 8192)")
     ap.add_argument("--fused-prefill", action="store_true", help="MoE prefill: the fused decode-and-multiply kernel instead of the two-pass form")
     ap.add_argument("--fo", action="store_true", help="moe_prefill: experts in the fragment-order layout (mma.sync batched kernel)")
     ap.add_argument("--nccl", action="store_true", help="N > 1, MoE workloads: NCCL collectives instead of the fused peer stores")

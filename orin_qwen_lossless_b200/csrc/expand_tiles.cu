@@ -2,7 +2,7 @@
 // operand tiles that the tensor-core pass (k_tile_mm in prefill.cu) copies into shared memory with one bulk copy each.
 //
 // The fused prefill kernel decodes inside the block that multiplies; its 16 decoder warps per SM are register-bound and
-// their dependent table lookups set the pace of the layer. Here one unit per warp and 32 warps per SM decode with the
+// their dependent table lookups set the pace of the layer. Here one unit per warp and 28 warps per SM decode with the
 // ring reader of the large-matrix GEMV (per-lane cp.async rings, window reader, four interleaved table copies), and
 // what they write is already the shared-memory image of the B operand:
 //
@@ -26,7 +26,8 @@ namespace {
 using namespace dev;
 using namespace ring;
 
-constexpr int EXPAND_WARPS = 32;
+constexpr int EXPAND_WARPS = 28;              // 72 registers per thread: four steps of plane bytes in flight per lane
+constexpr int AHEAD = 4;                     // plane bytes are loaded this many steps (of 512 weights) before they are decoded
 constexpr int IMG_ROWS = 256;                 // rows of a row block = N of the tensor-core pass
 constexpr int IMG_KTILE_BYTES = IMG_ROWS * 128;
 
@@ -43,14 +44,14 @@ struct ExpandArgs {
 template <int C, int R, bool CM>
 __global__ void __launch_bounds__(EXPAND_WARPS * 32, 1) k_expand_tiles(const ExpandArgs p, const Opaque k) {
     constexpr int K = C * CHUNK, STEPS = R * C, KT = K / 64;
-    static_assert(STEPS % 4 == 0, "the rings are topped up every four steps (32 codes)");
+    static_assert(AHEAD == 4 && STEPS % AHEAD == 0, "the rings are topped up every four steps (32 codes), which is also the plane read-ahead");
     extern __shared__ __align__(128) unsigned char smem[];
     uint32_t * lut = (uint32_t *) smem; // four interleaved tables | one 4 KB ring set per warp
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     const uint32_t lut_s = smem_u32(lut);
     const uint32_t lut_l = lut_s + (lane & 3) * 4;
     const uint32_t key = (lut_s + LUT_BYTES + (uint32_t) warp * (32 * RING_BYTES) + lane * RING_BYTES) | ((lane & 7) << 4);
-    const PairView & w = p.w[blockIdx.y];
+    const PairView w = blockIdx.y ? p.w[1] : p.w[0];
     const int row_offset = blockIdx.y ? IMG_ROWS / 2 : 0;
     for (int i = threadIdx.x; i < HP_MAX_PAIRS; i += blockDim.x) { const uint32_t e = __ldg(w.lut + i); ((uint4 *) lut)[i] = make_uint4(e, e, e, e); }
     __syncthreads();
@@ -70,32 +71,40 @@ __global__ void __launch_bounds__(EXPAND_WARPS * 32, 1) k_expand_tiles(const Exp
         }
         cp_async_commit();
         const uint8_t * pl = w.plane + u * R * K + 16 * lane;
-        uint4 nx = ld_stream16(pl); // plane bytes one step ahead of the decode
+        // Plane bytes AHEAD steps ahead of the decode: with every SM writing tiles at the same time a load takes several
+        // microseconds, more than one step of decoding hides.
+        uint4 nx[AHEAD];
+#pragma unroll
+        for (int i = 0; i < AHEAD; i++) { nx[i] = ld_stream16(pl + i * CHUNK); }
         rd.token = cp_async_wait_all();
         rd.first_words();
-#pragma unroll 4
-        for (int t = 0; t < STEPS; t++) {
-            if (t && (t & 3) == 0) {
+#pragma unroll 1
+        for (int t0 = 0; t0 < STEPS; t0 += AHEAD) {
+            if (t0) {
                 rd.token = cp_async_wait_all(); // copies issued four steps ago
                 rd.template top_up<3>(k);
                 cp_async_commit();
             }
-            const int rr = CM ? t % R : t / C, c = CM ? t / R : t % C;
-            const uint4 sm = nx;
-            nx = ld_stream16(pl + (t + 1 < STEPS ? t + 1 : t) * CHUNK); // the last step re-reads itself: one harmless L2 hit
-            const uint32_t pw[4] = {sm.x, sm.y, sm.z, sm.w};
-            const uint32_t row = (uint32_t) (img_row0 + rr);
-            unsigned char * rp = img + (size_t) c * 8 * IMG_KTILE_BYTES + row * 128 + ((piece ^ (row & 7)) << 4);
 #pragma unroll
-            for (int half = 0; half < 2; half++) {
-                uint32_t en[4];
-                rd.take2(lut_l, k, en[0], en[1]);
-                rd.take2(lut_l, k, en[2], en[3]);
+            for (int i = 0; i < AHEAD; i++) {
+                const int t = t0 + i;
+                const int rr = CM ? t % R : t / C, c = CM ? t / R : t % C;
+                const uint4 sm = nx[i];
+                nx[i] = ld_stream16(pl + (t + AHEAD < STEPS ? t + AHEAD : t) * CHUNK); // the last steps re-read themselves: harmless L2 hits
+                const uint32_t pw[4] = {sm.x, sm.y, sm.z, sm.w};
+                const uint32_t row = (uint32_t) (img_row0 + rr);
+                unsigned char * rp = img + (size_t) c * 8 * IMG_KTILE_BYTES + row * 128 + ((piece ^ (row & 7)) << 4);
 #pragma unroll
-                for (int jj = 0; jj < 2; jj++) { // quad 2 half + jj of the chunk: k-tiles 2 (2 half + jj) and the next one
-                    const uint32_t lo = merge_sm_exp(spread_lo(pw[2 * half + jj]), en[2 * jj]);
-                    const uint32_t hi = merge_sm_exp(spread_hi(pw[2 * half + jj]), en[2 * jj + 1]);
-                    *(uint2 *) (rp + (size_t) (2 * (2 * half + jj)) * IMG_KTILE_BYTES) = make_uint2(lo, hi);
+                for (int half = 0; half < 2; half++) {
+                    uint32_t en[4];
+                    rd.take2(lut_l, k, en[0], en[1]);
+                    rd.take2(lut_l, k, en[2], en[3]);
+#pragma unroll
+                    for (int jj = 0; jj < 2; jj++) { // quad 2 half + jj of the chunk: k-tiles 2 (2 half + jj) and the next one
+                        const uint32_t lo = merge_sm_exp(spread_lo(pw[2 * half + jj]), en[2 * jj]);
+                        const uint32_t hi = merge_sm_exp(spread_hi(pw[2 * half + jj]), en[2 * jj + 1]);
+                        *(uint2 *) (rp + (size_t) (2 * (2 * half + jj)) * IMG_KTILE_BYTES) = make_uint2(lo, hi);
+                    }
                 }
             }
         }

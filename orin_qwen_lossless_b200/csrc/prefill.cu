@@ -592,7 +592,8 @@ __global__ void __launch_bounds__(TM_THREADS, 1) k_tile_mm(const TileMmArgs p) {
                     uint32_t piece_no = 0;
                     const bool bulk_out = GLU && p.dst_bf16 && p.bulk_ok;
                     for (int tg = 0; tg < ng; tg++) {
-                        const int64_t drow = my_dst[tg];
+                        static_assert(TM_G == 2, "two token groups per pass");
+                        const int64_t drow = tg ? my_dst[1] : my_dst[0];
                         const uint32_t taddr = tmem + ((uint32_t) (32 * hw) << 16) + (uint32_t) (tg * TM_N);
                         const bool live = drow >= 0 && !*failed;
                         if (GLU) { // image rows 0..127: gate, 128..255: the same rows of up
