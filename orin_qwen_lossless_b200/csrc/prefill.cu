@@ -427,23 +427,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) k_prefill(const PrefillArgs p) {
 // ---------------------------------------------------------------- second pass of the two-pass product
 //
 // k_tile_mm multiplies routed activation rows with weights that expand_tiles.cu has already decoded into operand-tile
-// images ([k-tile][256 rows][128 bytes], 128-byte swizzled, 32 KB per k-tile). Without decoders the block is six warps:
-//   * warps 0..3 gather the routed activation rows (cp.async into a ring of 128-token x 64-column slots, each slot's
-//     mbarrier completed by cp.async.mbarrier.arrive) and afterwards read the accumulators (tcgen05.ld: warp w reads TMEM
-//     lanes 32 w .. 32 w + 31 = tokens) and store them, SwiGLU applied in registers;
-//   * warp 4, one thread: tcgen05.mma with M = 128 tokens, N = 256 weight rows, K = 16; per (k-tile, token group) four of
+// images ([k-tile][256 rows][128 bytes], 128-byte swizzled, 32 KB per k-tile). Without decoders the block is ten warps:
+//   * warps 0..7 gather the routed activation rows (cp.async into a ring of 128-token x 64-column slots, each slot's
+//     mbarrier completed by cp.async.mbarrier.arrive; eight warps because one slot per 472 MMA cycles is more copy
+//     instructions than four warps issue) and afterwards read the accumulators (tcgen05.ld: warp w reads TMEM lanes
+//     32 (w % 4) .. + 31 = tokens, warps 4..7 the second half of the columns) and store them, SwiGLU in registers;
+//   * warp 8, one thread: tcgen05.mma with M = 128 tokens, N = 256 weight rows, K = 16; per (k-tile, token group) four of
 //     them; tcgen05.commit hands activation slots and weight stages back and announces the finished accumulators;
-//   * warp 5, one thread: one 32 KB bulk copy per k-tile of the item's image into a ring of four weight stages
+//   * warp 9, one thread: one 32 KB bulk copy per k-tile of the item's image into a ring of four weight stages
 //     (mbarrier expect_tx / complete_tx).
 // A work item is (expert, row block of 256 image rows); a pass covers up to TM_G x 128 of the expert's tokens, whose
 // accumulators (TM_G x 256 columns) fill tensor memory. The activations of a pass cross L2 -> shared memory once per
 // 256 weight rows, and a weight k-tile is copied once per pass.
 constexpr int TM_N = 256, TM_G = 2, TM_WST = 4, TM_XSL = 6;
-constexpr int TM_GATHERERS = 128, TM_THREADS = 192, TM_MMA_WARP = 4, TM_W_WARP = 5;
+constexpr int TM_GATHERERS = 256, TM_THREADS = 320, TM_MMA_WARP = 8, TM_W_WARP = 9;
 constexpr int TM_W_STAGE = TM_N * 128;       // one k-tile of a row block
 constexpr int TM_STAGE_ROW = 256 + 16;       // epilogue staging: 256 output bytes per thread, padded so that 16-byte stores of a quarter warp miss each other's banks
-constexpr int TM_STAGE_BYTES = TM_GATHERERS * TM_STAGE_ROW;
-static_assert(2 * TM_STAGE_BYTES <= TM_XSL * X_SLOT_BYTES, "the epilogue stages its output rows in the activation ring");
+static_assert(TM_GATHERERS * TM_STAGE_ROW <= TM_XSL * X_SLOT_BYTES, "the epilogue stages its output rows in the activation ring");
 __host__ __device__ constexpr uint32_t tm_instr_desc() { return 1u << 4 | 1u << 7 | 1u << 10 | (uint32_t) (TM_N >> 3) << 17 | (uint32_t) (M_TOK >> 4) << 24; }
 static_assert(TM_G * TM_N <= TMEM_COLS, "accumulators of a pass must fit TMEM");
 
@@ -505,6 +505,8 @@ __global__ void __launch_bounds__(TM_THREADS, 1) k_tile_mm(const TileMmArgs p) {
         // ------------------------------------------------------------------ weight stages: one bulk copy per k-tile
         if (lane == 0) {
             uint32_t n = 0, issued = 0; // stages of the walk, copies actually started (equal until a wait fails)
+            // (Asking each k-tile into L2 eight k-tiles before its bulk copy was measured and lost: 988 / 1631 us per layer
+            // at 2048 / 8192 tokens against 952 / 1567 without.)
             for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
                 const int e = item / p.blocks_per_expert;
                 const int j0 = p.bounds[e], j1 = p.bounds[e + 1];
@@ -529,7 +531,8 @@ __global__ void __launch_bounds__(TM_THREADS, 1) k_tile_mm(const TileMmArgs p) {
         }
     } else {
         // ------------------------------------------------------------------ gather warps + epilogue, MMA warp
-        const int ht = tid, hw = warp;          // gather thread index / TMEM lane quarter (warps 0..3)
+        const int ht = tid;                     // gather thread index (warps 0..7)
+        const int hw = warp & 3, part = warp >> 2; // epilogue: TMEM lane quarter, and which half of the output columns
         const bool mma_warp = warp == TM_MMA_WARP;
         uint32_t n = 0;        // weight stages consumed
         uint32_t vv = 0;       // activation slots used
@@ -544,10 +547,10 @@ __global__ void __launch_bounds__(TM_THREADS, 1) k_tile_mm(const TileMmArgs p) {
                     int64_t my_dst[TM_G];    // output row of the token whose accumulators this thread reads
 #pragma unroll
                     for (int tg = 0; tg < TM_G; tg++) {
-                        const int ti = tg * M_TOK + ht;
+                        const int ti = tg * M_TOK + (ht & (M_TOK - 1));
                         my_dst[tg] = ti < ntok ? (int64_t) p.ids_dst[jp + ti] : -1;
                     }
-                    // ---- gather: this thread copies 16-byte piece pc of rows r0, r0 + 16, ... of every slot
+                    // ---- gather: this thread copies 16-byte piece pc of rows r0, r0 + 32, ... of every slot
                     const int pc = ht & 7, r0 = ht >> 3;
                     constexpr int RSTEP = TM_GATHERERS / 8, RMAX = M_TOK / RSTEP;
                     const bf16 * src[TM_G][RMAX]; // the rows' activations at piece pc (nullptr: no such token)
@@ -582,30 +585,29 @@ __global__ void __launch_bounds__(TM_THREADS, 1) k_tile_mm(const TileMmArgs p) {
                     passes++;
                     tc_fence_after();
                     // A thread holds one token's accumulators; written row by row from there, a store instruction would touch
-                    // 32 different lines. Both output forms go through shared memory instead (the activation ring is idle
-                    // now: every MMA of the pass is complete).
-                    // A thread stages 256 bytes of its token's output row (128 BF16 SwiGLU outputs, or 64 FP32 outputs: four
-                    // pieces per token) and sends them with one bulk store; two staging rows per thread alternate, so a
-                    // store is read out while the next piece is staged. (Measured at 8192 tokens per layer: direct stores
-                    // 1.91 ms, bulk stores 1.64 ms, a warp-level transposition through shared memory with four whole
-                    // lines per store instruction 1.68 ms.)
-                    uint32_t piece_no = 0;
+                    // 32 different lines. Instead a thread stages a piece of its token's output row in shared memory (the
+                    // activation ring is idle now: every MMA of the pass is complete) and sends it with one bulk store:
+                    // 64 BF16 SwiGLU outputs (128 bytes) or 64 FP32 outputs (256 bytes). Warps 0..3 take the first half of
+                    // the output columns, warps 4..7 the second. (Measured at 8192 tokens per layer with four helper
+                    // warps: direct stores 1.91 ms, bulk stores 1.64 ms, a warp-level transposition through shared memory
+                    // with four whole lines per store instruction 1.68 ms.)
                     const bool bulk_out = GLU && p.dst_bf16 && p.bulk_ok;
+                    unsigned char * row = xbuf + ht * TM_STAGE_ROW;
                     for (int tg = 0; tg < ng; tg++) {
                         static_assert(TM_G == 2, "two token groups per pass");
                         const int64_t drow = tg ? my_dst[1] : my_dst[0];
                         const uint32_t taddr = tmem + ((uint32_t) (32 * hw) << 16) + (uint32_t) (tg * TM_N);
                         const bool live = drow >= 0 && !*failed;
                         if (GLU) { // image rows 0..127: gate, 128..255: the same rows of up
-                            const int64_t at0 = drow * p.dst_col + (int64_t) nb * (TM_N / 2);
-                            unsigned char * row = xbuf + (piece_no & 1) * TM_STAGE_BYTES + ht * TM_STAGE_ROW;
-                            if (bulk_out) { bulk_wait_read<1>(); } // the store that used this staging row two pieces ago has read it
+                            const int o0 = part * (TM_N / 4);   // this warp's 64 outputs
+                            const int64_t at0 = drow * p.dst_col + (int64_t) nb * (TM_N / 2) + o0;
+                            if (bulk_out) { bulk_wait_read<0>(); } // the previous store has read the staging row
 #pragma unroll 1
-                            for (int cc = 0; cc < TM_N / 2; cc += 32) {
+                            for (int cc = 0; cc < TM_N / 4; cc += 32) {
                                 __syncwarp(); // the TMEM loads are warp-wide
                                 uint32_t v0[32], v1[32];
-                                tmem_ld32(taddr + cc, v0);
-                                tmem_ld32(taddr + TM_N / 2 + cc, v1);
+                                tmem_ld32(taddr + o0 + cc, v0);
+                                tmem_ld32(taddr + TM_N / 2 + o0 + cc, v1);
                                 if (!live) { continue; }
                                 float r[32];
 #pragma unroll
@@ -627,16 +629,14 @@ __global__ void __launch_bounds__(TM_THREADS, 1) k_tile_mm(const TileMmArgs p) {
                                 }
                             }
                             if (bulk_out) {
-                                if (live) { proxy_fence(); bulk_s2g((bf16 *) p.dst + at0, smem_u32(row), 256); }
+                                if (live) { proxy_fence(); bulk_s2g((bf16 *) p.dst + at0, smem_u32(row), 128); }
                                 bulk_commit();
-                                piece_no++;
                             }
-                        } else if (!p.dst_bf16 && p.bulk_ok) {   // 256 FP32 outputs = four pieces of 64
+                        } else if (!p.dst_bf16 && p.bulk_ok) {   // this warp's 128 FP32 outputs = two pieces of 64
                             const int64_t at0 = drow * p.dst_col + (int64_t) nb * TM_N;
 #pragma unroll 1
-                            for (int c0 = 0; c0 < TM_N; c0 += 64) {
-                                unsigned char * row = xbuf + (piece_no & 1) * TM_STAGE_BYTES + ht * TM_STAGE_ROW;
-                                bulk_wait_read<1>();
+                            for (int c0 = part * (TM_N / 2); c0 < (part + 1) * (TM_N / 2); c0 += 64) {
+                                bulk_wait_read<0>();
 #pragma unroll 1
                                 for (int cc = c0; cc < c0 + 64; cc += 32) {
                                     __syncwarp();
@@ -648,12 +648,11 @@ __global__ void __launch_bounds__(TM_THREADS, 1) k_tile_mm(const TileMmArgs p) {
                                 }
                                 if (live) { proxy_fence(); bulk_s2g((float *) p.dst + at0 + c0, smem_u32(row), 256); }
                                 bulk_commit();
-                                piece_no++;
                             }
                         } else {
                             const int64_t at0 = drow * p.dst_col + (int64_t) nb * TM_N;
 #pragma unroll 1
-                            for (int cc = 0; cc < TM_N; cc += 32) {
+                            for (int cc = part * (TM_N / 2); cc < (part + 1) * (TM_N / 2); cc += 32) {
                                 __syncwarp();
                                 uint32_t v0[32];
                                 tmem_ld32(taddr + cc, v0);
@@ -669,7 +668,7 @@ __global__ void __launch_bounds__(TM_THREADS, 1) k_tile_mm(const TileMmArgs p) {
                     bulk_wait_read<0>(); // the staging rows are activation slots again from the next pass on
                     __syncwarp();
                     tc_fence_before();
-                    tm_helper_bar(); // all four quarters are read
+                    tm_helper_bar(); // every helper warp has read its part
                     if (tid == 0) { mbar_arrive(smem_u32(drained)); } // the next pass may overwrite the accumulators
                 } else if (lane == 0) {
                     // ---- MMA issue
