@@ -658,6 +658,8 @@ def moe_decode_runs(args, torch, dist, ops, rank, world, dev, weights, shared):
         g = torch.Generator(device=dev).manual_seed(1234 + T)   # the same tokens and routing on every rank
         xs = [torch.randn(T, 2048, device=dev, generator=g).to(torch.bfloat16) for _ in range(steps)]
         logits = [torch.randn(T, E, device=dev, generator=g) for _ in range(steps)]
+        if getattr(args, "shared_routing", False):   # a verify batch whose tokens agree on their experts
+            logits = [l[:1].expand(T, E).contiguous() for l in logits]
         scratch = ops.moe_decode_scratch(T, k, gate, down, n_local, dev)
         ids = [torch.empty(T, k, dtype=torch.int32, device=dev) for _ in range(steps)]
         wts = [torch.empty(T, k, device=dev) for _ in range(steps)]
@@ -895,9 +897,11 @@ def run_moe_decode(args):
     rank, world, dev = _dist_setup(torch)
     ops.init()
     n_local = 256 // world
-    weights = _moe_weights(ops, dev, rank * n_local, n_local)
+    weights = _moe_weights(ops, dev, rank * n_local, n_local, args.fo and world == 1)
     shared = (_enc(ops, 1024, 2048, 1, 0, False, 104, dev), _enc(ops, 2048, 512, 1, 0, False, 105, dev))
     for rec in moe_decode_runs(args, torch, dist, ops, rank, world, dev, weights, shared):
+        rec["layout"] = "fragment order" if args.fo and world == 1 else "lane-major (chunk-major R=8 gate/up, R=16 down)"
+        rec["routing"] = "every token of a step picks the same experts" if args.shared_routing else "independent N(0,1) router logits per token"
         print(json.dumps({"workload": f"MoE decode layer, {rec['tokens']} token(s), 256 experts top-8 + shared expert", **rec}), flush=True)
     if world > 1:
         dist.barrier()
@@ -955,7 +959,8 @@ def main():
     ap.add_argument("--no-moe", action="store_true", help="skip the MoE layer and small-matrix blocks of the contract line")
     ap.add_argument("--tokens", type=int, default=0, help="--workload moe_prefill: this token count only (default: 2048 and 8192)")
     ap.add_argument("--fused-prefill", action="store_true", help="MoE prefill: the fused decode-and-multiply kernel instead of the two-pass form")
-    ap.add_argument("--fo", action="store_true", help="moe_prefill: experts in the fragment-order layout (mma.sync batched kernel)")
+    ap.add_argument("--fo", action="store_true", help="moe_prefill / moe_decode (one GPU): experts in the fragment-order layout")
+    ap.add_argument("--shared-routing", action="store_true", help="moe_decode: every token of a step picks the same experts")
     ap.add_argument("--nccl", action="store_true", help="N > 1, MoE workloads: NCCL collectives instead of the fused peer stores")
     ap.add_argument("--workload", default="lm_head", choices=["lm_head", "small", "moe_decode", "moe_prefill", "dense_mid"],
                     help="lm_head is the headline contract line; the others print extra lines for the other baseline configs "

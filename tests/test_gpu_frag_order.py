@@ -110,6 +110,34 @@ def test_routed_columns(ops, K, rows_e, fp32_x):
             assert (np.abs(y[t, s_].cpu().numpy() - ref) <= GEMV_REL * s).all()
 
 
+@pytest.mark.parametrize("K,rows_e,per_slot", [(2048, 64, False), (512, 96, True)])
+@pytest.mark.parametrize("fp32_x", [False, True])
+def test_columns_of_one_expert_share_a_decode_with_the_same_bits(ops, K, rows_e, per_slot, fp32_x):
+    """Routed columns of 4..8 tokens are grouped by expert inside the kernel (up to four columns per decode; a fifth
+    starts a new group): every (token, slot) pair gets the bits it gets when its token is multiplied alone, whatever
+    else is in the batch. Routings: every token picks the same experts, one expert in every slot of every token, and a
+    mix with unshared experts."""
+    E, k = 6, 4
+    bits = o.weights_like(E * rows_e, K, 91 + K)
+    w = fo(ops, bits)
+    for T, routing in [(8, "same"), (7, "one_expert"), (5, "mixed"), (4, "same"), (2, "same")]:
+        g = np.random.default_rng(T)
+        if routing == "same":
+            ids_np = np.tile(g.permutation(E)[:k], (T, 1))
+        elif routing == "one_expert":
+            ids_np = np.full((T, k), 3)
+        else:
+            ids_np = np.stack([g.permutation(E)[:k] for _ in range(T)])
+        ids = torch.from_numpy(ids_np.astype(np.int32)).cuda()
+        x, _ = act((T, k, K) if per_slot else (T, K), 11 + T)
+        x = x.float() if fp32_x else x
+        y = ops.mmv(x, w, ids, rows_e)
+        for t in range(T):
+            alone = ops.mmv(x[t:t + 1], w, ids[t:t + 1], rows_e)
+            assert torch.equal(y[t:t + 1], alone), (routing, T, t)
+    assert ops.fault_status() == 0
+
+
 def test_get_rows_and_linear(ops):
     rows, K = 256, 2048
     bits = o.weights_like(rows, K, 5)
