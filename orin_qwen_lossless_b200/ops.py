@@ -588,6 +588,18 @@ def set_workspace(buf: torch.Tensor | None) -> None:
     _workspace = buf
 
 
+_auto_workspace = False
+
+
+def set_auto_workspace(on: bool) -> None:
+    """With on = True, moe_mm_ids (and so moe_experts and torch.ops.bf16n.moe_mm_ids) grows the registered workspace to
+    what its matrices need before it launches, unless the stream is being captured (a capture never allocates: it uses
+    the workspace registered before it, or the fused kernel). Off by default: the reference's operators allocate only
+    their outputs."""
+    global _auto_workspace
+    _auto_workspace = bool(on)
+
+
 def ensure_workspace(*pairs) -> int:
     """Grows the registered workspace to what the given (w, up) pairs need; returns its size in bytes."""
     need = max((mm_ids_workspace_bytes(w, up) for w, up in pairs), default=0)
@@ -639,6 +651,8 @@ def moe_mm_ids(x: torch.Tensor, topk_ids: torch.Tensor, w: Weight, n_experts: in
     if not lib().bf16n_mm_ids_supported(C.byref(cw), C.byref(cu) if cu is not None else None):
         raise ValueError("bf16n.moe_mm_ids: no batched kernel for this matrix (format/K/R/layout)")
     src1, dst, bounds = moe_route(topk_ids, n_experts, per_slot) if route is None else route
+    if _auto_workspace and not torch.cuda.is_current_stream_capturing():
+        ensure_workspace((w, up))
     with torch.cuda.device(x.device):
         check(lib().bf16n_mm_ids(C.byref(cw), C.byref(cu) if cu is not None else None, x.data_ptr(), w.meta.K,
                                  src1.data_ptr(), dst.data_ptr(), bounds.data_ptr(), y.data_ptr(),

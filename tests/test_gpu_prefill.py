@@ -130,6 +130,30 @@ def test_moe_layer_batched_path(ops, layer, T):
     assert err.max() <= 2.0 ** -6 * np.abs(ref).max()
 
 
+def test_workspace_on_demand(ops, layer):
+    """set_auto_workspace: the batched operator registers a workspace of the needed size itself (two-pass form from then
+    on); results agree with the fused kernel to accumulation order."""
+    bits, w, f64 = layer
+    if w["gate"].meta.frag_order or ops.mm_ids_workspace_bytes(w["down"]) == 0:
+        pytest.skip("lane-major experts only")
+    x, _ = act((40, H), 5)
+    ids = torch.from_numpy(routing(40, "uniform", 40).astype(np.int32)).cuda()
+    had_workspace = ops._workspace is not None
+    ops.set_workspace(None)
+    fused = ops.moe_mm_ids(x, ids, w["gate"], E)
+    ops.set_auto_workspace(True)
+    try:
+        two = ops.moe_mm_ids(x, ids, w["gate"], E)
+        assert ops.ensure_workspace((w["gate"], None)) >= E * N * H * 2
+    finally:
+        ops.set_auto_workspace(False)
+    assert torch.allclose(two, fused, rtol=0, atol=1e-5 * float(fused.abs().max()))
+    torch.cuda.synchronize()
+    ops.set_workspace(None)   # back to what the fixture set up for the other tests
+    if had_workspace:
+        ops.ensure_workspace((w["gate"], w["up"]), (w["down"], None))
+
+
 def test_unsupported_shapes_are_rejected(ops, layer):
     bits, w, f64 = layer
     x, _ = act((9, H), 1)
