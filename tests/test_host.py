@@ -186,3 +186,24 @@ def test_ep_layout_is_aligned_and_large_enough():
     assert offs == sorted(offs) and all(o % 256 == 0 for o in offs)
     assert lay.off_pair - lay.off_expert >= 4 * 8 * 8192 and lay.off_back - lay.off_rows >= 2 * 8 * 8192 * 2048
     assert n >= lay.off_back + 4 * 8192 * 2048
+
+
+def test_workspace_size_and_registration_rules():
+    """The two-pass batched product: workspace bytes follow from the matrix (rows x K x 2, twice for a gate/up pair;
+    0 for layouts it does not take); registering needs a 1024-byte aligned buffer. No GPU work."""
+    from orin_qwen_lossless_b200._lib import Weight, lib
+    L = lib()
+
+    def weight(rows, K, R, cm, fo=0, fmt=3):
+        w = Weight()
+        w.format, w.R, w.K, w.rows, w.cm, w.fo = fmt, R, K, rows, cm, fo
+        return w
+
+    gate, up, down = weight(256 * 512, 2048, 8, 1), weight(256 * 512, 2048, 8, 1), weight(256 * 2048, 512, 16, 0)
+    assert L.bf16n_mm_ids_workspace_bytes(C.byref(gate), C.byref(up)) == 2 * 256 * 512 * 2048 * 2
+    assert L.bf16n_mm_ids_workspace_bytes(C.byref(down), None) == 256 * 2048 * 512 * 2
+    for other in (weight(4096, 2048, 16, 0, fo=1), weight(4096, 2048, 8, 0), weight(4096, 1024, 0, 0, fmt=1)):
+        assert L.bf16n_mm_ids_workspace_bytes(C.byref(other), None) == 0
+    assert L.bf16n_set_workspace(C.c_void_p(4096 + 16), 1 << 20) == 1      # EINVAL: not 1024-byte aligned
+    assert b"1024" in L.bf16n_last_error()
+    assert L.bf16n_set_workspace(None, 0) == 0
