@@ -127,7 +127,8 @@ __global__ void __launch_bounds__(NT, 1) k_pair_gemv_rings(const PairView w, int
     tmem_ld4(x_addr(0), xa);
 
     const int64_t units = p.nrows / R;
-    for (int64_t u = (int64_t) blockIdx.x * nwarp + warp; u < units; u += (int64_t) gridDim.x * nwarp) {
+    // warp w of block b takes units w * blocks + b, + blocks * warps, ...: a matrix with few units still reaches every SM
+    for (int64_t u = (int64_t) warp * gridDim.x + blockIdx.x; u < units; u += (int64_t) gridDim.x * nwarp) {
         const int64_t g = rbase / R + u;
         RingReader rd;
         {
@@ -231,6 +232,11 @@ bool gemv_rings_applies(const bf16n_weight & w, const bf16n_mmv_args & a) {
     const int64_t C = w.K / CHUNK;
     if (w.format != FMT_HUFPAIR || w.cm || w.fo || !(C == 1 || C == 2 || C == 4) || a.nrows <= 0 || !a.x_bf16) { return false; }
     const int groups = a.ids ? a.ncols : (a.ncols + 3) / 4; // dense columns share a decode four at a time
+    // Several dense columns over a mid-size matrix (from 12 M weights and one unit per SM on): sharing the decode among
+    // up to four columns beats one staged decode per column (8192 x 2048, R = 16: 33 / 64 us at 4 / 8 tokens against
+    // 51 / 78; 16384 x 2048: 37 / 73 against 65 / 121), while a single column is faster there with the staged kernel's
+    // short prologue (23 against 30 us) and 4096 x 2048 is level.
+    if (!a.ids && a.ncols >= 2 && a.nrows * w.K >= (12ll << 20)) { return a.nrows / w.R >= (int64_t) device_info().sms; }
     return a.nrows / w.R >= (int64_t) device_info().sms * 16 * std::max(1, groups);
 }
 
@@ -243,7 +249,11 @@ void launch_rings(const bf16n_weight & w, const Cols & p, int nc, int ncols_grid
     const int max_warps = std::max(4, cap);
     int best = max_warps;
     double best_eff = 0.0;
-    for (int nw = max_warps; nw >= std::max(4, max_warps - 3); nw--) { // static round-robin: waste least of the last round
+    if (units <= sms * max_warps) { // one round: as many warps as there are units per SM (four fill the tensor-memory quarters)
+        best = (int) std::max<int64_t>(4, (units + sms - 1) / sms);
+        best_eff = 1.0;
+    }
+    for (int nw = max_warps; best_eff < 1.0 && nw >= std::max(4, max_warps - 3); nw--) { // static round-robin: waste least of the last round
         const int64_t slots = sms * nw, rounds = (units + slots - 1) / slots;
         const double eff = (double) units / (double) (rounds * slots) * (1.0 - 0.01 * (max_warps - nw));
         if (eff > best_eff + 1e-9) { best_eff = eff; best = nw; }
