@@ -12,6 +12,9 @@
 #include "bf16n/encode.h"
 #include "bf16n/format.h"
 #include "bf16n/launch.h"
+#ifdef WITH_WORKSPACE
+#include "bf16n_c.h"
+#endif
 
 #include <cuda_runtime.h>
 
@@ -313,6 +316,21 @@ static void moe_prefill(int reps) {
         const double flops = 6.0 * N * H * k * T;
         printf("{\"impl\": \"%s\", \"workload\": \"MoE prefill layer, %d tokens\", \"us\": %.1f, \"TFLOPs\": %.1f, \"sum_abs_y\": %.6e}\n",
                IMPL_NAME, T, us, flops / us / 1e6, checksum(y, (size_t) T * H, "moe_prefill_" + std::to_string(T)));
+#ifdef WITH_WORKSPACE
+        {   // this library only: the same calls with a caller-owned workspace registered (two-pass form of mm_ids)
+            const bf16n_weight cg = bf16n::detail::c(gate.w), cu = bf16n::detail::c(up.w);
+            const size_t need = bf16n_mm_ids_workspace_bytes(&cg, &cu);
+            void * ws = nullptr;
+            CK(cudaMalloc(&ws, need));
+            if (bf16n_set_workspace(ws, need) != BF16N_OK) { fprintf(stderr, "set_workspace: %s\n", bf16n_last_error()); exit(1); }
+            const double us2 = median_us(std::max(5, reps / 4), step);
+            printf("{\"impl\": \"%s\", \"workload\": \"MoE prefill layer, %d tokens, workspace registered (two-pass)\", \"us\": %.1f, \"TFLOPs\": %.1f, "
+                   "\"sum_abs_y\": %.6e}\n", IMPL_NAME, T, us2, flops / us2 / 1e6, checksum(y, (size_t) T * H, "moe_prefill_ws_" + std::to_string(T)));
+            CK(cudaDeviceSynchronize());
+            bf16n_set_workspace(nullptr, 0);
+            CK(cudaFree(ws));
+        }
+#endif
         CK(cudaFree(src1)); CK(cudaFree(dst)); CK(cudaFree(bounds)); CK(cudaFree(act)); CK(cudaFree(ys)); CK(cudaFree(y));
     }
 }

@@ -193,19 +193,26 @@ __global__ void __launch_bounds__(256) k_fo_gemv(const PairView w, int C, Cols p
 // and the activations are staged, and the plane is read four tile pairs ahead. A unit whose streams do not fit the
 // buffer (more than 3 bits per weight) is read from global memory.
 constexpr uint32_t FO_SPLIT_CAP = (BAND * CHUNK * 3 / 8 + 64 + 15) & ~15u;
-constexpr int FO_GROUP = 4;      // routed columns of one expert that share a decode
-static_assert(FO_GROUP == 4, "k_fo_gemv_split specialises its loop for 1, 2, 3 and FO_GROUP members");
+constexpr int FO_GROUP = 2;      // routed columns of one expert that share a decode (4: 80 registers, a block fewer per SM: 96 against 81 us per layer when no experts are shared)
+static_assert(FO_GROUP == 2 || FO_GROUP == 4, "k_fo_gemv_split specialises its loop for 1, 2, 3 and FO_GROUP members");
 constexpr int FO_SPLIT_XPAD = 8; // BF16 elements of padding per activation row of the tensor-core form (as XPAD below)
 // MMA = false: one column (routed or dense) on FMAs, FP32 or BF16 activations. MMA = true: up to 8 dense BF16 columns on
 // mma.m16n8k16 (the activations are the B operand, columns beyond ncols are zero rows in shared memory).
 // G > 1 (FMA form, routed columns of 4..8 tokens): columns that picked the same expert are multiplied by one decode. The
 // block of column c first looks at the other columns' expert ids: if c is the first, G-th, 2G-th ... column with its
 // expert it leads a group of up to G such columns (itself and the next ones) and the blocks of the group's other columns
-// end at once. Every column keeps its own accumulators and the order of its additions, so a (token, slot) pair gets
+// end at once. The leader's activations are staged in shared memory as before, the other members' are read from global
+// memory in the loop, so a launch without shared experts keeps the occupancy of the ungrouped kernel. Every column keeps its own accumulators and the order of its additions, so a (token, slot) pair gets
 // the same bits whatever else is in the batch (the reference's k_fo_mmv_grp / k_fo_mmv8_grp, core/include/bf16n/
 // kernels.cuh:1839, 2003, group inside the kernel as well).
+__device__ __forceinline__ float2 load_x2(const float * p) { return *(const float2 *) p; }
+__device__ __forceinline__ float2 load_x2(const bf16 * p) {
+    const uint32_t v = *(const uint32_t *) p;
+    return make_float2(bf16lo_f32(v), bf16hi_f32(v));
+}
+
 template <typename TX, bool MMA, int G = 1>
-__global__ void __launch_bounds__(256) k_fo_gemv_split(const PairView w, const AuxHeader * hdr, int C, Cols p, int nb, int ncols, const Opaque k) {
+__global__ void __launch_bounds__(256, G > 1 ? 4 : 1) k_fo_gemv_split(const PairView w, const AuxHeader * hdr, int C, Cols p, int nb, int ncols, const Opaque k) {
     static_assert(!MMA || G == 1, "grouping is for the FMA form");
     extern __shared__ __align__(128) unsigned char smem[];
     uint32_t * lut = (uint32_t *) smem;
@@ -214,7 +221,7 @@ __global__ void __launch_bounds__(256) k_fo_gemv_split(const PairView w, const A
     const int XS = (int) K + FO_SPLIT_XPAD;
     float * xs = (float *) (smem + 4 * HP_MAX_PAIRS + 128);              // MMA: 8 rows of XS BF16 values instead
     bf16 * xh = (bf16 *) xs;
-    float * part = MMA ? (float *) (xh + 8 * XS) : xs + G * K;           // [band of the block][slab][16 rows | 32 lanes x 4 | G x 16 rows]
+    float * part = MMA ? (float *) (xh + 8 * XS) : xs + K;               // [band of the block][slab][16 rows | 32 lanes x 4 | G x 16 rows]
     constexpr int PART = MMA ? 128 : 16 * G;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     unsigned char * buf = (unsigned char *) (part + nb * C * PART) + (size_t) warp * FO_SPLIT_CAP;
@@ -246,6 +253,18 @@ __global__ void __launch_bounds__(256) k_fo_gemv_split(const PairView w, const A
             if (later & 1ull) { members[m++] = cc; }
         }
     }
+    // where the other members' activations start (byte offsets from p.x: three registers), looked up once and here
+    uint32_t xoff[G];
+    xoff[0] = 0;
+#pragma unroll
+    for (int g = 1; g < G; g++) {
+        xoff[g] = 0;
+        if (g < m) {
+            const TX * xm; OutVec om; int64_t rb;
+            column<TX>(p, members[g], xm, om, rb);
+            xoff[g] = (uint32_t) ((const char *) xm - p.x);
+        }
+    }
     const int64_t bands = p.nrows / BAND, b = (int64_t) blockIdx.x * nb + j;
     const bool active = b < bands;
     const int64_t unit = active ? (rbase / BAND + b) * C + slab : 0;
@@ -271,14 +290,9 @@ __global__ void __launch_bounds__(256) k_fo_gemv_split(const PairView w, const A
             xh[n * XS + c] = n < ncols ? ((const bf16 *) (p.x + n * p.x_tok))[c] : __float2bfloat16(0.f);
         }
     } else {
-#pragma unroll
-        for (int g = 0; g < G; g++) {
-            if (g < m) {
-                const TX * xm; OutVec om; int64_t rb;
-                column<TX>(p, members[g], xm, om, rb);
-                for (int i = threadIdx.x; i < K; i += blockDim.x) { xs[g * K + i] = to_f32(xm[i]); }
-            }
-        }
+        // the leader's activations are staged as FP32; further members of a group are read from global memory in the
+        // loop (staging all of them would cost a block of every SM, grouped or not)
+        for (int i = threadIdx.x; i < K; i += blockDim.x) { xs[i] = to_f32(xg[i]); }
     }
     __syncthreads();
     const int cq = 2 * (lane & 3), g8 = lane >> 2, t4 = lane & 3;
@@ -318,9 +332,12 @@ __global__ void __launch_bounds__(256) k_fo_gemv_split(const PairView w, const A
                         for (int q8 = 0; q8 < 8; q8++) {
                             const int q = q8 & 3;
                             const float wl = bf16lo_f32(wv[q8]), wh = bf16hi_f32(wv[q8]);
+                            const int xi = (slab * 32 + 2 * pp + (q8 >> 2)) * 16 + cq + 8 * (q >> 1);
+                            const float2 x0 = *(const float2 *) (xs + xi);
+                            acc[q & 1] = fmaf(wh, x0.y, fmaf(wl, x0.x, acc[q & 1]));
 #pragma unroll
-                            for (int g = 0; g < M; g++) {
-                                const float2 xv = *(const float2 *) (xs + g * K + (slab * 32 + 2 * pp + (q8 >> 2)) * 16 + cq + 8 * (q >> 1));
+                            for (int g = 1; g < M; g++) { // the other members' activations come straight from global memory (L1)
+                                const float2 xv = load_x2((const TX *) (p.x + xoff[g]) + xi);
                                 acc[2 * g + (q & 1)] = fmaf(wh, xv.y, fmaf(wl, xv.x, acc[2 * g + (q & 1)]));
                             }
                         }
@@ -331,12 +348,10 @@ __global__ void __launch_bounds__(256) k_fo_gemv_split(const PairView w, const A
         auto by_members = [&](auto & rd, uint32_t lut_arg) {
             if constexpr (G == 1) { body(rd, lut_arg, std::integral_constant<int, 1>{}); }
             else {
-                switch (m) {
-                    case 1: body(rd, lut_arg, std::integral_constant<int, 1>{}); break;
-                    case 2: body(rd, lut_arg, std::integral_constant<int, 2>{}); break;
-                    case 3: body(rd, lut_arg, std::integral_constant<int, 3>{}); break;
-                    default: body(rd, lut_arg, std::integral_constant<int, G>{}); break;
-                }
+                if (m == 1) { body(rd, lut_arg, std::integral_constant<int, 1>{}); }
+                else if (G == 2 || m == 2) { body(rd, lut_arg, std::integral_constant<int, 2>{}); }
+                else if (m == 3) { body(rd, lut_arg, std::integral_constant<int, (G > 2 ? 3 : 2)>{}); }
+                else { body(rd, lut_arg, std::integral_constant<int, G>{}); }
             }
         };
         if (bytes <= FO_SPLIT_CAP) {
@@ -390,12 +405,11 @@ __global__ void __launch_bounds__(256) k_fo_gemv_split(const PairView w, const A
             if (g < m) {
                 float v = sums[g * 16 + lane];
                 for (int s2 = 1; s2 < C; s2++) { v += sums[s2 * PART + g * 16 + lane]; }
-                if constexpr (G > 1) {
+                if (g == 0) { out.put(b * BAND + lane, v); }
+                else {
                     const TX * xm; OutVec om; int64_t rb;
                     column<TX>(p, members[g], xm, om, rb);
                     om.put(b * BAND + lane, v);
-                } else {
-                    out.put(b * BAND + lane, v);
                 }
             }
         }
@@ -867,7 +881,7 @@ void fo_gemv_t(const bf16n_weight & w, const bf16n_mmv_args & a, cudaStream_t st
             // that two tokens do not fill), so fewer than four tokens go per column, as in the reference.
             const bool grouped = a.ids && a.n_used > 0 && a.ncols % a.n_used == 0 && a.ncols >= 4 * a.n_used && a.ncols <= 64;
             const int g = grouped ? FO_GROUP : 1;
-            const size_t shm = 4 * HP_MAX_PAIRS + 128 + (size_t) g * w.K * 4 + (size_t) nb * C * 16 * g * 4 + (size_t) nb * C * FO_SPLIT_CAP;
+            const size_t shm = 4 * HP_MAX_PAIRS + 128 + (size_t) w.K * 4 + (size_t) nb * C * 16 * g * 4 + (size_t) nb * C * FO_SPLIT_CAP;
             if (grouped) {
                 launch_chained(k_fo_gemv_split<TX, false, FO_GROUP>, grid, dim3(nb * C * 32), shm, st, pair_view(w), (const AuxHeader *) w.aux, C, p,
                                nb, a.ncols, k);

@@ -113,8 +113,8 @@ def test_routed_columns(ops, K, rows_e, fp32_x):
 @pytest.mark.parametrize("K,rows_e,per_slot", [(2048, 64, False), (512, 96, True)])
 @pytest.mark.parametrize("fp32_x", [False, True])
 def test_columns_of_one_expert_share_a_decode_with_the_same_bits(ops, K, rows_e, per_slot, fp32_x):
-    """Routed columns of 4..8 tokens are grouped by expert inside the kernel (up to four columns per decode; a fifth
-    starts a new group): every (token, slot) pair gets the bits it gets when its token is multiplied alone, whatever
+    """Routed columns of 4..8 tokens are grouped by expert inside the kernel (two columns per decode; a third starts a
+    new group): every (token, slot) pair gets the bits it gets when its token is multiplied alone, whatever
     else is in the batch. Routings: every token picks the same experts, one expert in every slot of every token, and a
     mix with unshared experts."""
     E, k = 6, 4
